@@ -1,0 +1,164 @@
+/*
+ * m3scan - C ABI of the fused Mamba-3 SSD scan for NVIDIA B200 (sm_100a).
+ *
+ * One fused operator (forward + hand-written adjoint) replaces the scan that the
+ * mamba3 crate composes from differentiable primitives.  Every entry point below
+ * names the reference interface it stands in for (paths are relative to the
+ * mamba3 crate root).  All pointers in descriptors are DEVICE pointers unless
+ * stated otherwise; tensors are dense row-major in the reference's own layouts;
+ * the library never writes to an input buffer.
+ *
+ * Threading: an m3_ctx is bound to one device and one stream and must be used by
+ * one host thread at a time; different contexts are independent.  All work is
+ * enqueued on the context's stream and returns without waiting; only
+ * m3_download and m3_sync block (the reference's only blocking call is
+ * Tensor::to_data, src/tensor/base.rs:92-96).
+ *
+ * Errors: every call returns an m3_status; nothing aborts or throws across the
+ * boundary.  m3_last_error gives the message of the last failure on a context.
+ * The codes mirror the reference's Error enum (src/error.rs:9-48).
+ */
+#ifndef M3SCAN_H
+#define M3SCAN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct m3_ctx m3_ctx;     /* device + stream + caches            */
+typedef struct m3_saved m3_saved; /* what forward keeps for the adjoint  */
+
+typedef enum {
+  M3_OK = 0,
+  M3_ERR_SHAPE = 1,       /* Error::Shape  - inconsistent extents              */
+  M3_ERR_RANK = 2,        /* Error::Rank   - kept for the host mirror          */
+  M3_ERR_CONFIG = 3,      /* Error::Config - e.g. odd d_state with rotation    */
+  M3_ERR_UNSUPPORTED = 4, /* Error::Unsupported                                */
+  M3_ERR_CUDA = 5,        /* a CUDA runtime call failed                        */
+  M3_ERR_TIMEOUT = 6,     /* a bounded device-side wait gave up                */
+  M3_ERR_NULL = 7         /* a required pointer was NULL                       */
+} m3_status;
+
+/* Element type of x, b, c, dt, lambda, theta, y and their gradients
+ * (FloatElem, src/backend.rs; f32 and bf16 are the two the build serves).
+ * a_log, d_skip, the carried state and their gradients are always float. */
+typedef enum { M3_F32 = 0, M3_BF16 = 1 } m3_dtype;
+
+/* Discretization, src/ssm/config.rs:18-42.  Euler and Trapezoid use the constant
+ * lambda of fixed_lambda() (:30-36) and ignore desc.lambda (it may be NULL). */
+typedef enum { M3_EULER = 0, M3_TRAPEZOID = 1, M3_LEARNED_TRAPEZOID = 2 } m3_discretization;
+
+/* StateDynamics, src/ssm/config.rs:45-56.  Rotational needs theta and even d_state. */
+typedef enum { M3_REAL = 0, M3_ROTATIONAL = 1 } m3_dynamics;
+
+/* Which kernel family runs.  AUTO picks the tensor-core family when the shape is
+ * one it serves and the generic family otherwise. */
+typedef enum { M3_PATH_AUTO = 0, M3_PATH_GENERIC = 1, M3_PATH_TENSOR = 2 } m3_path;
+
+/* ScanInputs, src/ssm/scan.rs:361-385.  rank is SsmMode::rank() (config.rs:74-79). */
+typedef struct {
+  int32_t batch, seq, heads, head_dim, d_state, rank;
+  int32_t chunk;          /* ScanInputs::chunk_size; clamped to [1, seq] (scan.rs:146) */
+  int32_t dtype;          /* m3_dtype */
+  int32_t discretization; /* m3_discretization */
+  int32_t dynamics;       /* m3_dynamics */
+  int32_t want_state;     /* ScanInputs::want_state */
+  int32_t path;           /* m3_path */
+  const void *x;          /* [batch, seq, heads, head_dim, rank] */
+  const void *b;          /* [batch, seq, heads, d_state, rank]  */
+  const void *c;          /* [batch, seq, heads, d_state, rank]  */
+  const void *dt;         /* [batch, seq, heads], positive       */
+  const void *lambda;     /* [batch, seq, heads] in [0,1]; NULL unless learned */
+  const void *theta;      /* [batch, seq, heads, d_state/2]; NULL for real dynamics */
+  const float *a_log;     /* [heads], A = -exp(a_log)            */
+  const float *d_skip;    /* [heads] or NULL                     */
+  const float *h0;        /* SsmState::h      [batch, heads, head_dim, d_state] or NULL */
+  const float *last_u0;   /* SsmState::last_u [batch, heads, head_dim, d_state] or NULL */
+  const float *angle0;    /* SsmState::angle  [batch, heads, d_state/2] or NULL */
+} m3_scan_desc;
+
+/* ScanOutput, src/ssm/scan.rs:446-452.  Caller-allocated.  The three state
+ * buffers are written only when want_state is set (NULL skips that one). */
+typedef struct {
+  void *y;        /* [batch, seq, heads, head_dim, rank], desc.dtype */
+  float *h;       /* [batch, heads, head_dim, d_state] */
+  float *last_u;  /* [batch, heads, head_dim, d_state] */
+  float *angle;   /* [batch, heads, d_state/2] (rotational only) */
+} m3_scan_out;
+
+/* Upstream gradients handed to the adjoint: the argument of the BackwardRule
+ * (src/autograd/graph.rs:61-62) for y, plus the optional gradients that reach the
+ * returned SsmState (states are Vars in the reference, scan.rs:294-302). */
+typedef struct {
+  const void *dy;        /* like y */
+  const float *dh;       /* like h, or NULL */
+  const float *dlast_u;  /* like last_u, or NULL */
+  const float *dangle;   /* like angle, or NULL */
+} m3_scan_bwd_in;
+
+/* Bits of grad_mask: the `wanted` slice of Var::record_with_mask
+ * (src/autograd/var.rs:169-204).  A cleared bit (or a NULL pointer) skips the store. */
+enum {
+  M3_GRAD_X = 1u << 0, M3_GRAD_B = 1u << 1, M3_GRAD_C = 1u << 2, M3_GRAD_DT = 1u << 3,
+  M3_GRAD_A_LOG = 1u << 4, M3_GRAD_LAMBDA = 1u << 5, M3_GRAD_THETA = 1u << 6,
+  M3_GRAD_D_SKIP = 1u << 7, M3_GRAD_H0 = 1u << 8, M3_GRAD_LAST_U0 = 1u << 9,
+  M3_GRAD_ANGLE0 = 1u << 10, M3_GRAD_ALL = 0x7ffu
+};
+
+/* Caller-allocated gradient buffers, shaped like the corresponding inputs. */
+typedef struct {
+  void *dx, *db, *dc, *ddt, *dlambda, *dtheta;   /* desc.dtype */
+  float *da_log, *dd_skip;                        /* [heads]    */
+  float *dh0, *dlast_u0, *dangle0;                /* float      */
+} m3_scan_grads;
+
+/* Library version string "major.minor.patch". */
+const char *m3_version(void);
+
+/* Device<R>::default() / Device::new, src/backend.rs: bind a context to a device
+ * ordinal.  The context starts on a stream of its own. */
+int m3_ctx_create(int device, m3_ctx **out);
+int m3_ctx_destroy(m3_ctx *ctx);
+/* Run on a caller-owned cudaStream_t instead (NULL = the legacy default stream). */
+int m3_ctx_set_stream(m3_ctx *ctx, void *cuda_stream);
+/* Block until everything enqueued on the context has finished. */
+int m3_sync(m3_ctx *ctx);
+/* Message of the last failure on this context ("" if none).  Never NULL. */
+const char *m3_last_error(const m3_ctx *ctx);
+/* Kernels launched through this context so far (the reference's launch_count(),
+ * src/backend.rs:231-281). */
+uint64_t m3_launch_count(const m3_ctx *ctx);
+
+/* Device buffers owned by the library: Tensor::zeros / from_f32 / to_data,
+ * src/tensor/base.rs:21-199. */
+int m3_alloc(m3_ctx *ctx, size_t bytes, void **out);
+int m3_free(m3_ctx *ctx, void *ptr);
+int m3_upload(m3_ctx *ctx, void *dst_device, const void *src_host, size_t bytes);
+int m3_download(m3_ctx *ctx, void *dst_host, const void *src_device, size_t bytes);
+
+/* mamba3_scan, src/ssm/scan.rs:458-618 (with ssd_chunked :116-291 folded in).
+ * `saved` may be NULL (inference, no rule is built: var.rs:174-180); otherwise it
+ * receives a handle the caller frees with m3_saved_free after the last backward.
+ * The saved context refers to the input buffers of `desc`: keep them alive and
+ * unchanged until then (the reference's closure holds clones, var.rs:210-216). */
+int m3_scan_forward(m3_ctx *ctx, const m3_scan_desc *desc, const m3_scan_out *out,
+                    m3_saved **saved);
+
+/* The BackwardRule of the fused node (src/autograd/graph.rs:61-62).  It does not
+ * consume `saved`, so it may run again (backward_retain, var.rs:218-221). */
+int m3_scan_backward(m3_ctx *ctx, const m3_saved *saved, const m3_scan_bwd_in *in,
+                     uint32_t grad_mask, const m3_scan_grads *grads);
+
+int m3_saved_free(m3_ctx *ctx, m3_saved *saved);
+
+/* Bytes of device scratch a forward with this descriptor allocates (kept until
+ * m3_saved_free when `saved` is requested). */
+size_t m3_scan_scratch_bytes(const m3_scan_desc *desc, int for_backward);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* M3SCAN_H */

@@ -1,0 +1,86 @@
+"""ctypes binding of libm3scan.so - the same declarations a Rust `-sys` crate would carry.
+
+The structures mirror include/m3scan.h field for field.  Loading fails loudly when the
+library has not been built: there is no CPU or eager fallback behind this module.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_LIB_PATH = Path(__file__).resolve().parent / "libm3scan.so"
+
+# m3_status
+OK, ERR_SHAPE, ERR_RANK, ERR_CONFIG, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_NULL = range(8)
+# m3_dtype
+F32, BF16 = 0, 1
+# m3_path
+PATH_AUTO, PATH_GENERIC, PATH_TENSOR = 0, 1, 2
+
+GRAD_X, GRAD_B, GRAD_C, GRAD_DT, GRAD_A_LOG, GRAD_LAMBDA, GRAD_THETA, GRAD_D_SKIP, \
+    GRAD_H0, GRAD_LAST_U0, GRAD_ANGLE0 = (1 << i for i in range(11))
+GRAD_ALL = 0x7FF
+
+
+class ScanDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in (
+        "batch", "seq", "heads", "head_dim", "d_state", "rank", "chunk", "dtype",
+        "discretization", "dynamics", "want_state", "path")] + [(n, C.c_void_p) for n in (
+        "x", "b", "c", "dt", "lambda_", "theta", "a_log", "d_skip", "h0", "last_u0", "angle0")]
+
+
+class ScanOut(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("y", "h", "last_u", "angle")]
+
+
+class ScanBwdIn(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("dy", "dh", "dlast_u", "dangle")]
+
+
+class ScanGrads(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in (
+        "dx", "db", "dc", "ddt", "dlambda", "dtheta", "da_log", "dd_skip", "dh0", "dlast_u0", "dangle0")]
+
+
+# name -> (restype, argtypes); every symbol include/m3scan.h declares.
+SYMBOLS = {
+    "m3_version": (C.c_char_p, []),
+    "m3_ctx_create": (C.c_int, [C.c_int, C.POINTER(C.c_void_p)]),
+    "m3_ctx_destroy": (C.c_int, [C.c_void_p]),
+    "m3_ctx_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "m3_sync": (C.c_int, [C.c_void_p]),
+    "m3_last_error": (C.c_char_p, [C.c_void_p]),
+    "m3_launch_count": (C.c_uint64, [C.c_void_p]),
+    "m3_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "m3_free": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "m3_upload": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "m3_download": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "m3_scan_forward": (C.c_int, [C.c_void_p, C.POINTER(ScanDesc), C.POINTER(ScanOut), C.POINTER(C.c_void_p)]),
+    "m3_scan_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(ScanBwdIn), C.c_uint32, C.POINTER(ScanGrads)]),
+    "m3_saved_free": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "m3_scan_scratch_bytes": (C.c_size_t, [C.POINTER(ScanDesc), C.c_int]),
+}
+
+_lib = None
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def load():
+    """Load libm3scan.so and type its entry points.  Raises if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.exists():
+        raise RuntimeError(
+            f"{_LIB_PATH} is missing: build it with `python -m mamba_trainer_b200.build` "
+            "(there is no fallback implementation)")
+    lib = C.CDLL(str(_LIB_PATH))
+    for name, (res, args) in SYMBOLS.items():
+        fn = getattr(lib, name)  # AttributeError if the library does not export it
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

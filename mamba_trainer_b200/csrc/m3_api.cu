@@ -1,0 +1,288 @@
+// C ABI of libm3scan: contexts, device buffers, and the forward / backward entry
+// points that validate a descriptor, lay out scratch and enqueue a kernel family.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "m3_internal.h"
+
+struct m3_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  uint64_t launches = 0;
+  char err[512] = {0};
+};
+
+struct m3_saved {
+  m3_scan_desc desc;
+  m3::Dims dims;
+  int path = M3_PATH_GENERIC;
+  char* ws_base = nullptr;
+  size_t ws_bytes = 0;
+  m3::GenericWs gws;
+};
+
+namespace {
+
+int fail(m3_ctx* ctx, int code, const char* fmt, ...) {
+  if (ctx) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
+    va_end(ap);
+  }
+  return code;
+}
+
+int cuda_fail(m3_ctx* ctx, cudaError_t e, const char* what) {
+  return fail(ctx, M3_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define M3_CUDA(ctx, call)                                   \
+  do {                                                       \
+    cudaError_t e_ = (call);                                 \
+    if (e_ != cudaSuccess) return cuda_fail(ctx, e_, #call); \
+  } while (0)
+
+// Largest number of rows (chunk length x rank) one chunk of the generic family may
+// have: its band tile lives in shared memory.  The scan's result does not depend on
+// the chunk length (only terms below exp(-60) move), so a longer requested chunk is
+// split; src/ssm/scan.rs:146 clamps the request in the same spirit.
+constexpr int kGenericMaxRows = 512;
+
+int make_dims(m3_ctx* ctx, const m3_scan_desc& s, m3::Dims* out) {
+  if (s.batch <= 0 || s.heads <= 0 || s.head_dim <= 0 || s.d_state <= 0 || s.rank <= 0 || s.seq < 0)
+    return fail(ctx, M3_ERR_SHAPE, "extents must be positive (batch %d seq %d heads %d head_dim %d d_state %d rank %d)",
+                s.batch, s.seq, s.heads, s.head_dim, s.d_state, s.rank);
+  if (s.dtype != M3_F32 && s.dtype != M3_BF16) return fail(ctx, M3_ERR_UNSUPPORTED, "dtype %d", s.dtype);
+  if (s.discretization < M3_EULER || s.discretization > M3_LEARNED_TRAPEZOID)
+    return fail(ctx, M3_ERR_CONFIG, "discretization %d", s.discretization);
+  if (s.dynamics != M3_REAL && s.dynamics != M3_ROTATIONAL) return fail(ctx, M3_ERR_CONFIG, "dynamics %d", s.dynamics);
+  if (s.dynamics == M3_ROTATIONAL && (s.d_state % 2))
+    return fail(ctx, M3_ERR_CONFIG, "rotational dynamics require an even d_state");
+  if (s.rank > 64) return fail(ctx, M3_ERR_UNSUPPORTED, "rank %d > 64", s.rank);
+  if (!s.x || !s.b || !s.c || !s.dt || !s.a_log) return fail(ctx, M3_ERR_NULL, "x, b, c, dt and a_log are required");
+  if (s.discretization == M3_LEARNED_TRAPEZOID && !s.lambda) return fail(ctx, M3_ERR_NULL, "learned trapezoid needs lambda");
+  if (s.dynamics == M3_ROTATIONAL && !s.theta) return fail(ctx, M3_ERR_NULL, "rotational dynamics need theta");
+  if ((s.h0 == nullptr) != (s.last_u0 == nullptr)) return fail(ctx, M3_ERR_NULL, "a carried state needs both h and last_u");
+  if ((size_t)s.batch * s.heads > 65535u) return fail(ctx, M3_ERR_UNSUPPORTED, "batch * heads > 65535");
+  m3::Dims d;
+  d.B = s.batch; d.T = s.seq; d.H = s.heads; d.P = s.head_dim; d.N = s.d_state; d.R = s.rank;
+  int L = s.chunk < 1 ? 1 : s.chunk;
+  if (s.seq > 0 && L > s.seq) L = s.seq;
+  const int cap = kGenericMaxRows / s.rank > 0 ? kGenericMaxRows / s.rank : 1;
+  if (L > cap) L = cap;
+  d.L = L;
+  d.C = (s.seq + L - 1) / L;
+  d.Tp = d.C * L;
+  d.rot = s.dynamics == M3_ROTATIONAL;
+  d.NH = d.rot ? s.d_state / 2 : 0;
+  d.disc = s.discretization;
+  d.LR = L * s.rank;
+  *out = d;
+  return M3_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* m3_version(void) { return "0.1.0"; }
+
+int m3_ctx_create(int device, m3_ctx** out) {
+  if (!out) return M3_ERR_NULL;
+  *out = nullptr;
+  m3_ctx* ctx = new (std::nothrow) m3_ctx();
+  if (!ctx) return M3_ERR_CUDA;
+  ctx->device = device;
+  cudaError_t e = cudaSetDevice(device);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+  if (e != cudaSuccess) {
+    delete ctx;
+    return M3_ERR_CUDA;
+  }
+  ctx->own_stream = true;
+  // Keep freed scratch in the stream-ordered pool instead of returning it to the
+  // driver, so steady-state calls do not pay for allocation.
+  cudaMemPool_t pool;
+  if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+    uint64_t keep = UINT64_MAX;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+  }
+  *out = ctx;
+  return M3_OK;
+}
+
+int m3_ctx_destroy(m3_ctx* ctx) {
+  if (!ctx) return M3_OK;
+  cudaSetDevice(ctx->device);
+  if (ctx->own_stream && ctx->stream) {
+    cudaStreamSynchronize(ctx->stream);
+    cudaStreamDestroy(ctx->stream);
+  }
+  delete ctx;
+  return M3_OK;
+}
+
+int m3_ctx_set_stream(m3_ctx* ctx, void* cuda_stream) {
+  if (!ctx) return M3_ERR_NULL;
+  if (ctx->own_stream && ctx->stream) {
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    cudaStreamDestroy(ctx->stream);
+  }
+  ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+  ctx->own_stream = false;
+  return M3_OK;
+}
+
+int m3_sync(m3_ctx* ctx) {
+  if (!ctx) return M3_ERR_NULL;
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  M3_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return M3_OK;
+}
+
+const char* m3_last_error(const m3_ctx* ctx) { return ctx ? ctx->err : "null context"; }
+
+uint64_t m3_launch_count(const m3_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int m3_alloc(m3_ctx* ctx, size_t bytes, void** out) {
+  if (!ctx || !out) return M3_ERR_NULL;
+  *out = nullptr;
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  M3_CUDA(ctx, cudaMalloc(out, bytes ? bytes : 1));
+  return M3_OK;
+}
+
+int m3_free(m3_ctx* ctx, void* ptr) {
+  if (!ctx) return M3_ERR_NULL;
+  if (!ptr) return M3_OK;
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  M3_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  M3_CUDA(ctx, cudaFree(ptr));
+  return M3_OK;
+}
+
+int m3_upload(m3_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  if (!ctx || (bytes && (!dst || !src))) return M3_ERR_NULL;
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  M3_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  return M3_OK;
+}
+
+int m3_download(m3_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  if (!ctx || (bytes && (!dst || !src))) return M3_ERR_NULL;
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  M3_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  M3_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return M3_OK;
+}
+
+size_t m3_scan_scratch_bytes(const m3_scan_desc* desc, int for_backward) {
+  if (!desc) return 0;
+  m3::Dims d;
+  m3_scan_desc s = *desc;
+  // Only the extents matter here: stand in for pointers the caller may not have yet.
+  static const float dummy = 0.0f;
+  s.x = s.b = s.c = s.dt = &dummy; s.a_log = &dummy;
+  if (s.discretization == M3_LEARNED_TRAPEZOID) s.lambda = &dummy;
+  if (s.dynamics == M3_ROTATIONAL) s.theta = &dummy;
+  s.h0 = s.last_u0 = nullptr;
+  if (make_dims(nullptr, s, &d) != M3_OK || d.T == 0) return 0;
+  size_t n = m3::generic_ws_layout(d, nullptr, nullptr);
+  if (for_backward) n += m3::generic_bwd_ws_layout(d, nullptr, nullptr);
+  return n;
+}
+
+int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* out, m3_saved** saved) {
+  if (saved) *saved = nullptr;
+  if (!ctx) return M3_ERR_NULL;
+  if (!desc || !out) return fail(ctx, M3_ERR_NULL, "descriptor and outputs are required");
+  m3::Dims d;
+  int rc = make_dims(ctx, *desc, &d);
+  if (rc != M3_OK) return rc;
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  const size_t PN = (size_t)d.P * d.N, BH = (size_t)d.B * d.H;
+  if (d.T == 0) {
+    // Nothing to scan (scan.rs:134-144): the carried state passes through.
+    if (desc->want_state) {
+      if (out->h) {
+        if (desc->h0) M3_CUDA(ctx, cudaMemcpyAsync(out->h, desc->h0, BH * PN * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        else M3_CUDA(ctx, cudaMemsetAsync(out->h, 0, BH * PN * 4, ctx->stream));
+      }
+      if (out->last_u) {
+        if (desc->last_u0) M3_CUDA(ctx, cudaMemcpyAsync(out->last_u, desc->last_u0, BH * PN * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        else M3_CUDA(ctx, cudaMemsetAsync(out->last_u, 0, BH * PN * 4, ctx->stream));
+      }
+      if (out->angle && d.rot) {
+        if (desc->angle0) M3_CUDA(ctx, cudaMemcpyAsync(out->angle, desc->angle0, BH * d.NH * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        else M3_CUDA(ctx, cudaMemsetAsync(out->angle, 0, BH * d.NH * 4, ctx->stream));
+      }
+    }
+    return M3_OK;
+  }
+  if (!out->y) return fail(ctx, M3_ERR_NULL, "y is required");
+  if (desc->path == M3_PATH_TENSOR) return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family does not take this shape");
+  const size_t bytes = m3::generic_ws_layout(d, nullptr, nullptr);
+  char* base = nullptr;
+  M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&base), bytes, ctx->stream));
+  m3::GenericWs ws;
+  m3::generic_ws_layout(d, &ws, base);
+  cudaError_t e = m3::generic_forward(ctx->stream, d, *desc, *out, ws, &ctx->launches);
+  if (e != cudaSuccess) {
+    cudaFreeAsync(base, ctx->stream);
+    return cuda_fail(ctx, e, "generic forward");
+  }
+  if (saved) {
+    m3_saved* sv = new (std::nothrow) m3_saved();
+    if (!sv) {
+      cudaFreeAsync(base, ctx->stream);
+      return fail(ctx, M3_ERR_CUDA, "out of host memory");
+    }
+    sv->desc = *desc;
+    sv->dims = d;
+    sv->path = M3_PATH_GENERIC;
+    sv->ws_base = base;
+    sv->ws_bytes = bytes;
+    sv->gws = ws;
+    *saved = sv;
+  } else {
+    M3_CUDA(ctx, cudaFreeAsync(base, ctx->stream));
+  }
+  return M3_OK;
+}
+
+int m3_scan_backward(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* in, uint32_t grad_mask,
+                     const m3_scan_grads* grads) {
+  if (!ctx) return M3_ERR_NULL;
+  if (!saved || !in || !grads) return fail(ctx, M3_ERR_NULL, "saved context, upstream gradients and outputs are required");
+  if (!in->dy) return fail(ctx, M3_ERR_NULL, "dy is required");
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  const m3::Dims& d = saved->dims;
+  const size_t bytes = m3::generic_bwd_ws_layout(d, nullptr, nullptr);
+  char* base = nullptr;
+  M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&base), bytes, ctx->stream));
+  m3::GenericBwdWs bw;
+  m3::generic_bwd_ws_layout(d, &bw, base);
+  cudaError_t e = m3::generic_backward(ctx->stream, d, saved->desc, saved->gws, bw, *in, grad_mask, *grads,
+                                       &ctx->launches);
+  cudaError_t e2 = cudaFreeAsync(base, ctx->stream);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "generic backward");
+  if (e2 != cudaSuccess) return cuda_fail(ctx, e2, "cudaFreeAsync");
+  return M3_OK;
+}
+
+int m3_saved_free(m3_ctx* ctx, m3_saved* saved) {
+  if (!ctx) return M3_ERR_NULL;
+  if (!saved) return M3_OK;
+  cudaSetDevice(ctx->device);
+  cudaError_t e = saved->ws_base ? cudaFreeAsync(saved->ws_base, ctx->stream) : cudaSuccess;
+  delete saved;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFreeAsync");
+  return M3_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,58 @@
+// Host-side declarations shared by the translation units of libm3scan.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/m3scan.h"
+#include "m3_common.cuh"
+
+namespace m3 {
+
+// Scratch of the generic family, all float, head-major (bh = b * H + h) so that the
+// rows of one chunk are contiguous.  Row rho = t * R + r.
+struct GenericWs {
+  float* Xh;     // [BH, Tp*R, P]   x, ranks as rows
+  float* Bh;     // [BH, Tp*R, N]   rotated B
+  float* Ch;     // [BH, Tp*R, N]   rotated C
+  float* acum;   // [BH, Tp]        in-chunk cumulative log decay
+  float* g;      // [BH, Tp]        diagonal weight
+  float* w;      // [BH, Tp]        off-diagonal weight
+  float* phi;    // [BH, Tp, NH]    wrapped cumulative angle
+  float* abase;  // [BH, C, NH]     angle entering each chunk
+  float* Hs;     // [BH, C+1, P, N] state entering chunk k; slot C = final state
+};
+
+// Extra scratch of the generic backward.
+struct GenericBwdWs {
+  float* dXh;    // [BH, Tp*R, P]
+  float* dBh;    // [BH, Tp*R, N]
+  float* dCh;    // [BH, Tp*R, N]
+  float* dHs;    // [BH, C, P, N]   local dH, then dS_k in place
+  float* dBand;  // [BH, C, L, L]
+  float* dcd;    // [BH, C]
+  float* dac;    // [BH, Tp]  d acum partial from the carry-out term
+  float* dws;    // [BH, Tp]  dw from the chunk-state term
+  float* dast;   // [BH, Tp]  d acum from the chunk-state term (sigma w q inside)
+  float* da;     // [BH, Tp]
+  float* dg;     // [BH, Tp]
+  float* dw;     // [BH, Tp]
+  float* dphi;   // [BH, Tp, NH]  then dstep in place
+  float* dpsum;  // [BH, C, NH]
+  float* ddt_rot;// [BH, Tp]
+  float* partA;  // [BH, C]   partial sums for d a_log
+  float* partD;  // [BH, C]   partial sums for d d_skip
+  float* ip0;    // [BH]      <dH_0, last_u0>
+};
+
+size_t generic_ws_layout(const Dims& d, GenericWs* ws, char* base);
+size_t generic_bwd_ws_layout(const Dims& d, GenericBwdWs* ws, char* base);
+
+cudaError_t generic_forward(cudaStream_t st, const Dims& d, const m3_scan_desc& desc,
+                            const m3_scan_out& out, const GenericWs& ws, uint64_t* launches);
+cudaError_t generic_backward(cudaStream_t st, const Dims& d, const m3_scan_desc& desc,
+                             const GenericWs& ws, const GenericBwdWs& bw,
+                             const m3_scan_bwd_in& in, uint32_t mask,
+                             const m3_scan_grads& grads, uint64_t* launches);
+
+}  // namespace m3

@@ -1,0 +1,302 @@
+"""Host side of the fused Mamba-3 scan: the reference's entry points over the C ABI.
+
+`ScanInputs`, `ScanOutput`, `SsmState` and `mamba3_scan` keep the names, argument
+meaning and error behaviour of src/ssm/scan.rs (:294-358, :361-443, :446-452,
+:458-618).  Where the reference composes ~25 differentiable primitives and lets its
+tape derive the backward pass, this module registers ONE node whose backward rule is
+the library's hand-written adjoint - the arrangement `Var::record_with_mask`
+(src/autograd/var.rs:169-204) gives a fused op in the reference.  PyTorch supplies
+device memory, streams and the tape; all arithmetic happens in libm3scan.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .. import _ffi
+from ..error import ConfigError, NullError, RankError, ShapeError, UnsupportedError, from_status
+from .config import Discretization
+
+_DTYPES = {torch.float32: _ffi.F32, torch.bfloat16: _ffi.BF16}
+
+
+class Context:
+    """One m3_ctx per CUDA device; work is enqueued on torch's current stream."""
+
+    _by_device: dict = {}
+
+    def __init__(self, device_index: int):
+        self.lib = _ffi.load()
+        self.device_index = device_index
+        handle = C.c_void_p()
+        rc = self.lib.m3_ctx_create(device_index, C.byref(handle))
+        if rc != _ffi.OK:
+            raise from_status(rc, f"m3_ctx_create({device_index}) failed")
+        self.handle = handle
+        self._stream = None
+
+    @classmethod
+    def for_device(cls, device: torch.device) -> "Context":
+        if device.type != "cuda":
+            raise UnsupportedError(f"the fused scan runs on CUDA devices only, got {device}")
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        ctx = cls._by_device.get(idx)
+        if ctx is None:
+            ctx = cls._by_device[idx] = Context(idx)
+        ctx.bind_current_stream()
+        return ctx
+
+    def bind_current_stream(self) -> None:
+        stream = torch.cuda.current_stream(self.device_index).cuda_stream
+        if stream != self._stream:
+            self.check(self.lib.m3_ctx_set_stream(self.handle, C.c_void_p(stream)))
+            self._stream = stream
+
+    def check(self, rc: int) -> None:
+        if rc != _ffi.OK:
+            raise from_status(rc, self.lib.m3_last_error(self.handle).decode())
+
+    def launch_count(self) -> int:
+        return int(self.lib.m3_launch_count(self.handle))
+
+    def sync(self) -> None:
+        self.check(self.lib.m3_sync(self.handle))
+
+
+class _Saved:
+    """Owns an m3_saved handle; freed when the tape node is dropped."""
+
+    def __init__(self, ctx: Context, handle: C.c_void_p):
+        self.ctx, self.handle = ctx, handle
+
+    def __del__(self):
+        if self.handle:
+            try:
+                self.ctx.lib.m3_saved_free(self.ctx.handle, self.handle)
+            except Exception:  # interpreter shutdown
+                pass
+            self.handle = None
+
+
+@dataclass
+class SsmState:
+    """State a Mamba-3 layer carries between windows (scan.rs:294-302)."""
+    h: torch.Tensor                        # [batch, heads, head_dim, d_state]
+    last_u: torch.Tensor                   # same shape
+    angle: Optional[torch.Tensor] = None   # [batch, heads, d_state / 2]
+
+    def num_elements(self) -> int:
+        return self.h.numel() + self.last_u.numel() + (self.angle.numel() if self.angle is not None else 0)
+
+    @staticmethod
+    def zeros(batch, heads, head_dim, d_state, rotational, device) -> "SsmState":
+        shape = (batch, heads, head_dim, d_state)
+        return SsmState(
+            torch.zeros(shape, device=device), torch.zeros(shape, device=device),
+            torch.zeros((batch, heads, d_state // 2), device=device) if rotational else None)
+
+    def detach(self) -> "SsmState":
+        return SsmState(self.h.detach(), self.last_u.detach(),
+                        self.angle.detach() if self.angle is not None else None)
+
+    def clone(self) -> "SsmState":
+        return SsmState(self.h, self.last_u, self.angle)
+
+
+@dataclass
+class ScanInputs:
+    """Inputs to a full scan, after projection and normalisation (scan.rs:361-385)."""
+    x: torch.Tensor        # [batch, seq, heads, head_dim, rank]
+    b: torch.Tensor        # [batch, seq, heads, d_state, rank]
+    c: torch.Tensor        # [batch, seq, heads, d_state, rank]
+    dt: torch.Tensor       # [batch, seq, heads], positive
+    a_log: torch.Tensor    # [heads]
+    lambda_: Optional[torch.Tensor]  # [batch, seq, heads] in [0, 1]
+    theta: Optional[torch.Tensor] = None    # [batch, seq, heads, d_state / 2]
+    d_skip: Optional[torch.Tensor] = None   # [heads]
+    state: Optional[SsmState] = None
+    chunk_size: int = 64
+    want_state: bool = True
+    # Not in the reference: lets a caller that knows lambda is the constant of
+    # Discretization::fixed_lambda skip reading it (lambda_ may then be None).
+    discretization: Discretization = Discretization.LearnedTrapezoid
+    path: int = _ffi.PATH_AUTO
+
+    @staticmethod
+    def new(x, b, c, dt, a_log, lambda_) -> "ScanInputs":
+        return ScanInputs(x, b, c, dt, a_log, lambda_)
+
+    def with_theta(self, theta) -> "ScanInputs":
+        self.theta = theta
+        return self
+
+    def with_skip(self, d_skip) -> "ScanInputs":
+        self.d_skip = d_skip
+        return self
+
+    def with_state(self, state: SsmState) -> "ScanInputs":
+        self.state = state
+        return self
+
+    def with_chunk_size(self, chunk_size: int) -> "ScanInputs":
+        self.chunk_size = chunk_size
+        return self
+
+    def with_state_output(self, want_state: bool) -> "ScanInputs":
+        self.want_state = want_state
+        return self
+
+    def with_discretization(self, discretization: Discretization) -> "ScanInputs":
+        self.discretization = Discretization(discretization)
+        return self
+
+    def with_path(self, path: int) -> "ScanInputs":
+        self.path = path
+        return self
+
+
+@dataclass
+class ScanOutput:
+    """Result of a scan (scan.rs:446-452)."""
+    y: torch.Tensor                 # [batch, seq, heads, head_dim, rank]
+    state: Optional[SsmState]
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+class _FusedScan(torch.autograd.Function):
+    """The fused node: forward = m3_scan_forward, backward rule = m3_scan_backward."""
+
+    @staticmethod
+    def forward(fctx, opts, x, b, c, dt, a_log, lam, theta, d_skip, h0, last_u0, angle0):
+        ctx = Context.for_device(x.device)
+        B, T, H, P, R = x.shape
+        N = b.shape[3]
+        desc = _ffi.ScanDesc(
+            batch=B, seq=T, heads=H, head_dim=P, d_state=N, rank=R, chunk=int(opts["chunk"]),
+            dtype=_DTYPES[x.dtype], discretization=int(opts["disc"]),
+            dynamics=1 if theta is not None else 0, want_state=1 if opts["want_state"] else 0,
+            path=int(opts["path"]),
+            x=_ptr(x), b=_ptr(b), c=_ptr(c), dt=_ptr(dt), lambda_=_ptr(lam), theta=_ptr(theta),
+            a_log=_ptr(a_log), d_skip=_ptr(d_skip), h0=_ptr(h0), last_u0=_ptr(last_u0), angle0=_ptr(angle0))
+        y = torch.empty_like(x)
+        h = lu = ang = None
+        if opts["want_state"]:
+            h = torch.empty((B, H, P, N), device=x.device, dtype=torch.float32)
+            lu = torch.empty((B, H, P, N), device=x.device, dtype=torch.float32)
+            if theta is not None:
+                ang = torch.empty((B, H, N // 2), device=x.device, dtype=torch.float32)
+        out = _ffi.ScanOut(y=_ptr(y), h=_ptr(h), last_u=_ptr(lu), angle=_ptr(ang))
+        tensors = (x, b, c, dt, a_log, lam, theta, d_skip, h0, last_u0, angle0)
+        # forward runs with grad mode off, so ask the node which parents are tracked
+        # (the `wanted` mask of Var::record_with_mask); none => inference, no rule built.
+        track = any(fctx.needs_input_grad)
+        saved = C.c_void_p()
+        ctx.check(ctx.lib.m3_scan_forward(ctx.handle, C.byref(desc), C.byref(out),
+                                          C.byref(saved) if track else None))
+        if track:
+            fctx.m3 = ctx
+            fctx.saved = _Saved(ctx, saved)
+            fctx.save_for_backward(*[t for t in tensors if t is not None])
+            fctx.present = [t is not None for t in tensors]
+            fctx.set_materialize_grads(False)
+        outs = [y] + [t for t in (h, lu, ang) if t is not None]
+        fctx.n_state_out = len(outs) - 1
+        fctx.has_angle = ang is not None
+        return tuple(outs)
+
+    @staticmethod
+    def backward(fctx, dy, *dstate):
+        ctx = fctx.m3
+        ctx.bind_current_stream()
+        it = iter(fctx.saved_tensors)
+        x, b, c, dt, a_log, lam, theta, d_skip, h0, lu0, ang0 = (
+            next(it) if p else None for p in fctx.present)
+        dstate = list(dstate) + [None] * (3 - len(dstate))
+        dh, dlu, dang = dstate[0], dstate[1], dstate[2] if fctx.has_angle else None
+        if dy is None:
+            dy = torch.zeros_like(x)
+        need = fctx.needs_input_grad[1:]
+        names = ("x", "b", "c", "dt", "a_log", "lam", "theta", "d_skip", "h0", "lu0", "ang0")
+        inputs = dict(zip(names, (x, b, c, dt, a_log, lam, theta, d_skip, h0, lu0, ang0)))
+        grads, mask = {}, 0
+        for i, name in enumerate(names):
+            t = inputs[name]
+            if t is not None and need[i]:
+                grads[name] = torch.empty_like(t)
+                mask |= 1 << i
+        cont = lambda t: t.contiguous() if t is not None else None
+        dy, dh, dlu, dang = cont(dy), cont(dh), cont(dlu), cont(dang)
+        bin_ = _ffi.ScanBwdIn(dy=_ptr(dy), dh=_ptr(dh), dlast_u=_ptr(dlu), dangle=_ptr(dang))
+        g = lambda n: _ptr(grads.get(n))
+        gout = _ffi.ScanGrads(dx=g("x"), db=g("b"), dc=g("c"), ddt=g("dt"), dlambda=g("lam"),
+                              dtheta=g("theta"), da_log=g("a_log"), dd_skip=g("d_skip"),
+                              dh0=g("h0"), dlast_u0=g("lu0"), dangle0=g("ang0"))
+        ctx.check(ctx.lib.m3_scan_backward(ctx.handle, fctx.saved.handle, C.byref(bin_),
+                                           C.c_uint32(mask), C.byref(gout)))
+        return (None,) + tuple(grads.get(n) for n in names)
+
+
+def _expect_rank(t: torch.Tensor, rank: int) -> None:
+    if t.dim() != rank:
+        raise RankError(rank, t.dim(), t.shape)
+
+
+def mamba3_scan(inputs: ScanInputs) -> ScanOutput:
+    """Run the Mamba-3 selective scan (scan.rs:458-618) as one fused device op."""
+    x, b, c = inputs.x, inputs.b, inputs.c
+    _expect_rank(x, 5)                                   # scan.rs:462
+    _expect_rank(b, 5)
+    _expect_rank(c, 5)
+    B, T, H, P, R = x.shape
+    N = b.shape[3]
+    if x.dtype not in _DTYPES:
+        raise UnsupportedError(f"element type {x.dtype}: float32 and bfloat16 are served")
+    if tuple(b.shape) != (B, T, H, N, R) or tuple(c.shape) != (B, T, H, N, R):
+        raise ShapeError(f"b {tuple(b.shape)} / c {tuple(c.shape)} do not match x {tuple(x.shape)}")
+    disc = Discretization(inputs.discretization)
+    lam = inputs.lambda_
+    if disc is Discretization.LearnedTrapezoid and lam is None:
+        raise NullError("LearnedTrapezoid needs a lambda tensor")
+    if disc is not Discretization.LearnedTrapezoid:
+        lam = None
+    for name, t in (("dt", inputs.dt), ("lambda", lam)):
+        if t is not None and tuple(t.shape) != (B, T, H):
+            raise ShapeError(f"{name} has shape {tuple(t.shape)}, expected {(B, T, H)}")
+    if tuple(inputs.a_log.shape) != (H,):
+        raise ShapeError(f"a_log has shape {tuple(inputs.a_log.shape)}, expected {(H,)}")
+    theta = inputs.theta
+    if theta is not None:
+        if N % 2:                                        # scan.rs:485-489
+            raise ConfigError("rotational dynamics require an even d_state")
+        if tuple(theta.shape) != (B, T, H, N // 2):
+            raise ShapeError(f"theta has shape {tuple(theta.shape)}, expected {(B, T, H, N // 2)}")
+    if inputs.d_skip is not None and tuple(inputs.d_skip.shape) != (H,):
+        raise ShapeError(f"d_skip has shape {tuple(inputs.d_skip.shape)}, expected {(H,)}")
+    st = inputs.state
+    if st is not None:
+        for name, t in (("h", st.h), ("last_u", st.last_u)):
+            if tuple(t.shape) != (B, H, P, N):
+                raise ShapeError(f"state.{name} has shape {tuple(t.shape)}, expected {(B, H, P, N)}")
+        if st.angle is not None and theta is not None and tuple(st.angle.shape) != (B, H, N // 2):
+            raise ShapeError(f"state.angle has shape {tuple(st.angle.shape)}")
+
+    el = x.dtype
+    big = lambda t: None if t is None else t.to(el).contiguous()
+    f32 = lambda t: None if t is None else t.to(torch.float32).contiguous()
+    opts = {"chunk": inputs.chunk_size, "disc": int(disc), "want_state": bool(inputs.want_state),
+            "path": inputs.path}
+    outs = _FusedScan.apply(
+        opts, x.contiguous(), big(b), big(c), big(inputs.dt), f32(inputs.a_log), big(lam), big(theta),
+        f32(inputs.d_skip), f32(st.h) if st else None, f32(st.last_u) if st else None,
+        f32(st.angle) if (st and theta is not None and st.angle is not None) else None)
+    y = outs[0]
+    state = None
+    if inputs.want_state:
+        state = SsmState(outs[1], outs[2], outs[3] if theta is not None else None)
+    return ScanOutput(y, state)

@@ -1,0 +1,149 @@
+"""Pin the CPU oracle: golden vectors from the reference's own PyTorch port, the
+unrolled recurrence of the reference's test-suite, and that suite's own cases."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import m3_oracle as O
+from oracle.recurrence import Case, lcg_noise, recurrence
+
+GOLD = Path(__file__).resolve().parent / "golden"
+T64 = lambda a, g=False: torch.tensor(np.asarray(a, dtype=np.float64), requires_grad=g)
+
+
+def rel_err(a, e):
+    """|a - e| / (1 + |e|), the reference's metric (tests/ssm.rs:36-53)."""
+    a, e = np.asarray(a, dtype=np.float64), np.asarray(e, dtype=np.float64)
+    return float(np.max(np.abs(a - e) / (1.0 + np.abs(e)))) if a.size else 0.0
+
+
+def test_lcg_noise_is_the_reference_generator():
+    v = lcg_noise(4, 1)
+    # first state: s0 = seed*M + 1, then s = s*M + INC; value = (s >> 33) / 2^31 - 1
+    M, INC, MASK = 6364136223846793005, 1442695040888963407, (1 << 64) - 1
+    s = (1 * M + 1) & MASK
+    want = []
+    for _ in range(4):
+        s = (s * M + INC) & MASK
+        want.append(np.float32(np.float32(s >> 33) / np.float32(2 ** 31)) - np.float32(1))
+    assert np.array_equal(v, np.array(want, dtype=np.float32))
+    assert v.min() >= -1.0 and v.max() < 1.0
+
+
+@pytest.mark.parametrize("name", ["ssd_chunked_even", "ssd_chunked_ragged", "ssd_chunked_one_chunk"])
+def test_ssd_chunked_matches_reference_port(name):
+    z = np.load(GOLD / f"{name}.npz")
+    leaves = [T64(z[k], True) for k in "xbcagw"]
+    y, state = O.ssd_chunked(*leaves, None, int(z["chunk"]), True)
+    assert rel_err(y.detach(), z["y"]) < 1e-12
+    grads = torch.autograd.grad((y * T64(z["dy"])).sum(), leaves)
+    for k, gr in zip("xbcagw", grads):
+        assert rel_err(gr, z[f"d{k}"]) < 1e-11, k
+    assert state.shape == (z["x"].shape[0], z["x"].shape[2], z["x"].shape[3], z["b"].shape[3])
+
+
+def test_rotation_matches_reference_port():
+    z = np.load(GOLD / "rotate_halves.npz")
+    v, phi = T64(z["v"], True), T64(z["phi"], True)
+    out = O.rotate_by_angle(v, phi)
+    assert rel_err(out.detach(), z["out"]) < 1e-13
+    dv, dphi = torch.autograd.grad((out * T64(z["go"])).sum(), [v, phi])
+    assert rel_err(dv, z["dv"]) < 1e-13 and rel_err(dphi, z["dphi"]) < 1e-13
+
+
+def test_full_scan_matches_reference_mixer_tail():
+    z = np.load(GOLD / "mixer_tail.npz")
+    names = ["x", "b", "c", "dt", "lam", "a_log", "theta", "d_skip"]
+    t = {n: T64(z[n], True) for n in names}
+    y, _ = O.mamba3_scan(t["x"].unsqueeze(-1), t["b"].unsqueeze(-1), t["c"].unsqueeze(-1), t["dt"], t["a_log"],
+                         t["lam"], t["theta"], t["d_skip"], None, int(z["chunk"]), True)
+    y = y.squeeze(-1)
+    assert rel_err(y.detach(), z["y"]) < 1e-12
+    grads = torch.autograd.grad((y * T64(z["dy"])).sum(), [t[n] for n in names])
+    for n, gr in zip(names, grads):
+        assert rel_err(gr, z[f"d_{n}"]) < 1e-10, n
+
+
+def _case_weights(case):
+    dt, lam = T64(case.dt), T64(case.lam)
+    a = dt * T64(case.a_head).view(1, 1, -1)
+    g, w = O.trapezoid_weights(lam, dt)
+    return a, g, w
+
+
+@pytest.mark.parametrize("chunk", [1, 2, 3, 4, 8, 16])
+def test_chunked_scan_matches_the_recurrence(chunk):
+    """tests/ssm.rs:187-205."""
+    case = Case(2, 12, 3, 4, 6)
+    a, g, w = _case_weights(case)
+    y, st = O.ssd_chunked(T64(case.x), T64(case.b), T64(case.c), a, g, w, None, chunk, True)
+    wy, wh, _, _ = recurrence(case.x[..., None], case.b[..., None], case.c[..., None], case.dt, case.a_log, case.lam)
+    assert rel_err(y, wy[..., 0]) < 2e-4 and rel_err(st, wh) < 2e-4
+    assert rel_err(y, wy[..., 0]) < 1e-6  # float64 oracle: far inside the reference's bound
+
+
+@pytest.mark.parametrize("seq", [1, 5, 7, 13])
+def test_chunked_scan_handles_ragged_lengths(seq):
+    """tests/ssm.rs:207-220."""
+    case = Case(1, seq, 2, 3, 4)
+    a, g, w = _case_weights(case)
+    y, st = O.ssd_chunked(T64(case.x), T64(case.b), T64(case.c), a, g, w, None, 4, True)
+    wy, wh, _, _ = recurrence(case.x[..., None], case.b[..., None], case.c[..., None], case.dt, case.a_log, case.lam)
+    assert rel_err(y, wy[..., 0]) < 1e-6 and rel_err(st, wh) < 1e-6
+
+
+def test_euler_mode_reproduces_mamba2():
+    """tests/ssm.rs:222-236."""
+    case = Case(1, 8, 2, 3, 4)
+    case.lam = np.ones_like(case.lam)
+    a, g, w = _case_weights(case)
+    assert rel_err(w, g) < 1e-6
+    y, st = O.ssd_chunked(T64(case.x), T64(case.b), T64(case.c), a, g, w, None, 4, False)
+    assert st is None
+    wy, _, _, _ = recurrence(case.x[..., None], case.b[..., None], case.c[..., None], case.dt, case.a_log, case.lam)
+    assert rel_err(y, wy[..., 0]) < 1e-6
+
+
+@pytest.mark.parametrize("rank", [1, 2, 3])
+def test_full_scan_matches_extended_recurrence(rank):
+    """Rotation + MIMO + skip + carried state against the token-by-token recurrence."""
+    rng = np.random.default_rng(rank)
+    B, T, H, P, N = 2, 11, 2, 3, 4
+    x = rng.standard_normal((B, T, H, P, rank))
+    b = rng.standard_normal((B, T, H, N, rank))
+    c = rng.standard_normal((B, T, H, N, rank))
+    dt = rng.uniform(0.05, 0.5, (B, T, H))
+    lam = rng.uniform(0, 1, (B, T, H))
+    a_log = rng.uniform(0, 1, H)
+    theta = rng.uniform(0, 3, (B, T, H, N // 2))
+    d_skip = rng.standard_normal(H)
+    h0, lu0 = rng.standard_normal((B, H, P, N)), rng.standard_normal((B, H, P, N))
+    ang0 = rng.uniform(-3, 3, (B, H, N // 2))
+    st = O.OracleState(T64(h0), T64(lu0), T64(ang0))
+    y, out = O.mamba3_scan(T64(x), T64(b), T64(c), T64(dt), T64(a_log), T64(lam), T64(theta), T64(d_skip), st, 4, True)
+    wy, wh, wu, wa = recurrence(x, b, c, dt, a_log, lam, theta, d_skip, h0, lu0, ang0)
+    assert rel_err(y, wy) < 1e-9 and rel_err(out.h, wh) < 1e-9 and rel_err(out.last_u, wu) < 1e-9
+    assert rel_err(np.sin(out.angle.numpy()), np.sin(wa)) < 1e-9
+
+
+def test_split_windows_match_a_single_pass():
+    """tests/ssm.rs:238-310."""
+    case = Case(2, 12, 2, 3, 4)
+    th = case.theta()
+    ex = lambda v: T64(v).unsqueeze(-1)
+    args = lambda s: (ex(case.x[:, s]), ex(case.b[:, s]), ex(case.c[:, s]), T64(case.dt[:, s]), T64(case.a_log),
+                      T64(case.lam[:, s]), T64(th[:, s]))
+    full, fst = O.mamba3_scan(*args(slice(None)), None, None, 4, True)
+    y1, s1 = O.mamba3_scan(*args(slice(0, 5)), None, None, 4, True)
+    y2, s2 = O.mamba3_scan(*args(slice(5, 12)), None, s1, 4, True)
+    assert rel_err(torch.cat([y1, y2], 1), full) < 1e-9 and rel_err(s2.h, fst.h) < 1e-9
+
+
+def test_odd_state_with_rotation_is_a_config_error():
+    case = Case(1, 4, 1, 2, 3)
+    ex = lambda v: T64(v).unsqueeze(-1)
+    with pytest.raises(ValueError):
+        O.mamba3_scan(ex(case.x), ex(case.b), ex(case.c), T64(case.dt), T64(case.a_log), T64(case.lam),
+                      T64(np.zeros((1, 4, 1, 1))))
