@@ -1,0 +1,262 @@
+"""Benchmark of the fused Mamba-3 SSD scan: forward + backward Mtokens/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config I] [--impl ours|reference]
+
+A step is one forward and one backward pass of the scan over one batch of synthetic
+inputs (mamba_trainer_b200.synthetic).  Every rank runs the same per-GPU workload on
+its own shard (weak scaling, no collective in the path).  Rank 0 prints one JSON line.
+`--impl reference` times the CPU oracle (the restated reference composition) on the
+host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from mamba_trainer_b200 import synthetic  # noqa: E402
+
+METRIC = "mamba3_ssd_scan_fwd_bwd_throughput"
+UNIT = "Mtokens/s"
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        time.sleep(0.06)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            f = [v.strip() for v in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons)}
+
+
+def cpu_oracle_throughput(w, budget_s: float = 20.0):
+    """Time the CPU oracle (fp32, forward + backward) on a bounded slice of the workload:
+    one batch row and as many heads as finish in the budget; the scan is independent
+    across batch and heads, so throughput in token-heads/s carries over."""
+    from oracle import m3_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    heads = min(w.heads, 2)
+    seq = min(w.seq, 2048)
+    sw = w.scaled(batch=1, heads=heads, seq=seq)
+    t = synthetic.make_inputs(sw, seed=0)
+    names = [n for n in ("x", "b", "c", "dt", "a_log", "lam", "theta", "d_skip") if t.get(n) is not None]
+    best, reps, t_start = None, 0, time.perf_counter()
+    while reps < 4 and (reps < 2 or time.perf_counter() - t_start < budget_s):
+        leaf = {n: t[n].float().requires_grad_(True) for n in names}
+        t0 = time.perf_counter()
+        y, _ = O.mamba3_scan(leaf["x"], leaf["b"], leaf["c"], leaf["dt"], leaf["a_log"], leaf["lam"],
+                             leaf.get("theta"), leaf.get("d_skip"), None, sw.chunk, False)
+        torch.autograd.grad((y * t["dy"].float()).sum(), [leaf[n] for n in names])
+        dt_ = time.perf_counter() - t0
+        if reps > 0:
+            best = dt_ if best is None else min(best, dt_)
+        reps += 1
+    tok_heads_per_s = sw.tokens * sw.heads / best
+    value = tok_heads_per_s / w.heads / 1e6   # Mtokens/s of the full-head workload
+    sample = f"batch 1 x seq {seq} x {heads} of {w.heads} heads, fp32, best of {reps - 1} after 1 warm-up, scaled by heads"
+    return value, cores, sample
+
+
+def run_reference(args, w, rank):
+    if rank != 0:
+        return
+    steps = max(1, args.steps)
+    value, cores, sample = cpu_oracle_throughput(w, budget_s=min(60.0, 6.0 * steps))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": w.tokens / (value * 1e6) * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": w.name},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", type=int, default=1)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--path", type=int, default=0, help="0 auto, 1 generic, 2 tensor-core")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    w = synthetic.WORKLOADS[args.config]
+    if args.config == 4:
+        # The scaling sweep shards its 64 sequences over 8 GPUs: 8 per GPU is one shard.
+        w = w.scaled(batch=8)
+    if args.impl == "reference":
+        run_reference(args, w, rank)
+        return
+
+    from mamba_trainer_b200.ssm import Context, ScanInputs, mamba3_scan
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_
+        dist = dist_
+        dist.init_process_group("nccl", device_id=dev)
+
+    t = synthetic.make_inputs(w, seed=rank, device=dev)
+    for n in ("x", "b", "c", "dt", "a_log", "lam", "theta", "d_skip"):
+        if t.get(n) is not None:
+            t[n].requires_grad_(True)
+    names = [n for n in ("x", "b", "c", "dt", "a_log", "lam", "theta", "d_skip") if t.get(n) is not None]
+    if not w.discretization.needs_lambda_projection():
+        names.remove("lam")   # a constant lambda is not an input of the op
+
+    def step(src):
+        inp = ScanInputs.new(src["x"], src["b"], src["c"], src["dt"], src["a_log"], src.get("lam"))
+        inp = inp.with_chunk_size(w.chunk).with_state_output(False).with_discretization(w.discretization)
+        inp = inp.with_path(args.path)
+        if src.get("theta") is not None:
+            inp = inp.with_theta(src["theta"])
+        inp = inp.with_skip(src["d_skip"])
+        out = mamba3_scan(inp)
+        grads = torch.autograd.grad(out.y, [src[n] for n in names if src[n].requires_grad], grad_outputs=src["dy"])
+        return out.y, grads
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step(t)
+    barrier()
+    ctx = Context.for_device(dev)
+    launches0 = ctx.launch_count()
+    sampler = ClockSampler(local) if rank == 0 else None
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step(t)
+    ev1.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    launches = ctx.launch_count() - launches0
+    ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms)
+    ms_step = ms_total / args.steps
+    value = world * w.tokens / (ms_step * 1e-3) / 1e6
+
+    # End to end: every step copies its inputs (and dy) from pinned host memory, runs
+    # forward + backward, and reads y and every input gradient back to pinned host memory.
+    big = [n for n in ("x", "b", "c", "dt", "lam", "theta", "dy") if t.get(n) is not None]
+    host = {n: t[n].detach().cpu().pin_memory() for n in big}
+    devbuf = {n: torch.empty_like(t[n].detach()) for n in big}
+    y0, g0 = step(t)
+    host_out = [torch.empty(v.shape, dtype=v.dtype).pin_memory() for v in (y0, *g0)]
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    d2h = sum(v.numel() * v.element_size() for v in host_out)
+
+    def e2e_step():
+        src = dict(t)
+        for n in big:
+            devbuf[n].copy_(host[n], non_blocking=True)
+            src[n] = devbuf[n].detach().requires_grad_(n != "dy")
+        y, grads = step(src)
+        for dst, v in zip(host_out, (y, *grads)):
+            dst.copy_(v, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e_steps = max(3, min(args.steps, 10))
+    ev0.record()
+    for _ in range(e_steps):
+        e2e_step()
+    ev1.record()
+    barrier()
+    ems = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if dist is not None:
+        dist.all_reduce(ems, op=dist.ReduceOp.MAX)
+    e2e_value = world * w.tokens / (float(ems) / e_steps * 1e-3) / 1e6
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        alg_bytes = w.bytes_per_token_head() * w.tokens * w.heads
+        achieved = alg_bytes / (ms_step * 1e-3) / 1e9
+        flops = w.flops_per_token_head() * w.tokens * w.heads
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16" if w.dtype == torch.bfloat16 else "f32", "data": "synthetic",
+            "config": {"workload": w.name, "batch_per_gpu": w.batch, "seq_len": w.seq, "heads": w.heads,
+                       "head_dim": w.head_dim, "d_state": w.d_state, "rank": w.rank, "chunk": w.chunk,
+                       "l2": "inputs larger than L2", "sharding": f"batch x heads, {world} shard(s), no collective"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": peak_kind, "kernel": "whole fused op (forward + backward)",
+                         "frac_of_8TBs": achieved / 8000.0, "tflops": flops / (ms_step * 1e-3) / 1e12},
+            "clocks": clocks, "gpu_launches": int(launches),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        }
+        if not args.no_cpu_baseline and world == 1:
+            v, cores, sample = cpu_oracle_throughput(w)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -286,6 +286,12 @@ def mamba3_scan(inputs: ScanInputs) -> ScanOutput:
         if st.angle is not None and theta is not None and tuple(st.angle.shape) != (B, H, N // 2):
             raise ShapeError(f"state.angle has shape {tuple(st.angle.shape)}")
 
+    if T == 0:                                           # scan.rs:134-144: nothing to scan
+        state = None
+        if inputs.want_state:
+            state = st.clone() if st is not None else SsmState.zeros(B, H, P, N, theta is not None, x.device)
+        return ScanOutput(x, state)
+
     el = x.dtype
     big = lambda t: None if t is None else t.to(el).contiguous()
     f32 = lambda t: None if t is None else t.to(torch.float32).contiguous()

@@ -1,0 +1,242 @@
+"""Parity of the fused CUDA scan with the oracle, through the host API and the C ABI.
+
+Tolerances (written here, as the contract asks):
+  float32 inputs:  |a - e| <= 1e-5 * scale + 1e-4 |e|, scale = max(1, max|e|) of the tensor
+  bfloat16 inputs: ||a - e|| / ||e|| <= 2e-2 per tensor, and the reference's own
+                   measure max |a - e| / (1 + |e|) <= 2e-2 * max(1, max|e|)
+The expected values come from the float64 oracle fed the same (rounded) inputs, so a
+correct kernel is never blamed for the float32 oracle's own rounding.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from mamba_trainer_b200 import synthetic
+from mamba_trainer_b200.error import ConfigError, RankError, ShapeError
+from mamba_trainer_b200.ssm import Discretization, ScanInputs, SsmState, mamba3_scan
+from oracle.recurrence import Case, recurrence
+from tests._util import (allclose_excess, angle_close, fused_run, norm_rel, oracle_run, ref_metric)
+
+pytestmark = pytest.mark.gpu
+
+
+def check_f32(name, a, e):
+    scale = max(1.0, float(e.abs().max())) if e.numel() else 1.0
+    ex = allclose_excess(a, e, 1e-4, 1e-5 * scale)
+    assert ex <= 1.0, f"{name}: {ex:.2f}x over the float32 tolerance"
+
+
+def check_bf16(name, a, e):
+    scale = max(1.0, float(e.abs().max())) if e.numel() else 1.0
+    nr, rm = norm_rel(a.float(), e), ref_metric(a.float(), e)
+    assert nr <= 2e-2, f"{name}: norm-relative error {nr:.3e}"
+    assert rm <= 2e-2 * scale, f"{name}: reference metric {rm:.3e} (scale {scale:.2f})"
+
+
+def compare_all(t, chunk, check, want_state=True, dstate=None, discretization=None, path=0):
+    y, st, g = fused_run(t, chunk, want_state, True, dstate, discretization, path)
+    ey, est, eg = oracle_run(t, chunk, want_state, torch.float64, True, dstate)
+    check("y", y, ey)
+    if want_state:
+        check("h", st.h, est.h.detach())
+        check("last_u", st.last_u, est.last_u.detach())
+        if est.angle is not None:
+            assert angle_close(st.angle, est.angle.detach(), 2e-3), "angle"
+    else:
+        assert st is None
+    for n, e in eg.items():
+        if n == "lam" and discretization is not None and int(discretization) != 2:
+            continue
+        assert n in g, f"missing gradient {n}"
+        check("d" + n, g[n], e)
+
+
+def case_tensors(case, rank1=True, theta=False, d_skip=None):
+    f = lambda v: torch.tensor(v, dtype=torch.float32)
+    t = {"x": f(case.x).unsqueeze(-1), "b": f(case.b).unsqueeze(-1), "c": f(case.c).unsqueeze(-1),
+         "dt": f(case.dt), "lam": f(case.lam), "a_log": f(case.a_log)}
+    if theta:
+        t["theta"] = f(case.theta())
+    if d_skip is not None:
+        t["d_skip"] = f(np.asarray(d_skip, dtype=np.float32))
+    t["dy"] = torch.randn(t["x"].shape, generator=torch.Generator().manual_seed(3))
+    return t
+
+
+def np_rec(t):
+    g = lambda k: None if t.get(k) is None else t[k].double().numpy()
+    return recurrence(g("x"), g("b"), g("c"), g("dt"), g("a_log"), g("lam"), g("theta"), g("d_skip"),
+                      g("h0"), g("last_u0"), g("angle0"))
+
+
+# ---- the reference's own scan tests, replayed against the fused op ----------------
+
+@pytest.mark.parametrize("chunk", [1, 2, 3, 4, 8, 16])
+def test_chunked_scan_matches_the_recurrence(chunk):
+    """tests/ssm.rs:187-205, eps 2e-4."""
+    t = case_tensors(Case(2, 12, 3, 4, 6))
+    y, st, _ = fused_run(t, chunk, True, False)
+    wy, wh, wu, _ = np_rec(t)
+    assert ref_metric(y, wy) <= 2e-4 and ref_metric(st.h, wh) <= 2e-4 and ref_metric(st.last_u, wu) <= 2e-4
+
+
+@pytest.mark.parametrize("seq", [1, 5, 7, 13])
+def test_chunked_scan_handles_ragged_lengths(seq):
+    """tests/ssm.rs:207-220."""
+    t = case_tensors(Case(1, seq, 2, 3, 4))
+    y, st, _ = fused_run(t, 4, True, False)
+    wy, wh, _, _ = np_rec(t)
+    assert ref_metric(y, wy) <= 2e-4 and ref_metric(st.h, wh) <= 2e-4
+
+
+def test_euler_mode_reproduces_mamba2():
+    """tests/ssm.rs:222-236: lambda = 1, and want_state = false returns no state."""
+    case = Case(1, 8, 2, 3, 4)
+    case.lam = np.ones_like(case.lam)
+    t = case_tensors(case)
+    wy, _, _, _ = np_rec(t)
+    y, st, _ = fused_run(t, 4, False, False)
+    assert st is None and ref_metric(y, wy) <= 2e-4
+    t2 = dict(t, lam=None)  # the constant-lambda fast path must agree with lambda == 1
+    y2, _, _ = fused_run(t2, 4, False, False, discretization=Discretization.Euler)
+    assert ref_metric(y2, wy) <= 2e-4
+
+
+def test_split_windows_match_a_single_pass():
+    """tests/ssm.rs:238-310, eps 3e-4: cut at 5 of 12, state carried across the seam."""
+    t = case_tensors(Case(2, 12, 2, 3, 4), theta=True)
+    full_y, full_st, _ = fused_run(t, 4, True, False)
+    cut = lambda s: {k: (v[:, s] if (v is not None and v.dim() >= 3) else v) for k, v in t.items()}
+    y1, s1, _ = fused_run(cut(slice(0, 5)), 4, True, False)
+    t2 = dict(cut(slice(5, 12)), h0=s1.h, last_u0=s1.last_u, angle0=s1.angle)
+    y2, s2, _ = fused_run(t2, 4, True, False)
+    assert ref_metric(torch.cat([y1, y2], 1), full_y) <= 3e-4
+    assert ref_metric(s2.h, full_st.h) <= 3e-4
+
+
+def test_step_recurrence_matches_the_chunked_scan():
+    """tests/ssm.rs:312-380: rotation + D skip, token-by-token evaluation vs the scan."""
+    t = case_tensors(Case(2, 9, 2, 3, 4), theta=True, d_skip=[0.3, -0.2])
+    y, _, _ = fused_run(t, 4, True, False)
+    wy, _, _, _ = np_rec(t)
+    assert ref_metric(y, wy) <= 3e-4
+
+
+def test_scan_is_differentiable():
+    """tests/ssm.rs:382-426: d/dx of sum(y^2) against central differences."""
+    case = Case(1, 6, 2, 3, 4)
+    t = case_tensors(case)
+    x = t["x"].cuda().requires_grad_(True)
+    dev = {k: (v.cuda() if v is not None else None) for k, v in t.items()}
+
+    def run(xv):
+        inp = ScanInputs.new(xv, dev["b"], dev["c"], dev["dt"], dev["a_log"], dev["lam"])
+        return mamba3_scan(inp.with_chunk_size(3).with_state_output(False)).y
+
+    loss = (run(x) ** 2).sum()
+    (analytic,) = torch.autograd.grad(loss, [x])
+    eps = 1e-3
+    for i in (0, 5, 17, 30):
+        plus, minus = t["x"].clone().view(-1), t["x"].clone().view(-1)
+        plus[i] += eps
+        minus[i] -= eps
+        f = lambda v: float((run(v.view_as(t["x"]).cuda()) ** 2).sum())
+        numeric = (f(plus) - f(minus)) / (2 * eps)
+        assert abs(float(analytic.view(-1)[i]) - numeric) < 2e-2 * (1 + abs(numeric))
+
+
+# ---- all inputs' gradients, every variant, small float32 shapes --------------------
+
+def small_inputs(B, T, H, P, N, R, rot, state, seed):
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s: torch.randn(*s, generator=g)
+    u = lambda *s: torch.rand(*s, generator=g)
+    t = {"x": r(B, T, H, P, R), "b": r(B, T, H, N, R), "c": r(B, T, H, N, R), "dt": u(B, T, H) * 0.5 + 0.05,
+         "lam": u(B, T, H), "a_log": u(H), "d_skip": r(H), "dy": r(B, T, H, P, R)}
+    t["theta"] = u(B, T, H, N // 2) * 3 if rot else None
+    if state:
+        t["h0"], t["last_u0"] = r(B, H, P, N), r(B, H, P, N)
+        t["angle0"] = (u(B, H, N // 2) * 2 - 1) * 3 if rot else None
+    ds = {"h": r(B, H, P, N), "last_u": r(B, H, P, N), "angle": r(B, H, N // 2) if rot else None}
+    return t, ds
+
+
+@pytest.mark.parametrize("B,T,H,P,N,R,L,rot,state", [
+    (2, 12, 2, 3, 4, 2, 4, True, True),
+    (1, 13, 2, 3, 4, 1, 4, False, False),
+    (2, 7, 1, 5, 6, 3, 16, True, False),
+    (1, 9, 2, 4, 4, 2, 3, True, True),
+    (1, 70, 2, 8, 16, 4, 32, True, True),
+    (2, 150, 3, 72, 80, 1, 64, False, True),
+    (1, 130, 2, 16, 24, 5, 64, True, False),
+])
+def test_every_gradient_matches_the_oracle_f32(B, T, H, P, N, R, L, rot, state):
+    t, ds = small_inputs(B, T, H, P, N, R, rot, state, seed=B * 100 + T)
+    compare_all(t, L, check_f32, True, ds)
+
+
+@pytest.mark.parametrize("disc", [Discretization.Euler, Discretization.Trapezoid])
+def test_fixed_lambda_modes(disc):
+    t, ds = small_inputs(2, 21, 2, 4, 6, 2, True, True, seed=5)
+    t["lam"] = torch.full_like(t["lam"], disc.fixed_lambda())
+    compare_all(t, 8, check_f32, True, ds, discretization=disc)
+
+
+def test_grad_mask_and_repeatable_backward():
+    t, _ = small_inputs(1, 20, 2, 4, 6, 2, True, False, seed=9)
+    dev = {k: (v.cuda() if v is not None else None) for k, v in t.items()}
+    dev["b"].requires_grad_(True)
+    dev["a_log"].requires_grad_(True)
+    inp = ScanInputs.new(dev["x"], dev["b"], dev["c"], dev["dt"], dev["a_log"], dev["lam"]).with_theta(dev["theta"])
+    out = mamba3_scan(inp.with_chunk_size(8))
+    loss = (out.y * dev["dy"]).sum()
+    g1 = torch.autograd.grad(loss, [dev["b"], dev["a_log"]], retain_graph=True)
+    g2 = torch.autograd.grad(loss, [dev["b"], dev["a_log"]])
+    assert torch.equal(g1[0], g2[0]) and torch.equal(g1[1], g2[1])
+    _, _, eg = oracle_run(t, 8, True)
+    check_f32("db", g1[0], eg["b"])
+    check_f32("da_log", g1[1], eg["a_log"])
+    with torch.no_grad():
+        y2 = mamba3_scan(inp).y
+    assert not y2.requires_grad
+
+
+# ---- the benchmark configurations ---------------------------------------------------
+
+def test_config0_full_size_f32():
+    w = synthetic.WORKLOADS[0]
+    t = synthetic.make_inputs(w, seed=0)
+    compare_all(t, w.chunk, check_f32, True, None)                       # lambda read as a tensor of ones
+    compare_all(t, w.chunk, check_f32, False, None, discretization=Discretization.Euler)
+
+
+@pytest.mark.parametrize("idx,batch,heads", [(1, 1, 12), (2, 1, 4), (3, 1, 2), (4, 1, 2)])
+def test_bf16_configs_reduced_batch(idx, batch, heads):
+    w = synthetic.WORKLOADS[idx].scaled(batch=batch, heads=heads, seq=min(synthetic.WORKLOADS[idx].seq, 2048))
+    t = synthetic.make_inputs(w, seed=idx)
+    compare_all(t, w.chunk, check_bf16, True, None)
+
+
+# ---- error behaviour (src/ssm/scan.rs:462, :485-489; src/error.rs) -------------------
+
+def test_errors_mirror_the_reference():
+    t, _ = small_inputs(1, 4, 1, 2, 3, 1, False, False, seed=1)
+    dev = {k: (v.cuda() if v is not None else None) for k, v in t.items()}
+    with pytest.raises(RankError):
+        mamba3_scan(ScanInputs.new(dev["x"][..., 0], dev["b"], dev["c"], dev["dt"], dev["a_log"], dev["lam"]))
+    with pytest.raises(ConfigError):
+        th = torch.zeros(1, 4, 1, 1, device="cuda")
+        mamba3_scan(ScanInputs.new(dev["x"], dev["b"], dev["c"], dev["dt"], dev["a_log"], dev["lam"]).with_theta(th))
+    with pytest.raises(ShapeError):
+        mamba3_scan(ScanInputs.new(dev["x"], dev["b"], dev["c"], dev["dt"][:, :2], dev["a_log"], dev["lam"]))
+
+
+def test_empty_sequence_passes_state_through():
+    x = torch.zeros(2, 0, 3, 4, 1, device="cuda")
+    b = torch.zeros(2, 0, 3, 6, 1, device="cuda")
+    z = torch.zeros(2, 0, 3, device="cuda")
+    st = SsmState(torch.randn(2, 3, 4, 6, device="cuda"), torch.randn(2, 3, 4, 6, device="cuda"))
+    out = mamba3_scan(ScanInputs.new(x, b, b, z, torch.zeros(3, device="cuda"), z).with_state(st))
+    assert out.y.shape == x.shape and torch.equal(out.state.h, st.h)
