@@ -7,14 +7,6 @@
 
 #include "m3_internal.h"
 
-struct m3_ctx {
-  int device = 0;
-  cudaStream_t stream = nullptr;
-  bool own_stream = false;
-  uint64_t launches = 0;
-  char err[512] = {0};
-};
-
 struct m3_saved {
   m3_scan_desc desc;
   m3::Dims dims;
@@ -24,7 +16,7 @@ struct m3_saved {
   m3::GenericWs gws;
 };
 
-namespace {
+namespace m3 {
 
 int fail(m3_ctx* ctx, int code, const char* fmt, ...) {
   if (ctx) {
@@ -39,6 +31,14 @@ int fail(m3_ctx* ctx, int code, const char* fmt, ...) {
 int cuda_fail(m3_ctx* ctx, cudaError_t e, const char* what) {
   return fail(ctx, M3_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
+
+}  // namespace m3
+
+using m3::cuda_fail;
+using m3::fail;
+using m3::make_dims;
+
+namespace m3 {
 
 #define M3_CUDA(ctx, call)                                   \
   do {                                                       \
@@ -85,7 +85,7 @@ int make_dims(m3_ctx* ctx, const m3_scan_desc& s, m3::Dims* out) {
   return M3_OK;
 }
 
-}  // namespace
+}  // namespace m3
 
 extern "C" {
 

@@ -7,7 +7,22 @@
 #include "../../include/m3scan.h"
 #include "m3_common.cuh"
 
+// A context: one device, one stream, a launch counter and the last error message.
+struct m3_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  uint64_t launches = 0;
+  char err[512] = {0};
+};
+
 namespace m3 {
+
+// Record a failure message on the context (if any) and return `code`.
+int fail(m3_ctx* ctx, int code, const char* fmt, ...);
+int cuda_fail(m3_ctx* ctx, cudaError_t e, const char* what);
+// Validate a descriptor and derive the extents the kernels use.
+int make_dims(m3_ctx* ctx, const m3_scan_desc& s, Dims* out);
 
 // Scratch of the generic family, all float, head-major (bh = b * H + h) so that the
 // rows of one chunk are contiguous.  Row rho = t * R + r.
