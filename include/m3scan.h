@@ -154,6 +154,25 @@ int m3_scan_backward(m3_ctx *ctx, const m3_saved *saved, const m3_scan_bwd_in *i
 
 int m3_saved_free(m3_ctx *ctx, m3_saved *saved);
 
+/* No counterpart in the reference.  The forward scan (inference form: no saved
+ * context) for hosts that must not allocate device memory while they run - a server
+ * that gave the whole GPU to its own arena at start-up, a latency-bound decode loop
+ * that cannot take an allocation's implicit synchronisation, any region where
+ * allocation calls are off limits.  It calls no cudaMalloc / cudaFree and no
+ * allocating library routine: the scratch m3_scan_forward would take from the
+ * stream-ordered pool is a block of M3_NOALLOC_SCRATCH_BYTES built into the library
+ * image (so every GPU that loads the library holds that much until the process
+ * exits).  Inputs and outputs are still the caller's.  Descriptors whose scratch
+ * (m3_scan_scratch_bytes(desc, 0)) exceeds the block are refused with
+ * M3_ERR_UNSUPPORTED.  The generic kernel family runs whatever desc->path says.
+ * The first call on each device looks up the block's device address (with that
+ * device current); make that first call before any stream capture.  All calls on a
+ * device share the block and it keeps the previous call's contents (nothing in it
+ * needs to start at zero): two calls whose kernels overlap on the GPU race - keep
+ * them on one stream or order them yourself. */
+#define M3_NOALLOC_SCRATCH_BYTES (16u << 20)
+int m3_scan_forward_noalloc(m3_ctx *ctx, const m3_scan_desc *desc, const m3_scan_out *out);
+
 /* Bytes of device scratch a forward with this descriptor allocates (kept until
  * m3_saved_free when `saved` is requested). */
 size_t m3_scan_scratch_bytes(const m3_scan_desc *desc, int for_backward);

@@ -20,6 +20,7 @@ PATH_AUTO, PATH_GENERIC, PATH_TENSOR = 0, 1, 2
 GRAD_X, GRAD_B, GRAD_C, GRAD_DT, GRAD_A_LOG, GRAD_LAMBDA, GRAD_THETA, GRAD_D_SKIP, \
     GRAD_H0, GRAD_LAST_U0, GRAD_ANGLE0 = (1 << i for i in range(11))
 GRAD_ALL = 0x7FF
+NOALLOC_SCRATCH_BYTES = 16 << 20   # M3_NOALLOC_SCRATCH_BYTES
 
 
 class ScanDesc(C.Structure):
@@ -59,6 +60,7 @@ SYMBOLS = {
     "m3_scan_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(ScanBwdIn), C.c_uint32, C.POINTER(ScanGrads)]),
     "m3_saved_free": (C.c_int, [C.c_void_p, C.c_void_p]),
     "m3_scan_scratch_bytes": (C.c_size_t, [C.POINTER(ScanDesc), C.c_int]),
+    "m3_scan_forward_noalloc": (C.c_int, [C.c_void_p, C.POINTER(ScanDesc), C.POINTER(ScanOut)]),
 }
 
 _lib = None
