@@ -6,6 +6,7 @@
 #include <new>
 
 #include "m3_internal.h"
+#include "m3_tc.h"
 
 struct m3_saved {
   m3_scan_desc desc;
@@ -104,6 +105,12 @@ int m3_ctx_create(int device, m3_ctx** out) {
     return M3_ERR_CUDA;
   }
   ctx->own_stream = true;
+  if (cudaMalloc(reinterpret_cast<void**>(&ctx->dev_err), sizeof(int)) != cudaSuccess ||
+      cudaMemset(ctx->dev_err, 0, sizeof(int)) != cudaSuccess) {
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return M3_ERR_CUDA;
+  }
   // Keep freed scratch in the stream-ordered pool instead of returning it to the
   // driver, so steady-state calls do not pay for allocation.
   cudaMemPool_t pool;
@@ -122,6 +129,7 @@ int m3_ctx_destroy(m3_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     cudaStreamDestroy(ctx->stream);
   }
+  if (ctx->dev_err) cudaFree(ctx->dev_err);
   delete ctx;
   return M3_OK;
 }
@@ -142,6 +150,12 @@ int m3_sync(m3_ctx* ctx) {
   if (!ctx) return M3_ERR_NULL;
   M3_CUDA(ctx, cudaSetDevice(ctx->device));
   M3_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  int flag = 0;
+  M3_CUDA(ctx, cudaMemcpy(&flag, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
+  if (flag) {
+    cudaMemset(ctx->dev_err, 0, sizeof(int));
+    return fail(ctx, M3_ERR_TIMEOUT, "a bounded device-side wait gave up; results of the affected call are invalid");
+  }
   return M3_OK;
 }
 
@@ -225,7 +239,26 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
     return M3_OK;
   }
   if (!out->y) return fail(ctx, M3_ERR_NULL, "y is required");
-  if (desc->path == M3_PATH_TENSOR) return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family does not take this shape");
+  const bool tc_ok = m3::tc_supported(*desc);
+  if (desc->path == M3_PATH_TENSOR && !tc_ok)
+    return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family does not take this shape");
+  if (tc_ok && desc->path != M3_PATH_GENERIC && !saved) {
+    m3::TcFwdParams p{};
+    p.x = static_cast<const __nv_bfloat16*>(desc->x); p.b = static_cast<const __nv_bfloat16*>(desc->b);
+    p.c = static_cast<const __nv_bfloat16*>(desc->c); p.dt = static_cast<const __nv_bfloat16*>(desc->dt);
+    p.lam = static_cast<const __nv_bfloat16*>(desc->lambda); p.theta = static_cast<const __nv_bfloat16*>(desc->theta);
+    p.a_log = desc->a_log; p.d_skip = desc->d_skip; p.h0 = desc->h0; p.lu0 = desc->last_u0; p.angle0 = desc->angle0;
+    p.y = static_cast<__nv_bfloat16*>(out->y);
+    p.h_out = desc->want_state ? out->h : nullptr;
+    p.lu_out = desc->want_state ? out->last_u : nullptr;
+    p.angle_out = (desc->want_state && d.rot) ? out->angle : nullptr;
+    p.err = ctx->dev_err;
+    p.B = d.B; p.T = d.T; p.H = d.H; p.R = d.R; p.disc = d.disc;
+    cudaError_t te = m3::tc_forward(ctx->stream, p, d.rot != 0);
+    if (te != cudaSuccess) return cuda_fail(ctx, te, "tensor-core forward");
+    ctx->launches += 1;
+    return M3_OK;
+  }
   const size_t bytes = m3::generic_ws_layout(d, nullptr, nullptr);
   char* base = nullptr;
   M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&base), bytes, ctx->stream));

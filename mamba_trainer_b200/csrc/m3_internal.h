@@ -13,6 +13,7 @@ struct m3_ctx {
   cudaStream_t stream = nullptr;
   bool own_stream = false;
   uint64_t launches = 0;
+  int* dev_err = nullptr;  // device flag raised by a kernel whose bounded wait gave up
   char err[512] = {0};
 };
 

@@ -1,0 +1,33 @@
+// Host-side interface of the tensor-core kernel family.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/m3scan.h"
+
+namespace m3 {
+
+// Shapes the family serves: bf16, head_dim 64, d_state 128, rank 1, 2 or 4.
+inline bool tc_supported(const m3_scan_desc& s) {
+  return s.dtype == M3_BF16 && s.head_dim == 64 && s.d_state == 128 && (s.rank == 1 || s.rank == 2 || s.rank == 4) &&
+         s.seq > 0;
+}
+// Time steps per 128-row tile and tiles per stripe.
+inline int tc_tile_steps(int rank) { return 128 / rank; }
+inline int tc_tiles(int seq, int rank) { return (seq + tc_tile_steps(rank) - 1) / tc_tile_steps(rank); }
+
+struct TcFwdParams {
+  const __nv_bfloat16 *x, *b, *c, *dt, *lam, *theta;
+  const float *a_log, *d_skip, *h0, *lu0, *angle0;
+  __nv_bfloat16* y;
+  float *h_out, *lu_out, *angle_out;
+  float* ckpt_h;      // [BH, tiles, 128 (n), 64 (p)] state entering each tile, or NULL
+  float* ckpt_angle;  // [BH, tiles, 64] angle entering each tile, or NULL
+  int* err;           // device flag set when a bounded wait gave up
+  int B, T, H, R, disc;
+};
+
+cudaError_t tc_forward(cudaStream_t st, const TcFwdParams& p, bool rotational);
+
+}  // namespace m3

@@ -240,3 +240,30 @@ def test_empty_sequence_passes_state_through():
     st = SsmState(torch.randn(2, 3, 4, 6, device="cuda"), torch.randn(2, 3, 4, 6, device="cuda"))
     out = mamba3_scan(ScanInputs.new(x, b, b, z, torch.zeros(3, device="cuda"), z).with_state(st))
     assert out.y.shape == x.shape and torch.equal(out.state.h, st.h)
+
+
+# ---- tensor-core family (tcgen05 / TMEM), explicit path = 2 --------------------------------
+
+def tc_workload(rank, rot, seq, batch=2, heads=2, disc=Discretization.LearnedTrapezoid, bc="scaled"):
+    return synthetic.Workload("tc_case", batch, seq, heads, 64, 128, 64, rank, torch.bfloat16, disc, rot, bc)
+
+
+@pytest.mark.parametrize("rank,rot,seq,state,disc", [
+    (1, False, 300, True, Discretization.LearnedTrapezoid),
+    (1, True, 256, False, Discretization.LearnedTrapezoid),
+    (1, False, 128, False, Discretization.Euler),
+    (2, True, 200, True, Discretization.LearnedTrapezoid),
+    (4, True, 130, True, Discretization.Trapezoid),
+    (4, False, 64, False, Discretization.LearnedTrapezoid),
+    (1, True, 1, True, Discretization.LearnedTrapezoid),
+])
+def test_tensor_core_forward(rank, rot, seq, state, disc):
+    w = tc_workload(rank, rot, seq, disc=disc, bc="rms" if rank == 1 else "scaled")
+    t = synthetic.make_inputs(w, seed=rank * 10 + seq, with_state=state)
+    y, st, _ = fused_run(t, w.chunk, True, False, None, disc, path=2)
+    ey, est, _ = oracle_run(t, w.chunk, True, torch.float64, False)
+    check_bf16("y", y, ey)
+    check_bf16("h", st.h, est.h)
+    check_bf16("last_u", st.last_u, est.last_u)
+    if rot:
+        assert angle_close(st.angle, est.angle, 2e-2), "angle"
