@@ -15,6 +15,8 @@ struct m3_saved {
   char* ws_base = nullptr;
   size_t ws_bytes = 0;
   m3::GenericWs gws;
+  float* tc_ckpt_h = nullptr;      // tensor-core family: state entering each tile
+  float* tc_ckpt_angle = nullptr;  // and the angle entering each tile
 };
 
 namespace m3 {
@@ -87,6 +89,61 @@ int make_dims(m3_ctx* ctx, const m3_scan_desc& s, m3::Dims* out) {
 }
 
 }  // namespace m3
+
+namespace {
+
+// Backward of a forward that ran the tensor-core family: one stripe kernel, then the shared
+// per-token / per-head finalisation.
+int tc_backward_call(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* in, uint32_t mask,
+                     const m3_scan_grads* g) {
+  const m3_scan_desc& desc = saved->desc;
+  m3::Dims d = saved->dims;
+  const int steps = m3::tc_tile_steps(d.R), tiles = m3::tc_tiles(d.T, d.R);
+  d.L = steps; d.C = tiles; d.Tp = tiles * steps; d.LR = 128;
+  const size_t BH = (size_t)d.B * d.H;
+  const size_t per_tok = BH * d.Tp, per_tile = BH * tiles;
+  const size_t nfloat = 4 * per_tok + 2 * per_tile + BH;
+  float* base = nullptr;
+  M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&base), nfloat * sizeof(float), ctx->stream));
+  m3::GenericBwdWs bw{};
+  bw.da = base; bw.dg = base + per_tok; bw.dw = base + 2 * per_tok; bw.ddt_rot = base + 3 * per_tok;
+  bw.partA = base + 4 * per_tok; bw.partD = bw.partA + per_tile; bw.ip0 = bw.partD + per_tile;
+  auto want = [&](uint32_t bit, const void* p) { return (mask & bit) && p; };
+  using bf16 = __nv_bfloat16;
+  m3::TcBwdParams p{};
+  p.x = static_cast<const bf16*>(desc.x); p.b = static_cast<const bf16*>(desc.b); p.c = static_cast<const bf16*>(desc.c);
+  p.dt = static_cast<const bf16*>(desc.dt); p.lam = static_cast<const bf16*>(desc.lambda);
+  p.theta = static_cast<const bf16*>(desc.theta); p.dy = static_cast<const bf16*>(in->dy);
+  p.a_log = desc.a_log; p.d_skip = desc.d_skip; p.h0 = desc.h0; p.lu0 = desc.last_u0;
+  p.dh = in->dh; p.dlu = in->dlast_u; p.dangle = d.rot ? in->dangle : nullptr;
+  p.ckpt_h = saved->tc_ckpt_h; p.ckpt_angle = saved->tc_ckpt_angle;
+  p.dx = want(M3_GRAD_X, g->dx) ? static_cast<bf16*>(g->dx) : nullptr;
+  p.db = want(M3_GRAD_B, g->db) ? static_cast<bf16*>(g->db) : nullptr;
+  p.dc = want(M3_GRAD_C, g->dc) ? static_cast<bf16*>(g->dc) : nullptr;
+  p.dtheta = (want(M3_GRAD_THETA, g->dtheta) && d.rot) ? static_cast<bf16*>(g->dtheta) : nullptr;
+  p.da = bw.da; p.dg = bw.dg; p.dw = bw.dw; p.ddt_rot = bw.ddt_rot; p.partA = bw.partA; p.partD = bw.partD; p.ip0 = bw.ip0;
+  const bool has_state = desc.h0 != nullptr;
+  p.dh0 = (has_state && want(M3_GRAD_H0, g->dh0)) ? g->dh0 : nullptr;
+  p.dlu0 = (has_state && want(M3_GRAD_LAST_U0, g->dlast_u0)) ? g->dlast_u0 : nullptr;
+  p.dangle0 = (d.rot && desc.angle0 && want(M3_GRAD_ANGLE0, g->dangle0)) ? g->dangle0 : nullptr;
+  p.err = ctx->dev_err;
+  p.B = d.B; p.T = d.T; p.H = d.H; p.R = d.R; p.disc = d.disc;
+  cudaError_t e = m3::tc_backward(ctx->stream, p, d.rot != 0);
+  if (e == cudaSuccess) {
+    ctx->launches += 1;
+    void* ddt = want(M3_GRAD_DT, g->ddt) ? g->ddt : nullptr;
+    void* dlam = (want(M3_GRAD_LAMBDA, g->dlambda) && d.disc == M3_LEARNED_TRAPEZOID) ? g->dlambda : nullptr;
+    float* dalog = want(M3_GRAD_A_LOG, g->da_log) ? g->da_log : nullptr;
+    float* ddsk = (want(M3_GRAD_D_SKIP, g->dd_skip) && desc.d_skip) ? g->dd_skip : nullptr;
+    e = m3::finalize_scalars(ctx->stream, d, desc, bw, ddt, dlam, dalog, ddsk, &ctx->launches);
+  }
+  cudaError_t e2 = cudaFreeAsync(base, ctx->stream);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "tensor-core backward");
+  if (e2 != cudaSuccess) return cuda_fail(ctx, e2, "cudaFreeAsync");
+  return M3_OK;
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -242,7 +299,7 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
   const bool tc_ok = m3::tc_supported(*desc);
   if (desc->path == M3_PATH_TENSOR && !tc_ok)
     return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family does not take this shape");
-  if (tc_ok && desc->path != M3_PATH_GENERIC && !saved) {
+  if (tc_ok && desc->path != M3_PATH_GENERIC) {
     m3::TcFwdParams p{};
     p.x = static_cast<const __nv_bfloat16*>(desc->x); p.b = static_cast<const __nv_bfloat16*>(desc->b);
     p.c = static_cast<const __nv_bfloat16*>(desc->c); p.dt = static_cast<const __nv_bfloat16*>(desc->dt);
@@ -254,9 +311,37 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
     p.angle_out = (desc->want_state && d.rot) ? out->angle : nullptr;
     p.err = ctx->dev_err;
     p.B = d.B; p.T = d.T; p.H = d.H; p.R = d.R; p.disc = d.disc;
+    char* base = nullptr;
+    size_t bytes = 0;
+    if (saved) {  // the backward pass needs the state and the angle entering every tile
+      const size_t tiles = (size_t)m3::tc_tiles(d.T, d.R);
+      const size_t nh = BH * tiles * 128 * 64, na = BH * tiles * 64;
+      bytes = (nh + na) * sizeof(float);
+      M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&base), bytes, ctx->stream));
+      p.ckpt_h = reinterpret_cast<float*>(base);
+      p.ckpt_angle = p.ckpt_h + nh;
+    }
     cudaError_t te = m3::tc_forward(ctx->stream, p, d.rot != 0);
-    if (te != cudaSuccess) return cuda_fail(ctx, te, "tensor-core forward");
+    if (te != cudaSuccess) {
+      if (base) cudaFreeAsync(base, ctx->stream);
+      return cuda_fail(ctx, te, "tensor-core forward");
+    }
     ctx->launches += 1;
+    if (saved) {
+      m3_saved* sv = new (std::nothrow) m3_saved();
+      if (!sv) {
+        cudaFreeAsync(base, ctx->stream);
+        return fail(ctx, M3_ERR_CUDA, "out of host memory");
+      }
+      sv->desc = *desc;
+      sv->dims = d;
+      sv->path = M3_PATH_TENSOR;
+      sv->ws_base = base;
+      sv->ws_bytes = bytes;
+      sv->tc_ckpt_h = p.ckpt_h;
+      sv->tc_ckpt_angle = p.ckpt_angle;
+      *saved = sv;
+    }
     return M3_OK;
   }
   const size_t bytes = m3::generic_ws_layout(d, nullptr, nullptr);
@@ -294,6 +379,7 @@ int m3_scan_backward(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* i
   if (!saved || !in || !grads) return fail(ctx, M3_ERR_NULL, "saved context, upstream gradients and outputs are required");
   if (!in->dy) return fail(ctx, M3_ERR_NULL, "dy is required");
   M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (saved->path == M3_PATH_TENSOR) return tc_backward_call(ctx, saved, in, grad_mask, grads);
   const m3::Dims& d = saved->dims;
   const size_t bytes = m3::generic_bwd_ws_layout(d, nullptr, nullptr);
   char* base = nullptr;

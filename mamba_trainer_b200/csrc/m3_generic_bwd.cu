@@ -109,6 +109,31 @@ static cudaError_t backward_t(cudaStream_t st, const Dims& d, const m3_scan_desc
   return cudaGetLastError();
 }
 
+// The last two launches of any backward: per-token d dt / d lambda from (da, dg, dw, the
+// rotation term, the seed-state term) and the per-head reductions.  `d.Tp` and `d.C` give the
+// pitch of the per-token arrays and the number of partial sums per (batch, head).
+cudaError_t finalize_scalars(cudaStream_t st, const Dims& d, const m3_scan_desc& desc, const GenericBwdWs& bw,
+                             void* ddt, void* dlam, float* dalog, float* ddsk, uint64_t* launches) {
+  const size_t total = (size_t)d.B * d.T * d.H;
+  const unsigned grid = (unsigned)((total + 255) / 256);
+  const int has_state = desc.h0 ? 1 : 0;
+  if (desc.dtype == M3_BF16) {
+    using T = __nv_bfloat16;
+    kb_final<T><<<grid, 256, 0, st>>>(d, static_cast<const T*>(desc.dt), static_cast<const T*>(desc.lambda), desc.a_log,
+                                      bw, has_state, static_cast<T*>(ddt), static_cast<T*>(dlam));
+  } else {
+    kb_final<float><<<grid, 256, 0, st>>>(d, static_cast<const float*>(desc.dt), static_cast<const float*>(desc.lambda),
+                                          desc.a_log, bw, has_state, static_cast<float*>(ddt), static_cast<float*>(dlam));
+  }
+  uint64_t n = 1;
+  if (dalog || ddsk) {
+    kb_reduce_heads<<<d.H, 256, 0, st>>>(d, desc.a_log, bw, dalog, ddsk);
+    n += 1;
+  }
+  if (launches) *launches += n;
+  return cudaGetLastError();
+}
+
 cudaError_t generic_backward(cudaStream_t st, const Dims& d, const m3_scan_desc& desc, const GenericWs& ws,
                              const GenericBwdWs& bw, const m3_scan_bwd_in& in, uint32_t mask,
                              const m3_scan_grads& grads, uint64_t* launches) {

@@ -71,4 +71,7 @@ cudaError_t generic_backward(cudaStream_t st, const Dims& d, const m3_scan_desc&
                              const m3_scan_bwd_in& in, uint32_t mask,
                              const m3_scan_grads& grads, uint64_t* launches);
 
+cudaError_t finalize_scalars(cudaStream_t st, const Dims& d, const m3_scan_desc& desc, const GenericBwdWs& bw,
+                             void* ddt, void* dlam, float* dalog, float* ddsk, uint64_t* launches);
+
 }  // namespace m3

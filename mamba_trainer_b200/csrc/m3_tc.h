@@ -30,4 +30,20 @@ struct TcFwdParams {
 
 cudaError_t tc_forward(cudaStream_t st, const TcFwdParams& p, bool rotational);
 
+struct TcBwdParams {
+  const __nv_bfloat16 *x, *b, *c, *dt, *lam, *theta, *dy;
+  const float *a_log, *d_skip, *h0, *lu0;
+  const float *dh, *dlu, *dangle;        // gradients reaching the returned state, or NULL
+  const float *ckpt_h, *ckpt_angle;      // written by the forward pass
+  __nv_bfloat16 *dx, *db, *dc, *dtheta;  // NULL skips the store
+  float *da, *dg, *dw, *ddt_rot;         // [BH, tiles * steps] per-token scalars for the final pass
+  float *partA, *partD;                  // [BH, tiles] partial sums of d a_log / d d_skip
+  float *ip0;                            // [BH] <dH_0, last_u0>
+  float *dh0, *dlu0, *dangle0;           // NULL skips the store
+  int* err;
+  int B, T, H, R, disc;
+};
+
+cudaError_t tc_backward(cudaStream_t st, const TcBwdParams& p, bool rotational);
+
 }  // namespace m3

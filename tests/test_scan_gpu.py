@@ -267,3 +267,22 @@ def test_tensor_core_forward(rank, rot, seq, state, disc):
     check_bf16("last_u", st.last_u, est.last_u)
     if rot:
         assert angle_close(st.angle, est.angle, 2e-2), "angle"
+
+
+@pytest.mark.parametrize("rank,rot,seq,state,disc", [
+    (1, False, 300, True, Discretization.LearnedTrapezoid),
+    (1, True, 256, False, Discretization.LearnedTrapezoid),
+    (1, False, 128, False, Discretization.Euler),
+    (2, True, 200, True, Discretization.LearnedTrapezoid),
+    (4, True, 130, True, Discretization.Trapezoid),
+    (4, False, 64, False, Discretization.LearnedTrapezoid),
+    (1, True, 1, True, Discretization.LearnedTrapezoid),
+])
+def test_tensor_core_backward(rank, rot, seq, state, disc):
+    w = tc_workload(rank, rot, seq, disc=disc, bc="rms" if rank == 1 else "scaled")
+    t = synthetic.make_inputs(w, seed=rank * 10 + seq + 1, with_state=state)
+    g = torch.Generator().manual_seed(seq)
+    ds = {"h": torch.randn(w.batch, w.heads, 64, 128, generator=g) * 0.1,
+          "last_u": torch.randn(w.batch, w.heads, 64, 128, generator=g) * 0.1,
+          "angle": torch.randn(w.batch, w.heads, 64, generator=g) * 0.1 if rot else None}
+    compare_all(t, w.chunk, check_bf16, True, ds, discretization=disc, path=2)
