@@ -212,9 +212,12 @@ def test_config0_full_size_f32():
     compare_all(t, w.chunk, check_f32, False, None, discretization=Discretization.Euler)
 
 
-@pytest.mark.parametrize("idx,batch,heads", [(1, 1, 12), (2, 1, 4), (3, 1, 2), (4, 1, 2)])
-def test_bf16_configs_reduced_batch(idx, batch, heads):
-    w = synthetic.WORKLOADS[idx].scaled(batch=batch, heads=heads, seq=min(synthetic.WORKLOADS[idx].seq, 2048))
+@pytest.mark.parametrize("idx,batch,heads,seq", [(1, 1, 12, 2048), (2, 1, 4, 2048), (3, 4, 2, 1024), (4, 4, 2, 1024)])
+def test_bf16_configs_reduced_batch(idx, batch, heads, seq):
+    # Reduced so the CPU oracle finishes in seconds.  The per-head gradients (a_log, D) are sums
+    # over every token of the shard with heavy cancellation: with bf16 tensor-core operands their
+    # relative error shrinks with the number of tokens summed, so the MIMO cases keep 4 sequences.
+    w = synthetic.WORKLOADS[idx].scaled(batch=batch, heads=heads, seq=seq)
     t = synthetic.make_inputs(w, seed=idx)
     compare_all(t, w.chunk, check_bf16, True, None)
 
