@@ -15,7 +15,7 @@ struct m3_saved {
   char* ws_base = nullptr;
   size_t ws_bytes = 0;
   m3::GenericWs gws;
-  float* tc_ckpt_h = nullptr;      // tensor-core family: state entering each tile
+  __nv_bfloat16* tc_ckpt_h = nullptr;  // tensor-core family: bf16 state entering each tile
   float* tc_ckpt_angle = nullptr;  // and the angle entering each tile
 };
 
@@ -128,6 +128,7 @@ int tc_backward_call(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* i
   p.dangle0 = (d.rot && desc.angle0 && want(M3_GRAD_ANGLE0, g->dangle0)) ? g->dangle0 : nullptr;
   p.err = ctx->dev_err;
   p.B = d.B; p.T = d.T; p.H = d.H; p.R = d.R; p.disc = d.disc;
+  p.stagger = m3::tc_stagger_cycles(true);
   cudaError_t e = m3::tc_backward(ctx->stream, p, d.rot != 0);
   if (e == cudaSuccess) {
     ctx->launches += 1;
@@ -311,15 +312,16 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
     p.angle_out = (desc->want_state && d.rot) ? out->angle : nullptr;
     p.err = ctx->dev_err;
     p.B = d.B; p.T = d.T; p.H = d.H; p.R = d.R; p.disc = d.disc;
+    p.stagger = m3::tc_stagger_cycles(false);
     char* base = nullptr;
     size_t bytes = 0;
     if (saved) {  // the backward pass needs the state and the angle entering every tile
       const size_t tiles = (size_t)m3::tc_tiles(d.T, d.R);
       const size_t nh = BH * tiles * 128 * 64, na = BH * tiles * 64;
-      bytes = (nh + na) * sizeof(float);
+      bytes = nh * sizeof(__nv_bfloat16) + na * sizeof(float);
       M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&base), bytes, ctx->stream));
-      p.ckpt_h = reinterpret_cast<float*>(base);
-      p.ckpt_angle = p.ckpt_h + nh;
+      p.ckpt_h = reinterpret_cast<__nv_bfloat16*>(base);
+      p.ckpt_angle = reinterpret_cast<float*>(base + nh * sizeof(__nv_bfloat16));
     }
     cudaError_t te = m3::tc_forward(ctx->stream, p, d.rot != 0);
     if (te != cudaSuccess) {

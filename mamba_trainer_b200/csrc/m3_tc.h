@@ -17,15 +17,19 @@ inline bool tc_supported(const m3_scan_desc& s) {
 inline int tc_tile_steps(int rank) { return 128 / rank; }
 inline int tc_tiles(int seq, int rank) { return (seq + tc_tile_steps(rank) - 1) / tc_tile_steps(rank); }
 
+// Start delay per CTA group in cycles (M3_TC_STAGGER overrides; 0 disables).
+int tc_stagger_cycles(bool backward);
+
 struct TcFwdParams {
   const __nv_bfloat16 *x, *b, *c, *dt, *lam, *theta;
   const float *a_log, *d_skip, *h0, *lu0, *angle0;
   __nv_bfloat16* y;
   float *h_out, *lu_out, *angle_out;
-  float* ckpt_h;      // [BH, tiles, 128 (n), 64 (p)] state entering each tile, or NULL
+  __nv_bfloat16* ckpt_h;  // [BH, tiles, 64 x 128 operand tile] bf16 state entering each tile, or NULL
   float* ckpt_angle;  // [BH, tiles, 64] angle entering each tile, or NULL
   int* err;           // device flag set when a bounded wait gave up
   int B, T, H, R, disc;
+  int stagger;        // cycles of start delay per CTA group (blockIdx & 3), 0 = none
 };
 
 cudaError_t tc_forward(cudaStream_t st, const TcFwdParams& p, bool rotational);
@@ -34,7 +38,8 @@ struct TcBwdParams {
   const __nv_bfloat16 *x, *b, *c, *dt, *lam, *theta, *dy;
   const float *a_log, *d_skip, *h0, *lu0;
   const float *dh, *dlu, *dangle;        // gradients reaching the returned state, or NULL
-  const float *ckpt_h, *ckpt_angle;      // written by the forward pass
+  const __nv_bfloat16* ckpt_h;           // written by the forward pass
+  const float* ckpt_angle;
   __nv_bfloat16 *dx, *db, *dc, *dtheta;  // NULL skips the store
   float *da, *dg, *dw, *ddt_rot;         // [BH, tiles * steps] per-token scalars for the final pass
   float *partA, *partD;                  // [BH, tiles] partial sums of d a_log / d d_skip
@@ -42,6 +47,7 @@ struct TcBwdParams {
   float *dh0, *dlu0, *dangle0;           // NULL skips the store
   int* err;
   int B, T, H, R, disc;
+  int stagger;
 };
 
 cudaError_t tc_backward(cudaStream_t st, const TcBwdParams& p, bool rotational);

@@ -19,13 +19,20 @@ using namespace m3tc;
 
 namespace {
 
-constexpr uint32_t OFF_C = 0, OFF_B = 32768, OFF_X = 65536, OFF_XW = 81920, OFF_DY = 98304, OFF_DYE = 114688,
+constexpr uint32_t OFF_C = 0, OFF_B = 32768, OFF_X = 65536, OFF_DY = 81920, OFF_XW = 98304, OFF_DYE = 114688,
                    OFF_M = 131072, OFF_DG = 163840, OFF_HS = 196608, OFF_SC = 212992;
-constexpr int kScalFloats = 8 * kScal + 256 * 4 + 512 + 256 + 132 + 132 + 16 + 64 + 64 + 256;
+constexpr int kScalFloats = kNumScal * kScal + 256 * 4 + 512 + 256 + 132 + 132 + 16 + 64 + 64 + 256;
 constexpr uint32_t kSmemBytes = OFF_SC + kScalFloats * 4 + 64;
 constexpr uint32_t TM_G = 0, TM_DM = 128, TM_T1 = 256, TM_DH = 384, TM_COLS = 512;
 // phase B reuse: dB^ accumulates over G's columns, dX~ and U over dM's.
 constexpr uint32_t TM_DB = 0, TM_DX = 128, TM_U = 192;
+
+#ifdef M3_TC_TIMING
+__device__ long long g_tcb_timing[16];
+#define TICK(i) do { if (blockIdx.x == 0 && threadIdx.x == 0) { long long c_ = clock64(); g_tcb_timing[i] += c_ - tick_; tick_ = c_; } } while (0)
+#else
+#define TICK(i) do { } while (0)
+#endif
 
 template <int R, bool ROT>
 __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
@@ -37,8 +44,8 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
   float* sDphi = reinterpret_cast<float*>(smem + OFF_DG);  // alive after phase B
   float* sc = reinterpret_cast<float*>(smem + OFF_SC);
   TileScalars ts{sc, sc + kScal, sc + 2 * kScal, sc + 3 * kScal, sc + 4 * kScal, sc + 5 * kScal, sc + 6 * kScal,
-                 sc + 7 * kScal};
-  float* part_row = sc + 8 * kScal;   // [2][128]
+                 sc + 7 * kScal, sc + 8 * kScal};
+  float* part_row = sc + kNumScal * kScal;   // [2][128]
   float* part_t1 = part_row + 256;    // [2][128]
   float* part_q = part_t1 + 256;      // [2][128]
   float* part_dg = part_q + 256;      // [2][128]
@@ -87,38 +94,62 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
   }
   tmem_wait_st();
 
+  if (p.stagger > 0) {  // spread the CTAs' memory phases: a fixed, bounded delay per CTA group
+    const long long until = clock64() + (long long)(blockIdx.x & 3) * p.stagger;
+    while (clock64() < until) {}
+  }
   bool failed = false;
+  float nx_dt, nx_lam;  // dt / lambda of the next tile to process, loaded one tile ahead
+  load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, (ntiles - 1) * LT);
+#ifdef M3_TC_TIMING
+  long long tick_ = clock64();
+#endif
   for (int k = ntiles - 1, it = 0; k >= 0; --k, ++it) {
     const int t0 = k * LT;
     const size_t tok0 = ((size_t)b * T + t0) * H + h;
     const bool last_tile = (k == ntiles - 1);
     const int l_end = T - 1 - t0;  // row of the final token when last_tile
-    // ---- 1-3. scalars, angles, operands -----------------------------------------------------
-    tile_scalars<R>(ts, p.dt, p.lam, p.disc, A, b, h, H, T, t0);
+    if (k > 0)  // warm L2 with the tile after this one
+      prefetch_tile_l2<R, ROT>(p.b, p.c, p.x, p.dy, p.theta, p.ckpt_h + ((size_t)bh * ntiles + k - 1) * kN * kP,
+                               tok0 - (size_t)LT * H, H, T, t0 - LT);
+    // ---- 1. every global load of the tile in flight, then scalars and angles ---------------------
+    RawBC<R, ROT> raw_bc;
+    RawPX<R> raw_x, raw_dy;
+    RawTheta<R> raw_th;
+    uint4 raw_h[4];
+    issue_bc<R, ROT>(raw_bc, p.b, p.c, tok0, H, T, t0);
+    issue_px<R>(raw_x, p.x, tok0, H, T, t0);
+    issue_px<R>(raw_dy, p.dy, tok0, H, T, t0);
+    if (ROT) issue_theta<R>(raw_th, p.theta, tok0, H, T, t0);
+    {
+      const uint4* src = reinterpret_cast<const uint4*>(p.ckpt_h + ((size_t)bh * ntiles + k) * kN * kP);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) raw_h[i] = __ldg(src + tid + 256 * i);
+    }
+    TICK(0);
+    tile_scalars<R>(ts, nx_dt, nx_lam, A, T, t0);
+    load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, t0 - LT);
     if (ROT) {
       if (tid < kNH) s_carry[tid] = p.ckpt_angle[((size_t)bh * ntiles + k) * kNH + tid];
+      commit_theta<R>(raw_th, sPhi);
       __syncthreads();
-      tile_angles<R>(sPhi, s_q, s_carry, ts.dt, p.theta, b, h, H, T, t0, nullptr);
+      tile_angles_smem<R>(sPhi, s_q, s_carry, ts.dt, T, t0, nullptr);
     }
     __syncthreads();
-    stage_bc<R, ROT>(sB, sC, p.b, p.c, sPhi, tok0, H, T, t0);
-    stage_px<R>(sX, sXw, p.x, ts.sw, tok0, H, T, t0);
-    stage_px<R>(sDY, sDYe, p.dy, ts.eac, tok0, H, T, t0);
-    {  // H_k (state entering the tile) as a bf16 [p][n] operand
-      const float* hk = p.ckpt_h + ((size_t)bh * ntiles + k) * kN * kP;
-      for (int e = tid; e < kN * 8; e += 256) {
-        const int n = e >> 3, p0 = (e & 7) * 8;
-        const float4 a4 = *reinterpret_cast<const float4*>(hk + (size_t)n * kP + p0);
-        const float4 b4 = *reinterpret_cast<const float4*>(hk + (size_t)n * kP + p0 + 4);
-        const float v[8] = {a4.x, a4.y, a4.z, a4.w, b4.x, b4.y, b4.z, b4.w};
+    TICK(1);
+    // ---- 2-3. operands ------------------------------------------------------------------------------
+    commit_bc<R, ROT>(raw_bc, sB, sC, sPhi);
+    commit_px<R>(raw_x, sX, sXw, ts.sw);
+    commit_px<R>(raw_dy, sDY, sDYe, ts.eac);
+    {  // H_k, the bf16 state entering the tile, already in operand layout [p][n]
+      uint4* dst = reinterpret_cast<uint4*>(sHS);
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<__nv_bfloat16*>(sHS + tile_off(p0 + j, n, kN)) = __float2bfloat16_rn(v[j]);
-      }
+      for (int i = 0; i < 4; ++i) dst[tid + 256 * i] = raw_h[i];
     }
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    TICK(2);
     // ---- 4. MMA phase A ------------------------------------------------------------------------
     if (tid == 0) {
       tc_fence_after();
@@ -132,10 +163,12 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
       if (__syncthreads_or(!ok)) { failed = true; break; }
     }
     tc_fence_after();
+    TICK(3);
     // ---- 5. epilogue A -------------------------------------------------------------------------
     const float acl = ts.ac[rl];
     const float cd = ts.ac[LT - 1];
     const float ecd = expc(cd);
+    float dcd_part = 0.0f;
     {
       const int lmax = (quad * 32 + 31) / R;
       float rowE = 0.0f, dgp = 0.0f;
@@ -153,29 +186,37 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
           part_col[quad * 128 + c0 + lane] = 0.0f;
           continue;
         }
+        float gq[2][16], dmq[2][16];
 #pragma unroll
         for (int hb = 0; hb < 2; ++hb) {
-          float g[16], dm[16], mv[16], dgv[16];
-          tmem_ld16(tmem_addr(tm, quad * 32, TM_G + c0 + 16 * hb), g);
-          tmem_ld16(tmem_addr(tm, quad * 32, TM_DM + c0 + 16 * hb), dm);
+          tmem_ld16_issue(tmem_addr(tm, quad * 32, TM_G + c0 + 16 * hb), gq[hb]);
+          tmem_ld16_issue(tmem_addr(tm, quad * 32, TM_DM + c0 + 16 * hb), dmq[hb]);
+        }
+        tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int s = (c0 + 16 * hb + j) / R;
-            float m_ = 0.0f, dg_ = 0.0f, d_ = 0.0f;
-            if (s < rl) {
-              const float dec = expc(acl - ts.ac[s]);
-              const float ws = ts.w[s];
-              const float gd = g[j] * dec;
-              m_ = gd * ws;
-              dg_ = dm[j] * dec * ws;
-              d_ = dm[j] * gd;
-              rowE += d_ * ws;
-            } else if (s == rl) {
-              m_ = g[j] * ts.g[s];
-              dg_ = dm[j] * ts.g[s];
-              dgp += dm[j] * g[j];
-            }
-            mv[j] = m_; dgv[j] = dg_; dbd[16 * hb + j] = d_;
+        for (int hb = 0; hb < 2; ++hb) { tmem_ld_fence(gq[hb]); tmem_ld_fence(dmq[hb]); }
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+          const float (&g)[16] = gq[hb];
+          const float (&dm)[16] = dmq[hb];
+          float mv[16], dgv[16];
+          ColScalars<R> cs;
+          load_col_scalars<R>(cs, ts, c0 + 16 * hb);
+          const int s0 = (c0 + 16 * hb) / R;
+          const float rf = row_factor(acl, ts.ac[s0 + 16 / R - 1]);  // one exponential per chunk
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {  // branch-free selects: below / on / above the diagonal
+            const int si = j / R, s = s0 + si;
+            const bool below = s < rl, on = s == rl;
+            const float dec = rf * cs.cf[si];
+            const float wgt = below ? cs.w[si] * dec : (on ? cs.g[si] : 0.0f);
+            const float gd = g[j] * dec;
+            const float d_ = below ? dm[j] * gd : 0.0f;
+            mv[j] = g[j] * wgt;
+            dgv[j] = dm[j] * wgt;
+            rowE += d_ * cs.w[si];
+            dgp += on ? dm[j] * g[j] : 0.0f;
+            dbd[16 * hb + j] = d_;
           }
           float lo[8], hi[8];
 #pragma unroll
@@ -193,42 +234,44 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
       part_row[ch * 128 + row] = rowE;
       part_dg[ch * 128 + row] = dgp;
       // carry-out term: T1 = dY~ H_k ; d acum += exp(acum) <T1, C^> ; dC^ base = exp(acum) T1
+      float t1[4][16], dhv[2][16];
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) tmem_ld16_issue(tmem_addr(tm, quad * 32, TM_T1 + 64 * ch + 16 * cc), t1[cc]);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) tmem_ld16_issue(tmem_addr(tm, quad * 32, TM_DH + 32 * ch + 16 * cc), dhv[cc]);
+      tmem_wait_ld();
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) tmem_ld_fence(t1[cc]);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) tmem_ld_fence(dhv[cc]);
       const float eac = ts.eac[rl];
       float dot = 0.0f;
-#pragma unroll 1
+#pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
         const int n0 = 64 * ch + 16 * cc;
-        float v[16], c1[8], c2[8];
-        tmem_ld16(tmem_addr(tm, quad * 32, TM_T1 + n0), v);
+        float c1[8], c2[8];
         load_chunk(sC, tile_off(row, n0, kN), c1);
         load_chunk(sC, tile_off(row, n0 + 8, kN), c2);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { dot += v[j] * c1[j] + v[8 + j] * c2[j]; }
+        for (int j = 0; j < 8; ++j) { dot += t1[cc][j] * c1[j] + t1[cc][8 + j] * c2[j]; }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] *= eac;
-        tmem_st16(tmem_addr(tm, quad * 32, TM_T1 + n0), v);
+        for (int j = 0; j < 16; ++j) t1[cc][j] *= eac;
+        tmem_st16(tmem_addr(tm, quad * 32, TM_T1 + n0), t1[cc]);
       }
       part_t1[ch * 128 + row] = dot;
-    }
-    float dcd_part = 0.0f;
-    {  // state gradient: lanes are n, columns p
-      const float* hk = p.ckpt_h + (((size_t)bh * ntiles + k) * kN + row) * kP;
+      // state gradient: lanes are n, columns p
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int p0 = 32 * ch + 16 * cc;
-        float v[16];
-        tmem_ld16(tmem_addr(tm, quad * 32, TM_DH + p0), v);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float4 h4 = *reinterpret_cast<const float4*>(hk + p0 + 4 * j);
-          dcd_part += v[4 * j] * h4.x + v[4 * j + 1] * h4.y + v[4 * j + 2] * h4.z + v[4 * j + 3] * h4.w;
+        for (int j = 0; j < 16; ++j) {
+          __nv_bfloat16* slot = reinterpret_cast<__nv_bfloat16*>(sHS + tile_off(p0 + j, row, kN));
+          dcd_part += dhv[cc][j] * __bfloat162float(*slot);  // <dH, H_k>
+          *slot = __float2bfloat16_rn(dhv[cc][j]);           // dS_k replaces H_k
         }
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-          *reinterpret_cast<__nv_bfloat16*>(sHS + tile_off(p0 + j, row, kN)) = __float2bfloat16_rn(v[j]);  // dS_k
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] *= ecd;
-        tmem_st16(tmem_addr(tm, quad * 32, TM_DH + p0), v);
+        for (int j = 0; j < 16; ++j) dhv[cc][j] *= ecd;
+        tmem_st16(tmem_addr(tm, quad * 32, TM_DH + p0), dhv[cc]);
       }
     }
     tmem_wait_st();
@@ -236,6 +279,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    TICK(4);
     // ---- 6. MMA phase B ------------------------------------------------------------------------
     if (tid == 0) {
       tc_fence_after();
@@ -253,14 +297,36 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
       if (__syncthreads_or(!ok)) { failed = true; break; }
     }
     tc_fence_after();
+    TICK(5);
     // ---- 7. epilogue B -------------------------------------------------------------------------
     if (ROT) {  // the angles again (their buffer held M in between)
-      tile_angles<R>(sPhi, s_q, s_carry, ts.dt, p.theta, b, h, H, T, t0, nullptr);
+      RawTheta<R> th2;
+      issue_theta<R>(th2, p.theta, tok0, H, T, t0);
+      commit_theta<R>(th2, sPhi);
+      __syncthreads();
+      tile_angles_smem<R>(sPhi, s_q, s_carry, ts.dt, T, t0, nullptr);
       __syncthreads();
     }
+    TICK(6);
     const int t = t0 + rl;
     const bool live = t < T;
     const bool at_end = last_tile && rl == l_end;
+    // Column blocks of this thread in a [128 x 128] gradient tile: with rotation the pairs
+    // (m, m + 64) must sit in one thread, so it takes [32ch, 32ch+32) and [64+32ch, 64+32ch+32).
+    auto gcol = [&](int q4) { return ROT ? ((q4 >> 1) * kNH + 32 * ch + 16 * (q4 & 1)) : (64 * ch + 16 * q4); };
+    float acc[2][16], u[2][16], gq[4][16];
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+      tmem_ld16_issue(tmem_addr(tm, quad * 32, TM_DX + 32 * ch + 16 * cc), acc[cc]);
+      tmem_ld16_issue(tmem_addr(tm, quad * 32, TM_U + 32 * ch + 16 * cc), u[cc]);
+    }
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) tmem_ld16_issue(tmem_addr(tm, quad * 32, TM_DB + gcol(q4)), gq[q4]);
+    tmem_wait_ld();
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) { tmem_ld_fence(acc[cc]); tmem_ld_fence(u[cc]); }
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) tmem_ld_fence(gq[q4]);
     float dD_part = 0.0f;
     {  // dx = M^T dY~ + sw (B^ dS^T) + D dy ; q = <U, x>
       const float sw = ts.sw[rl];
@@ -268,148 +334,94 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int p0 = 32 * ch + 16 * cc;
-        float acc[16], u[16], xv[16], dyv[16];
-        tmem_ld16(tmem_addr(tm, quad * 32, TM_DX + p0), acc);
-        tmem_ld16(tmem_addr(tm, quad * 32, TM_U + p0), u);
-        {
-          float a8[8], b8[8];
-          load_chunk(sX, tile_off(row, p0, kP), a8);
-          load_chunk(sX, tile_off(row, p0 + 8, kP), b8);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) { xv[j] = a8[j]; xv[8 + j] = b8[j]; }
-          load_chunk(sDY, tile_off(row, p0, kP), a8);
-          load_chunk(sDY, tile_off(row, p0 + 8, kP), b8);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) { dyv[j] = a8[j]; dyv[8 + j] = b8[j]; }
-        }
+        float xv[16], dyv[16];
+        load_chunk(sX, tile_off(row, p0, kP), *reinterpret_cast<float(*)[8]>(&xv[0]));
+        load_chunk(sX, tile_off(row, p0 + 8, kP), *reinterpret_cast<float(*)[8]>(&xv[8]));
+        load_chunk(sDY, tile_off(row, p0, kP), *reinterpret_cast<float(*)[8]>(&dyv[0]));
+        load_chunk(sDY, tile_off(row, p0 + 8, kP), *reinterpret_cast<float(*)[8]>(&dyv[8]));
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          qp += u[j] * xv[j];
+          qp += u[cc][j] * xv[j];
           dD_part += dyv[j] * xv[j];
-          acc[j] += sw * u[j] + dsk * dyv[j];
+          acc[cc][j] += sw * u[cc][j] + dsk * dyv[j];
         }
         if (at_end && p.dlu) {  // gradient through last_u = sum_r x (x) B^ at the final token
+#pragma unroll 1
           for (int j = 0; j < 16; ++j) {
             const float* gl = p.dlu + ((size_t)bh * kP + p0 + j) * kN;
-            float s = 0.0f;
+            float s_ = 0.0f;
             for (int n = 0; n < kN; ++n)
-              s += gl[n] * __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sB + tile_off(row, n, kN)));
-            acc[j] += s;
-          }
-        }
-        if (live && p.dx) {
-          __nv_bfloat16* dst = p.dx + (tok0 + (size_t)rl * H) * kP * R;
-          if (R == 1) {
-            uint4 q0, q1;
-            q0.x = pack_bf16(acc[0], acc[1]); q0.y = pack_bf16(acc[2], acc[3]); q0.z = pack_bf16(acc[4], acc[5]); q0.w = pack_bf16(acc[6], acc[7]);
-            q1.x = pack_bf16(acc[8], acc[9]); q1.y = pack_bf16(acc[10], acc[11]); q1.z = pack_bf16(acc[12], acc[13]); q1.w = pack_bf16(acc[14], acc[15]);
-            reinterpret_cast<uint4*>(dst + p0)[0] = q0;
-            reinterpret_cast<uint4*>(dst + p0)[1] = q1;
-          } else {
+              s_ += gl[n] * __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sB + tile_off(row, n, kN)));
+            float add[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) dst[(size_t)(p0 + j) * R + rr] = __float2bfloat16_rn(acc[j]);
+            for (int jj = 0; jj < 16; ++jj) add[jj] = (jj == j) ? s_ : 0.0f;
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) acc[cc][jj] += add[jj];
           }
         }
+        stage_store16<kP>(sHS, row, p0, acc[cc]);  // dS is spent: its buffer stages dx
       }
       part_q[ch * 128 + row] = qp;
     }
-    {  // dB^ (TM_DB, operand sB, out db) and dC^ (TM_T1, operand sC, out dc)
+    TICK(7);
+    {  // dB^ (TM_DB, operand sB, out db) then dC^ (TM_T1, operand sC, out dc)
       float dphi[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) dphi[j] = 0.0f;
+      float gc[4][16];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) tmem_ld16_issue(tmem_addr(tm, quad * 32, TM_T1 + gcol(q4)), gc[q4]);  // in flight during dB^
+      auto finish = [&](float (&g)[4][16], const uint8_t* sop, uint8_t* stg, bool is_b) {
+        if (is_b && at_end && p.dlu) {  // d last_u reaches B^ of the final token: += dlu^T x
 #pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        const uint32_t tcol = which ? TM_T1 : TM_DB;
-        const uint8_t* sop = which ? sC : sB;
-        __nv_bfloat16* gout = which ? p.dc : p.db;
-        __nv_bfloat16* dst = gout ? gout + (tok0 + (size_t)rl * H) * kN * R : nullptr;
+          for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll 1
+            for (int j = 0; j < 16; ++j) {
+              const int n = gcol(q4) + j;
+              float s_ = 0.0f;
+              for (int pp = 0; pp < kP; ++pp)
+                s_ += p.dlu[((size_t)bh * kP + pp) * kN + n] *
+                      __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sX + tile_off(row, pp, kP)));
+#pragma unroll
+              for (int a4 = 0; a4 < 4; ++a4)
+#pragma unroll
+                for (int jj = 0; jj < 16; ++jj) g[a4][jj] += (a4 == q4 && jj == j) ? s_ : 0.0f;
+            }
+        }
         if (ROT) {
 #pragma unroll
           for (int mc = 0; mc < 2; ++mc) {
             const int m0 = 32 * ch + 16 * mc;
-            float g1[16], g2[16], o1[16], o2[16];
-            tmem_ld16(tmem_addr(tm, quad * 32, tcol + m0), g1);
-            tmem_ld16(tmem_addr(tm, quad * 32, tcol + kNH + m0), g2);
-            {
-              float a8[8], b8[8];
-              load_chunk(sop, tile_off(row, m0, kN), a8);
-              load_chunk(sop, tile_off(row, m0 + 8, kN), b8);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) { o1[j] = a8[j]; o1[8 + j] = b8[j]; }
-              load_chunk(sop, tile_off(row, kNH + m0, kN), a8);
-              load_chunk(sop, tile_off(row, kNH + m0 + 8, kN), b8);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) { o2[j] = a8[j]; o2[8 + j] = b8[j]; }
-            }
-            if (which == 0 && at_end && p.dlu) {
-              for (int j = 0; j < 16; ++j) {
-                float s1 = 0.0f, s2 = 0.0f;
-                for (int pp = 0; pp < kP; ++pp) {
-                  const float xv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sX + tile_off(row, pp, kP)));
-                  s1 += p.dlu[((size_t)bh * kP + pp) * kN + m0 + j] * xv;
-                  s2 += p.dlu[((size_t)bh * kP + pp) * kN + kNH + m0 + j] * xv;
-                }
-                g1[j] += s1; g2[j] += s2;
-              }
-            }
+            float (&g1)[16] = g[mc];
+            float (&g2)[16] = g[2 + mc];
+            float o1[16], o2[16];
+            load_chunk(sop, tile_off(row, m0, kN), *reinterpret_cast<float(*)[8]>(&o1[0]));
+            load_chunk(sop, tile_off(row, m0 + 8, kN), *reinterpret_cast<float(*)[8]>(&o1[8]));
+            load_chunk(sop, tile_off(row, kNH + m0, kN), *reinterpret_cast<float(*)[8]>(&o2[0]));
+            load_chunk(sop, tile_off(row, kNH + m0 + 8, kN), *reinterpret_cast<float(*)[8]>(&o2[8]));
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               dphi[16 * mc + j] += g1[j] * o2[j] - g2[j] * o1[j];
               float sn, cs;
-              __sincosf(sPhi[rl * kNH + m0 + j], &sn, &cs);
+              sincos_poly(sPhi[phi_idx(rl, m0 + j)], &sn, &cs);
               const float u1 = g1[j] * cs - g2[j] * sn, u2 = g1[j] * sn + g2[j] * cs;
               g1[j] = u1; g2[j] = u2;
             }
-            if (live && dst) {
-              if (R == 1) {
-                uint4 q0, q1;
-                q0.x = pack_bf16(g1[0], g1[1]); q0.y = pack_bf16(g1[2], g1[3]); q0.z = pack_bf16(g1[4], g1[5]); q0.w = pack_bf16(g1[6], g1[7]);
-                q1.x = pack_bf16(g1[8], g1[9]); q1.y = pack_bf16(g1[10], g1[11]); q1.z = pack_bf16(g1[12], g1[13]); q1.w = pack_bf16(g1[14], g1[15]);
-                reinterpret_cast<uint4*>(dst + m0)[0] = q0;
-                reinterpret_cast<uint4*>(dst + m0)[1] = q1;
-                q0.x = pack_bf16(g2[0], g2[1]); q0.y = pack_bf16(g2[2], g2[3]); q0.z = pack_bf16(g2[4], g2[5]); q0.w = pack_bf16(g2[6], g2[7]);
-                q1.x = pack_bf16(g2[8], g2[9]); q1.y = pack_bf16(g2[10], g2[11]); q1.z = pack_bf16(g2[12], g2[13]); q1.w = pack_bf16(g2[14], g2[15]);
-                reinterpret_cast<uint4*>(dst + kNH + m0)[0] = q0;
-                reinterpret_cast<uint4*>(dst + kNH + m0)[1] = q1;
-              } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  dst[(size_t)(m0 + j) * R + rr] = __float2bfloat16_rn(g1[j]);
-                  dst[(size_t)(kNH + m0 + j) * R + rr] = __float2bfloat16_rn(g2[j]);
-                }
-              }
-            }
-          }
-        } else {
-#pragma unroll 1
-          for (int cc = 0; cc < 4; ++cc) {
-            const int n0 = 64 * ch + 16 * cc;
-            float g1[16];
-            tmem_ld16(tmem_addr(tm, quad * 32, tcol + n0), g1);
-            if (which == 0 && at_end && p.dlu) {
-              for (int j = 0; j < 16; ++j) {
-                float s1 = 0.0f;
-                for (int pp = 0; pp < kP; ++pp)
-                  s1 += p.dlu[((size_t)bh * kP + pp) * kN + n0 + j] *
-                        __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sX + tile_off(row, pp, kP)));
-                g1[j] += s1;
-              }
-            }
-            if (live && dst) {
-              if (R == 1) {
-                uint4 q0, q1;
-                q0.x = pack_bf16(g1[0], g1[1]); q0.y = pack_bf16(g1[2], g1[3]); q0.z = pack_bf16(g1[4], g1[5]); q0.w = pack_bf16(g1[6], g1[7]);
-                q1.x = pack_bf16(g1[8], g1[9]); q1.y = pack_bf16(g1[10], g1[11]); q1.z = pack_bf16(g1[12], g1[13]); q1.w = pack_bf16(g1[14], g1[15]);
-                reinterpret_cast<uint4*>(dst + n0)[0] = q0;
-                reinterpret_cast<uint4*>(dst + n0)[1] = q1;
-              } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) dst[(size_t)(n0 + j) * R + rr] = __float2bfloat16_rn(g1[j]);
-              }
-            }
           }
         }
-      }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) stage_store16<kN>(stg, row, gcol(q4), g[q4]);
+      };
+      finish(gq, sB, sXw, true);     // sigma_w X~ and exp(acum) dY~ are spent: 32 KB to stage dB
+      tmem_wait_ld();
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) tmem_ld_fence(gc[q4]);
+      finish(gc, sC, sDG, false);    // dG is spent: its buffer stages dC
+      __syncthreads();
+      if (p.dx) copy_out<R, kP>(sHS, p.dx, tok0, H, T, t0);
+      if (p.db) copy_out<R, kN>(sXw, p.db, tok0, H, T, t0);
+      if (p.dc) copy_out<R, kN>(sDG, p.dc, tok0, H, T, t0);
+      __syncthreads();
       if (ROT) {
         // d phi of a time step sums its R rows (adjacent lanes); it then overwrites dG's buffer,
         // which the phase-B products have finished reading.
@@ -420,53 +432,77 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
           for (int o = 1; o < R; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
           dphi[j] = v;
         }
-        __syncthreads();  // every thread is done reading sB / sC / sM-as-phi? (phi stays; dG region is free)
         if (rr == 0) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             float v = live ? dphi[j] : 0.0f;
             if (at_end && p.dangle) v += p.dangle[(size_t)bh * kNH + 32 * ch + j];
-            sDphi[rl * kNH + 32 * ch + j] = v;
+            sDphi[phi_idx(rl, 32 * ch + j)] = v;
           }
         }
       }
     }
+    TICK(8);
     const float dD_tile = cta_sum(dD_part, s_red);  // also orders part_* and sDphi for what follows
     if (tid == 0) p.partD[(size_t)bh * ntiles + k] = dD_tile;
     // ---- 8. reverse cumulative sum of d phi over time -> d theta, and the dt term -----------------
     if (ROT) {
-      constexpr int LQ = LT / 4;
+      constexpr int LQ = LT / 4, NV = 4 / R;  // NV: (time step, 8-plane group) items per thread
       const int q = tid >> 6, m = tid & 63;
+      uint4 thq[NV];  // theta of this thread's items of the vector pass below, requested early
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int it = tid + 256 * i, l = it >> 3, mg = it & 7;
+        thq[i] = (t0 + l < T) ? __ldg(reinterpret_cast<const uint4*>(p.theta + (tok0 + (size_t)l * H) * kNH + mg * 8))
+                              : make_uint4(0u, 0u, 0u, 0u);
+      }
       float run = 0.0f;
+#pragma unroll
       for (int i = LQ - 1; i >= 0; --i) {
         const int l = q * LQ + i;
-        run += sDphi[l * kNH + m];
-        sDphi[l * kNH + m] = run;
+        run += sDphi[phi_idx(l, m)];
+        sDphi[phi_idx(l, m)] = run;
       }
       s_q[q * 64 + m] = run;
       __syncthreads();
       float off = s_dcar[m];
       for (int qq = 3; qq > q; --qq) off += s_q[qq * 64 + m];
-      for (int i = 0; i < LQ; ++i) {
-        const int l = q * LQ + i, tt = t0 + l;
-        const float ds = sDphi[l * kNH + m] + off;
-        float prod = 0.0f;
-        if (tt < T) {
-          const size_t ti = (tok0 + (size_t)l * H) * kNH + m;
-          if (p.dtheta) p.dtheta[ti] = __float2bfloat16_rn(ds * ts.dt[l]);
-          prod = ds * bf(p.theta, ti);
-        }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) prod += __shfl_xor_sync(0xffffffffu, prod, o);
-        if (lane == 0) part_rot[((tid >> 5) & 1) * 128 + l] = prod;
-      }
+      for (int i = 0; i < LQ; ++i) sDphi[phi_idx(q * LQ + i, m)] += off;  // d step: sum of d phi from here on
       const float total = off + s_q[0 * 64 + m];  // for q == 0: carry + all four quarters
       __syncthreads();
       if (q == 0) {
         s_dcar[m] = total;
         if (k == 0 && p.dangle0) p.dangle0[(size_t)bh * kNH + m] = total;
       }
+      // vector pass: d theta = d step * dt (16-byte stores) and the rotation's share of d dt
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int it = tid + 256 * i, l = it >> 3, mg = it & 7;
+        const float4 d0 = *reinterpret_cast<const float4*>(&sDphi[phi_idx(l, mg * 8)]);
+        const float4 d1 = *reinterpret_cast<const float4*>(&sDphi[phi_idx(l, mg * 8 + 4)]);
+        const float ds[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+        const uint32_t tw[4] = {thq[i].x, thq[i].y, thq[i].z, thq[i].w};
+        const float dtl = ts.dt[l];
+        float prod = 0.0f, o[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          prod += ds[2 * j] * bf16_lo(tw[j]) + ds[2 * j + 1] * bf16_hi(tw[j]);
+          o[2 * j] = ds[2 * j] * dtl;
+          o[2 * j + 1] = ds[2 * j + 1] * dtl;
+        }
+        if (t0 + l < T && p.dtheta) {
+          uint4 qv;
+          qv.x = pack_bf16(o[0], o[1]); qv.y = pack_bf16(o[2], o[3]); qv.z = pack_bf16(o[4], o[5]); qv.w = pack_bf16(o[6], o[7]);
+          *reinterpret_cast<uint4*>(p.dtheta + (tok0 + (size_t)l * H) * kNH + mg * 8) = qv;
+        }
+#pragma unroll
+        for (int o_ = 1; o_ < 8; o_ <<= 1) prod += __shfl_xor_sync(0xffffffffu, prod, o_);
+        if (mg == 0) part_rot[l] = prod;
+      }
+      __syncthreads();
     }
+    TICK(9);
     // ---- 9. per-token scalars of the tile ---------------------------------------------------------
     if (tid < LT) {
       const int l = tid;
@@ -490,7 +526,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
       const size_t o = (size_t)bh * Tp + t0 + l;
       p.dw[o] = col + sg * q;
       p.dg[o] = dgv;
-      if (ROT) p.ddt_rot[o] = part_rot[l] + part_rot[128 + l];
+      if (ROT) p.ddt_rot[o] = part_rot[l];
     }
     __syncthreads();
     if (warp == 0) {  // reverse inclusive scan of d acum (+ the chunk-decay terms on the last step)
@@ -530,6 +566,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    TICK(10);
   }
   // ---- gradient of the seed state -----------------------------------------------------------------
   if (!failed) {
@@ -572,6 +609,15 @@ cudaError_t launch_r(cudaStream_t st, const TcBwdParams& p, bool rot) {
 }
 
 }  // namespace
+
+#ifdef M3_TC_TIMING
+extern "C" void m3_debug_timing_bwd(long long* out, int reset) {
+  long long z[16] = {0};
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, g_tcb_timing, sizeof(z));
+  if (reset) cudaMemcpyToSymbol(g_tcb_timing, z, sizeof(z));
+}
+#endif
 
 cudaError_t tc_backward(cudaStream_t st, const TcBwdParams& p, bool rot) {
   switch (p.R) {

@@ -15,6 +15,58 @@ __device__ __forceinline__ float wrap2pi(float v) { return v - rintf(v * kInvTwo
 __device__ __forceinline__ float expc(float d) { return __expf(fmaxf(d, -60.0f)); }
 __device__ __forceinline__ float inside(float d) { return (d > -60.0f && d < 0.0f) ? 1.0f : 0.0f; }
 
+// sin and cos of an angle already wrapped into [-pi, pi], as polynomials in x^2 on the FMA pipe
+// (max error 3e-7): the special-function unit is the scarcest resource of these kernels.
+__device__ __forceinline__ void sincos_poly(float x, float* sn, float* cs) {
+  const float z = x * x;
+  float s = -2.069813466e-08f;
+  s = fmaf(s, z, 2.708831159e-06f);
+  s = fmaf(s, z, -1.981763099e-04f);
+  s = fmaf(s, z, 8.332791503e-03f);
+  s = fmaf(s, z, -1.666662111e-01f);
+  s = fmaf(s, z, 9.999999378e-01f);
+  float c = 1.724509175e-09f;
+  c = fmaf(c, z, -2.707903082e-07f);
+  c = fmaf(c, z, 2.476988356e-05f);
+  c = fmaf(c, z, -1.388780360e-03f);
+  c = fmaf(c, z, 4.166648922e-02f);
+  c = fmaf(c, z, -4.999998910e-01f);
+  c = fmaf(c, z, 9.999999891e-01f);
+  *sn = x * s;
+  *cs = c;
+}
+
+// Index of angle (l, m) in a [LT][64] float buffer whose 16-byte chunks are XOR-swizzled by
+// l & 7: threads that own different rows read the same plane group without bank conflicts.
+__device__ __forceinline__ int phi_idx(int l, int m) { return l * kNH + ((((m >> 2) ^ (l & 7)) << 2) | (m & 3)); }
+
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// Ask L2 for every input row of tile `t0` (and a 16 KB checkpoint), one 128-byte line per thread
+// and tensor: the real loads of that tile, a whole tile period later, then hit L2.
+template <int R, bool ROT>
+__device__ __forceinline__ void prefetch_tile_l2(const __nv_bfloat16* gb, const __nv_bfloat16* gc, const __nv_bfloat16* gx,
+                                                 const __nv_bfloat16* gdy, const __nv_bfloat16* gth, const void* ckpt,
+                                                 size_t tok0, int H, int T, int t0) {
+  constexpr int LT = kRows / R;
+  const int tid = threadIdx.x;
+  {  // B and C: LT rows of 256 R bytes = 2R lines each -> exactly 256 lines per tensor
+    const int l = tid / (2 * R), j = tid % (2 * R);
+    if (t0 + l < T) {
+      const size_t off = (tok0 + (size_t)l * H) * kN * R + (size_t)j * 64;
+      prefetch_l2(gb + off);
+      prefetch_l2(gc + off);
+    }
+  }
+  {  // x (threads 0..127) and dy (threads 128..255): LT rows of R lines
+    const int u = tid & 127, l = u / R, j = u % R;
+    const __nv_bfloat16* g = (tid < 128) ? gx : gdy;
+    if (g && t0 + l < T) prefetch_l2(g + (tok0 + (size_t)l * H) * kP * R + (size_t)j * 64);
+  }
+  if (ROT && tid < LT && t0 + tid < T) prefetch_l2(gth + (tok0 + (size_t)tid * H) * kNH);
+  if (ckpt && tid >= 128) prefetch_l2(static_cast<const char*>(ckpt) + (size_t)(tid - 128) * 128);
+}
+
 template <int R>
 __device__ __forceinline__ void load_row_group(const __nv_bfloat16* src, bool live, uint32_t (&raw)[4 * R]) {
   if (live) {
@@ -48,24 +100,43 @@ __device__ __forceinline__ void load_chunk(const uint8_t* base, uint32_t off, fl
 // Scalar arrays of one tile, all [kScal] floats in shared memory.
 struct TileScalars {
   float *dt, *lam, *a, *ac, *g, *w, *sw, *eac;
+  float *cf;   // cf[s] = exp(ac[e(s)] - ac[s]) <= 1, e(s) = last time step of s's 16-column chunk
 };
+constexpr int kNumScal = 9;  // arrays in a TileScalars block
 
-// dt, lambda (with one step of look-ahead), g, w (shifted add), a = dt A, its inclusive
-// cumulative sum ac, sw = exp(cd - ac) w and eac = exp(ac).  Ends with every array visible
-// to all threads (the caller's next __syncthreads is still required for sw / eac).
+// Decay between a row's step l and the columns of one 16-column chunk, factorised so that a
+// thread pays ONE exponential per chunk: exp(ac_l - ac_s) = exp(ac_l - ac_e) * cf[s].  The row
+// factor exceeds 1 only for rows inside the chunk, where it is bounded by the chunk's own span;
+// it is clamped at e^80 (a chunk whose 16 / R steps decay by more than e^80 has no
+// representable contribution left) and at e^-87 below.
+__device__ __forceinline__ float row_factor(float ac_l, float ac_e) {
+  return __expf(fminf(fmaxf(ac_l - ac_e, -87.0f), 80.0f));
+}
+
+// dt and lambda of step t0 + tid (threads tid <= LT; one step of look-ahead), as registers, so
+// the loads of the NEXT tile can be in flight while the current one computes.
 template <int R>
-__device__ __forceinline__ void tile_scalars(const TileScalars& s, const __nv_bfloat16* dt, const __nv_bfloat16* lam,
-                                             int disc, float A, int b, int h, int H, int T, int t0) {
+__device__ __forceinline__ void load_dt_lam(float& vdt, float& vl, const __nv_bfloat16* dt, const __nv_bfloat16* lam,
+                                            int disc, int b, int h, int H, int T, int t0) {
+  constexpr int LT = kRows / R;
+  const int tid = threadIdx.x, t = t0 + tid;
+  vdt = 0.0f;
+  vl = 1.0f;
+  if (tid <= LT && t >= 0 && t < T) {
+    const size_t i = ((size_t)b * T + t) * H + h;
+    vdt = bf(dt, i);
+    vl = disc == 0 ? 1.0f : (disc == 1 ? 0.5f : bf(lam, i));
+  }
+}
+
+// g, w (shifted add), a = dt A, its inclusive cumulative sum ac, sw = exp(cd - ac) w,
+// eac = exp(ac) and the column factors cf, from the (dt, lambda) registers of load_dt_lam.
+// The caller's next __syncthreads makes sw / eac / cf visible.
+template <int R>
+__device__ __forceinline__ void tile_scalars(const TileScalars& s, float vdt, float vl, float A, int T, int t0) {
   constexpr int LT = kRows / R;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid <= LT) {
-    const int t = t0 + tid;
-    float vdt = 0.0f, vl = 1.0f;
-    if (t < T) {
-      const size_t i = ((size_t)b * T + t) * H + h;
-      vdt = bf(dt, i);
-      vl = disc == 0 ? 1.0f : (disc == 1 ? 0.5f : bf(lam, i));
-    }
     s.dt[tid] = vdt;
     s.lam[tid] = vl;
   }
@@ -100,92 +171,96 @@ __device__ __forceinline__ void tile_scalars(const TileScalars& s, const __nv_bf
   }
   __syncthreads();
   if (tid < LT) {
-    const float cd = s.ac[LT - 1];
-    s.sw[tid] = expc(cd - s.ac[tid]) * s.w[tid];
-    s.eac[tid] = expc(s.ac[tid]);
+    constexpr int SPC = 16 / R;  // time steps per 16-column chunk
+    const float cd = s.ac[LT - 1], ac = s.ac[tid];
+    s.sw[tid] = expc(cd - ac) * s.w[tid];
+    s.eac[tid] = expc(ac);
+    s.cf[tid] = __expf(fmaxf(s.ac[(tid / SPC) * SPC + SPC - 1] - ac, -87.0f));
   }
 }
 
-// phi[l][m] = wrap(carry[m] + sum_{l' <= l} dt_l' theta[t0 + l'][m]) for the tile; returns (to
-// threads with q == 3) the wrapped angle leaving the tile.  s_q: [4][64] scratch.  Contains
-// one __syncthreads; the caller syncs again before reading phi written by other threads.
-template <int R>
-__device__ __forceinline__ float tile_angles(float* sPhi, float* s_q, const float* carry, const float* s_dt,
-                                             const __nv_bfloat16* theta, int b, int h, int H, int T, int t0,
-                                             float* angle_out_bh) {
-  constexpr int LT = kRows / R, LQ = LT / 4;
-  const int tid = threadIdx.x, q = tid >> 6, m = tid & 63;
-  float run = 0.0f;
-#pragma unroll 4
-  for (int i = 0; i < LQ; ++i) {
-    const int l = q * LQ + i, t = t0 + l;
-    if (t < T) run += s_dt[l] * bf(theta, (((size_t)b * T + t) * H + h) * kNH + m);
-    sPhi[l * kNH + m] = run;
-  }
-  s_q[q * 64 + m] = run;
-  __syncthreads();
-  float off = carry[m];
-  for (int qq = 0; qq < q; ++qq) off += s_q[qq * 64 + m];
-  for (int i = 0; i < LQ; ++i) {
-    const int l = q * LQ + i;
-    const float wv = wrap2pi(sPhi[l * kNH + m] + off);
-    sPhi[l * kNH + m] = wv;
-    if (angle_out_bh && t0 + l == T - 1) angle_out_bh[m] = wv;
-  }
-  return wrap2pi(off + s_q[3 * 64 + m]);  // meaningful for q == 3
+// ---------------------------------------------------------------------------------------
+// Split staging: `issue_*` puts every global load of a tile in flight (into registers) before
+// anything depends on them; `commit_*` converts and stores once the scalars and angles exist.
+// Work items are (time step l, 16-byte group) pairs laid over the warp as 4 steps x 8 groups.
+// ---------------------------------------------------------------------------------------
+template <int GB>
+__device__ __forceinline__ void item_coords(int i, int& l, int& grp) {
+  // 4 steps x 8 groups per warp: each row contributes a full 128-byte line to a warp's load
+  // (half as many lines per instruction as an 8 x 4 split, which measured 3-6 % slower end to
+  // end), at the price of 2-way conflicts on the 16-byte operand stores.
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int w = warp + 8 * i;
+  constexpr int GB8 = GB / 2;
+  l = (w / GB8) * 4 + (lane & 3);
+  grp = (w % GB8) * 8 + (lane >> 2);
 }
 
-// Rotated (or plain) B^ / C^ rows of the tile into [128 x 128] operand buffers.
 template <int R, bool ROT>
-__device__ __forceinline__ void stage_bc(uint8_t* sB, uint8_t* sC, const __nv_bfloat16* gb, const __nv_bfloat16* gc,
-                                         const float* sPhi, size_t tok0, int H, int T, int t0) {
-  constexpr int LT = kRows / R;
-  const int tid = threadIdx.x;
-  if (ROT) {
-    for (int it = tid; it < LT * 8; it += 256) {
-      const int l = it >> 3, m0 = (it & 7) * 8;
-      const bool live = t0 + l < T;
+struct RawBC {
+  static constexpr int NIT = (ROT ? 4 : 8) / R;
+  static constexpr int NP = ROT ? 2 : 1;
+  static constexpr int GB = ROT ? 2 : 4;
+  uint32_t v[NIT][2][NP][4 * R];
+};
+
+template <int R, bool ROT>
+__device__ __forceinline__ void issue_bc(RawBC<R, ROT>& raw, const __nv_bfloat16* gb, const __nv_bfloat16* gc,
+                                         size_t tok0, int H, int T, int t0) {
+  using RB = RawBC<R, ROT>;
+#pragma unroll
+  for (int i = 0; i < RB::NIT; ++i) {
+    int l, grp;
+    item_coords<RB::GB>(i, l, grp);
+    const bool live = t0 + l < T;
+    const size_t base = (tok0 + (size_t)l * H) * kN * R + (size_t)grp * 8 * R;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const __nv_bfloat16* src = which ? gc : gb;
+#pragma unroll
+      for (int part = 0; part < RB::NP; ++part)
+        load_row_group<R>(src + base + (size_t)part * kNH * R, live, raw.v[i][which][part]);
+    }
+  }
+}
+
+template <int R, bool ROT>
+__device__ __forceinline__ void commit_bc(const RawBC<R, ROT>& raw, uint8_t* sB, uint8_t* sC, const float* sPhi) {
+  using RB = RawBC<R, ROT>;
+#pragma unroll
+  for (int i = 0; i < RB::NIT; ++i) {
+    int l, grp;
+    item_coords<RB::GB>(i, l, grp);
+    const int n0 = grp * 8;
+    if (ROT) {
       float cs[8], sn[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) __sincosf(sPhi[l * kNH + m0 + j], &sn[j], &cs[j]);
-      const size_t base = (tok0 + (size_t)l * H) * kN * R;
+      for (int j = 0; j < 8; ++j) sincos_poly(sPhi[phi_idx(l, n0 + j)], &sn[j], &cs[j]);
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
-        const __nv_bfloat16* src = which ? gc : gb;
         uint8_t* dst = which ? sC : sB;
-        uint32_t r1[4 * R], r2[4 * R];
-        load_row_group<R>(src + base + (size_t)m0 * R, live, r1);
-        load_row_group<R>(src + base + (size_t)(m0 + kNH) * R, live, r2);
 #pragma unroll
         for (int r = 0; r < R; ++r) {
           float o1[8], o2[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const float v1 = elem(r1, j * R + r), v2 = elem(r2, j * R + r);
+            const float v1 = elem(raw.v[i][which][0], j * R + r), v2 = elem(raw.v[i][which][RB::NP - 1], j * R + r);
             o1[j] = v1 * cs[j] + v2 * sn[j];
             o2[j] = v2 * cs[j] - v1 * sn[j];
           }
-          store_chunk(dst, tile_off(l * R + r, m0, kN), o1);
-          store_chunk(dst, tile_off(l * R + r, m0 + kNH, kN), o2);
+          store_chunk(dst, tile_off(l * R + r, n0, kN), o1);
+          store_chunk(dst, tile_off(l * R + r, n0 + kNH, kN), o2);
         }
       }
-    }
-  } else {
-    for (int it = tid; it < LT * 16; it += 256) {
-      const int l = it >> 4, n0 = (it & 15) * 8;
-      const bool live = t0 + l < T;
-      const size_t base = (tok0 + (size_t)l * H) * kN * R + (size_t)n0 * R;
+    } else {
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
-        const __nv_bfloat16* src = which ? gc : gb;
         uint8_t* dst = which ? sC : sB;
-        uint32_t r1[4 * R];
-        load_row_group<R>(src + base, live, r1);
 #pragma unroll
         for (int r = 0; r < R; ++r) {
           float o[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = elem(r1, j * R + r);
+          for (int j = 0; j < 8; ++j) o[j] = elem(raw.v[i][which][0], j * R + r);
           store_chunk(dst, tile_off(l * R + r, n0, kN), o);
         }
       }
@@ -193,25 +268,154 @@ __device__ __forceinline__ void stage_bc(uint8_t* sB, uint8_t* sC, const __nv_bf
   }
 }
 
-// A [B,T,H,64,R] tensor's tile as a [128 x 64] operand, plus a copy with row l scaled by scale[l].
 template <int R>
-__device__ __forceinline__ void stage_px(uint8_t* s_plain, uint8_t* s_scaled, const __nv_bfloat16* g, const float* scale,
-                                         size_t tok0, int H, int T, int t0) {
-  constexpr int LT = kRows / R;
-  for (int it = threadIdx.x; it < LT * 8; it += 256) {
-    const int l = it >> 3, p0 = (it & 7) * 8;
-    const bool live = t0 + l < T;
-    uint32_t r1[4 * R];
-    load_row_group<R>(g + (tok0 + (size_t)l * H) * kP * R + (size_t)p0 * R, live, r1);
+struct RawPX {
+  static constexpr int NIT = 4 / R;
+  uint32_t v[NIT][4 * R];
+};
+
+template <int R>
+__device__ __forceinline__ void issue_px(RawPX<R>& raw, const __nv_bfloat16* g, size_t tok0, int H, int T, int t0) {
+#pragma unroll
+  for (int i = 0; i < RawPX<R>::NIT; ++i) {
+    int l, grp;
+    item_coords<2>(i, l, grp);
+    load_row_group<R>(g + (tok0 + (size_t)l * H) * kP * R + (size_t)grp * 8 * R, t0 + l < T, raw.v[i]);
+  }
+}
+
+template <int R>
+__device__ __forceinline__ void commit_px(const RawPX<R>& raw, uint8_t* s_plain, uint8_t* s_scaled, const float* scale) {
+#pragma unroll
+  for (int i = 0; i < RawPX<R>::NIT; ++i) {
+    int l, grp;
+    item_coords<2>(i, l, grp);
     const float sv = scale[l];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       float o[8], ow[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { o[j] = elem(r1, j * R + r); ow[j] = o[j] * sv; }
-      store_chunk(s_plain, tile_off(l * R + r, p0, kP), o);
-      store_chunk(s_scaled, tile_off(l * R + r, p0, kP), ow);
+      for (int j = 0; j < 8; ++j) { o[j] = elem(raw.v[i], j * R + r); ow[j] = o[j] * sv; }
+      store_chunk(s_plain, tile_off(l * R + r, grp * 8, kP), o);
+      store_chunk(s_scaled, tile_off(l * R + r, grp * 8, kP), ow);
     }
+  }
+}
+
+// theta of a tile: [LT][64] bf16, 16-byte chunks spread over the CTA.
+template <int R>
+struct RawTheta {
+  static constexpr int NIT = 4 / R;
+  uint4 v[NIT];
+};
+
+template <int R>
+__device__ __forceinline__ void issue_theta(RawTheta<R>& raw, const __nv_bfloat16* theta, size_t tok0, int H, int T, int t0) {
+#pragma unroll
+  for (int i = 0; i < RawTheta<R>::NIT; ++i) {
+    const int c = threadIdx.x + 256 * i, l = c >> 3, c8 = c & 7;
+    raw.v[i] = (t0 + l < T) ? __ldg(reinterpret_cast<const uint4*>(theta + (tok0 + (size_t)l * H) * kNH + c8 * 8))
+                            : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// Store the raw theta rows at the start of the angle buffer (row pitch 128 bytes).
+template <int R>
+__device__ __forceinline__ void commit_theta(const RawTheta<R>& raw, float* sPhi) {
+  uint4* dst = reinterpret_cast<uint4*>(sPhi);
+#pragma unroll
+  for (int i = 0; i < RawTheta<R>::NIT; ++i) dst[threadIdx.x + 256 * i] = raw.v[i];
+}
+
+// As tile_angles, but theta comes from the raw rows commit_theta left in the angle buffer
+// (they are consumed before any angle is written: one __syncthreads separates the passes).
+template <int R>
+__device__ __forceinline__ float tile_angles_smem(float* sPhi, float* s_q, const float* carry, const float* s_dt,
+                                                  int T, int t0, float* angle_out_bh) {
+  constexpr int LT = kRows / R, LQ = LT / 4;
+  const __nv_bfloat16* raw = reinterpret_cast<const __nv_bfloat16*>(sPhi);
+  const int tid = threadIdx.x, q = tid >> 6, m = tid & 63;
+  float loc[LQ];
+  float run = 0.0f;
+#pragma unroll
+  for (int i = 0; i < LQ; ++i) {
+    const int l = q * LQ + i;
+    run += s_dt[l] * __bfloat162float(raw[l * kNH + m]);
+    loc[i] = run;
+  }
+  s_q[q * 64 + m] = run;
+  __syncthreads();
+  float off = carry[m];
+  for (int qq = 0; qq < q; ++qq) off += s_q[qq * 64 + m];
+#pragma unroll
+  for (int i = 0; i < LQ; ++i) {
+    const int l = q * LQ + i;
+    const float wv = wrap2pi(loc[i] + off);
+    sPhi[phi_idx(l, m)] = wv;
+    if (angle_out_bh && t0 + l == T - 1) angle_out_bh[m] = wv;
+  }
+  return wrap2pi(off + s_q[3 * 64 + m]);
+}
+
+// Per-source scalars of the 16 columns [c0, c0 + 16) of a band chunk: 16 / R distinct time steps.
+template <int R>
+struct ColScalars {
+  static constexpr int NS = 16 / R;
+  float cf[NS], w[NS], g[NS];
+};
+template <int R>
+__device__ __forceinline__ void load_col_scalars(ColScalars<R>& c, const TileScalars& ts, int c0) {
+  const int s0 = c0 / R;
+#pragma unroll
+  for (int i = 0; i < ColScalars<R>::NS; ++i) { c.cf[i] = ts.cf[s0 + i]; c.w[i] = ts.w[s0 + i]; c.g[i] = ts.g[s0 + i]; }
+}
+
+// ---------------------------------------------------------------------------------------
+// Output staging: a thread owns a ROW of an accumulator tile, but the caller's tensors want
+// whole rows written by neighbouring lanes.  Rows go to shared memory first ([128][C] bf16,
+// 16-byte chunks XOR-swizzled by row & 7 so that both the row-owner writes and the
+// row-spanning reads are conflict-free), then leave as coalesced 16-byte stores, with the
+// rank de-interleave ((t, r) rows -> [.., C, R] elements) done on the way out.
+// ---------------------------------------------------------------------------------------
+template <int C>
+__device__ __forceinline__ uint32_t stg_off(int row, int chunk) {
+  return (uint32_t)(row * (C * 2) + ((chunk ^ (row & 7)) << 4));
+}
+template <int C>
+__device__ __forceinline__ void stage_store16(uint8_t* stg, int row, int col0, const float (&v)[16]) {
+  uint4 q0, q1;
+  q0.x = pack_bf16(v[0], v[1]); q0.y = pack_bf16(v[2], v[3]); q0.z = pack_bf16(v[4], v[5]); q0.w = pack_bf16(v[6], v[7]);
+  q1.x = pack_bf16(v[8], v[9]); q1.y = pack_bf16(v[10], v[11]); q1.z = pack_bf16(v[12], v[13]); q1.w = pack_bf16(v[14], v[15]);
+  *reinterpret_cast<uint4*>(stg + stg_off<C>(row, col0 >> 3)) = q0;
+  *reinterpret_cast<uint4*>(stg + stg_off<C>(row, (col0 >> 3) + 1)) = q1;
+}
+// Tile rows (l * R + r) -> g[(tok0 + l * H) * C * R + c * R + r], tokens t0 + l < T only.
+template <int R, int C>
+__device__ __forceinline__ void copy_out(const uint8_t* stg, __nv_bfloat16* g, size_t tok0, int H, int T, int t0) {
+  constexpr int LT = kRows / R, CPT = C * R / 8;  // 16-byte chunks per token
+#pragma unroll
+  for (int i = 0; i < LT * CPT / 256; ++i) {
+    const int it = threadIdx.x + 256 * i, l = it / CPT, o = it % CPT;
+    if (t0 + l >= T) continue;
+    uint4 q;
+    if (R == 1) {
+      q = *reinterpret_cast<const uint4*>(stg + stg_off<C>(l, o));
+    } else {
+      uint32_t w[4];
+#pragma unroll
+      for (int e2 = 0; e2 < 4; ++e2) {
+        uint32_t pair = 0;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int e = o * 8 + e2 * 2 + hh, c = e / R, r = e % R, row = l * R + r;
+          const uint16_t v = *reinterpret_cast<const uint16_t*>(stg + stg_off<C>(row, c >> 3) + ((c & 7) << 1));
+          pair |= (uint32_t)v << (16 * hh);
+        }
+        w[e2] = pair;
+      }
+      q = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    *reinterpret_cast<uint4*>(g + (tok0 + (size_t)l * H) * C * R + (size_t)o * 8) = q;
   }
 }
 
