@@ -26,6 +26,10 @@ sys.path.insert(0, str(ROOT))
 
 from mamba_trainer_b200 import synthetic  # noqa: E402
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one tc_bwd_kernel launch, from the ncu captures
+# summarised under profiles/ (bytes per launch; None where no capture was taken).
+NCU_TRAFFIC_BYTES = {}
+
 METRIC = "mamba3_ssd_scan_fwd_bwd_throughput"
 UNIT = "Mtokens/s"
 
@@ -39,44 +43,78 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons sampled DURING the timed region: an NVML polling thread
+    (2 ms period, so even a few-millisecond region gets samples), nvidia-smi as a fallback."""
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, index: int):
-        self.proc = None
+        import threading
+        self.sm, self.mask, self.max = [], 0, None
+        self._stop = threading.Event()
+        self._thread = None
+        self._smi = None
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(index)],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(index).uuid)
+            try:
+                h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:
+                h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            get_reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+
+            def poll():
+                while not self._stop.is_set():
+                    try:
+                        self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                        self.mask |= int(get_reasons(h))
+                    except Exception:
+                        pass
+                    time.sleep(0.002)
+
+            self._thread = threading.Thread(target=poll, daemon=True)
+            self._thread.start()
+        except Exception:
+            q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                 "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+            try:
+                self._smi = subprocess.Popen(
+                    ["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "20", "-i", str(index)],
+                    stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            except OSError:
+                self._smi = None
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
-        time.sleep(0.06)
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, mx, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.splitlines():
-            f = [v.strip() for v in line.split(",")]
-            if len(f) < 6:
-                continue
+        reasons = []
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=1.0)
+            reasons = sorted(n for bit, n in self.REASONS.items() if self.mask & bit)
+        elif self._smi is not None:
+            time.sleep(0.05)
+            self._smi.terminate()
             try:
-                sm.append(float(f[0]))
-                mx = float(f[1])
-            except ValueError:
-                continue
-            for n, v in zip(names, f[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons)}
+                out, _ = self._smi.communicate(timeout=5)
+            except subprocess.TimeoutExpired:
+                self._smi.kill()
+                out, _ = self._smi.communicate()
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            found = set()
+            for line in out.splitlines():
+                f = [v.strip() for v in line.split(",")]
+                if len(f) < 6:
+                    continue
+                try:
+                    self.sm.append(float(f[0]))
+                    self.max = float(f[1])
+                except ValueError:
+                    continue
+                found |= {n for n, v in zip(names, f[2:6]) if v.lower().startswith("active")}
+            reasons = sorted(found)
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.max,
+                "reasons": reasons, "samples": len(self.sm)}
 
 
 def cpu_oracle_throughput(w, budget_s: float = 20.0):
@@ -162,7 +200,7 @@ def main():
     if not w.discretization.needs_lambda_projection():
         names.remove("lam")   # a constant lambda is not an input of the op
 
-    def step(src):
+    def step(src, mid=None):
         inp = ScanInputs.new(src["x"], src["b"], src["c"], src["dt"], src["a_log"], src.get("lam"))
         inp = inp.with_chunk_size(w.chunk).with_state_output(False).with_discretization(w.discretization)
         inp = inp.with_path(args.path)
@@ -170,6 +208,8 @@ def main():
             inp = inp.with_theta(src["theta"])
         inp = inp.with_skip(src["d_skip"])
         out = mamba3_scan(inp)
+        if mid is not None:
+            mid.record()
         grads = torch.autograd.grad(out.y, [src[n] for n in names if src[n].requires_grad], grad_outputs=src["dy"])
         return out.y, grads
 
@@ -185,9 +225,11 @@ def main():
     launches0 = ctx.launch_count()
     sampler = ClockSampler(local) if rank == 0 else None
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     ev0.record()
-    for _ in range(args.steps):
-        step(t)
+    for i in range(args.steps):
+        step(t, marks[i][0])       # event between the forward and the backward launches
+        marks[i][1].record()
     ev1.record()
     barrier()
     clocks = sampler.stop() if sampler else None
@@ -197,6 +239,10 @@ def main():
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_total = float(ms)
     ms_step = ms_total / args.steps
+    # per-launch durations of the two stripe kernels (the backward one dominates the step)
+    bwd_ms = sum(m0.elapsed_time(m1) for m0, m1 in marks) / args.steps
+    fwd_ms = (ev0.elapsed_time(marks[0][0]) + sum(marks[i][1].elapsed_time(marks[i + 1][0])
+                                                   for i in range(args.steps - 1))) / args.steps
     value = world * w.tokens / (ms_step * 1e-3) / 1e6
 
     # End to end: every step copies its inputs (and dy) from pinned host memory, runs
@@ -234,9 +280,17 @@ def main():
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
-        alg_bytes = w.bytes_per_token_head() * w.tokens * w.heads
-        achieved = alg_bytes / (ms_step * 1e-3) / 1e9
-        flops = w.flops_per_token_head() * w.tokens * w.heads
+        th = w.tokens * w.heads
+        alg_bytes = w.bytes_per_token_head() * th
+        es = w.elem_bytes()
+        inputs_b = es * (w.head_dim * w.rank + 2 * w.d_state * w.rank + (w.d_state // 2 if w.rotational else 0) + 2)
+        y_b = es * w.head_dim * w.rank
+        bwd_bytes = (2 * inputs_b + y_b) * th      # inputs re-read, dy read, every input gradient written
+        fwd_bytes = (inputs_b + y_b) * th
+        achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+        whole = alg_bytes / (ms_step * 1e-3) / 1e9
+        flops = w.flops_per_token_head() * th
+        traffic = NCU_TRAFFIC_BYTES.get(w.name)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
@@ -245,8 +299,14 @@ def main():
                        "head_dim": w.head_dim, "d_state": w.d_state, "rank": w.rank, "chunk": w.chunk,
                        "l2": "inputs larger than L2", "sharding": f"batch x heads, {world} shard(s), no collective"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_kind": peak_kind, "kernel": "whole fused op (forward + backward)",
-                         "frac_of_8TBs": achieved / 8000.0, "tflops": flops / (ms_step * 1e-3) / 1e12},
+                         "traffic": traffic, "peak_kind": peak_kind,
+                         "kernel": "tc_bwd_kernel (backward stripe kernel, with its two finalisation launches)",
+                         "ms_per_launch": bwd_ms,
+                         "forward": {"kernel": "tc_fwd_kernel", "ms_per_launch": fwd_ms,
+                                     "achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
+                                     "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak},
+                         "whole_step": {"achieved": whole, "frac": whole / peak, "frac_of_8TBs": whole / 8000.0,
+                                        "tflops": flops / (ms_step * 1e-3) / 1e12}},
             "clocks": clocks, "gpu_launches": int(launches),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         }
