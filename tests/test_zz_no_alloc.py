@@ -20,7 +20,8 @@ def _desc(t, w, want_state=True):
     return _ffi.ScanDesc(
         batch=w.batch, seq=w.seq, heads=w.heads, head_dim=w.head_dim, d_state=w.d_state, rank=w.rank,
         chunk=w.chunk, dtype=_ffi.F32 if w.dtype == torch.float32 else _ffi.BF16, discretization=2,
-        dynamics=1 if t["theta"] is not None else 0, want_state=int(want_state), path=_ffi.PATH_AUTO,
+        dynamics=1 if t["theta"] is not None else 0, want_state=int(want_state),
+        path=_ffi.PATH_GENERIC,   # the no-alloc entry runs the generic family: compare like with like
         x=p(t["x"]), b=p(t["b"]), c=p(t["c"]), dt=p(t["dt"]), lambda_=p(t["lam"]), theta=p(t["theta"]),
         a_log=p(t["a_log"]), d_skip=p(t["d_skip"]), h0=None, last_u0=None, angle0=None)
 
