@@ -390,32 +390,34 @@ __device__ __forceinline__ void stage_store16(uint8_t* stg, int row, int col0, c
   *reinterpret_cast<uint4*>(stg + stg_off<C>(row, (col0 >> 3) + 1)) = q1;
 }
 // Tile rows (l * R + r) -> g[(tok0 + l * H) * C * R + c * R + r], tokens t0 + l < T only.
+// An item is (time step, 8-column chunk): it reads that chunk from each of the R rank rows and
+// writes R consecutive 16-byte pieces, interleaving the ranks with byte permutes in registers.
 template <int R, int C>
 __device__ __forceinline__ void copy_out(const uint8_t* stg, __nv_bfloat16* g, size_t tok0, int H, int T, int t0) {
-  constexpr int LT = kRows / R, CPT = C * R / 8;  // 16-byte chunks per token
+  constexpr int LT = kRows / R, CPR = C / 8;  // chunks per row
 #pragma unroll
-  for (int i = 0; i < LT * CPT / 256; ++i) {
-    const int it = threadIdx.x + 256 * i, l = it / CPT, o = it % CPT;
+  for (int i = 0; i < LT * CPR / 256; ++i) {
+    const int it = threadIdx.x + 256 * i, l = it / CPR, c = it % CPR;
     if (t0 + l >= T) continue;
-    uint4 q;
-    if (R == 1) {
-      q = *reinterpret_cast<const uint4*>(stg + stg_off<C>(l, o));
-    } else {
-      uint32_t w[4];
+    uint32_t in[R][4];
 #pragma unroll
-      for (int e2 = 0; e2 < 4; ++e2) {
-        uint32_t pair = 0;
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          const int e = o * 8 + e2 * 2 + hh, c = e / R, r = e % R, row = l * R + r;
-          const uint16_t v = *reinterpret_cast<const uint16_t*>(stg + stg_off<C>(row, c >> 3) + ((c & 7) << 1));
-          pair |= (uint32_t)v << (16 * hh);
-        }
-        w[e2] = pair;
-      }
-      q = make_uint4(w[0], w[1], w[2], w[3]);
+    for (int r = 0; r < R; ++r) {
+      const uint4 q = *reinterpret_cast<const uint4*>(stg + stg_off<C>(l * R + r, c));
+      in[r][0] = q.x; in[r][1] = q.y; in[r][2] = q.z; in[r][3] = q.w;
     }
-    *reinterpret_cast<uint4*>(g + (tok0 + (size_t)l * H) * C * R + (size_t)o * 8) = q;
+    uint4* dst = reinterpret_cast<uint4*>(g + (tok0 + (size_t)l * H) * C * R + (size_t)c * 8 * R);
+    if (R == 1) {
+      dst[0] = make_uint4(in[0][0], in[0][1], in[0][2], in[0][3]);
+    } else {
+      uint32_t out[4 * R];
+#pragma unroll
+      for (int w = 0; w < 4 * R; ++w) {  // output word w holds elements (j, r), (j, r + 1)
+        const int j = (2 * w) / R, r = (2 * w) % R;
+        out[w] = __byte_perm(in[r][j >> 1], in[(r + 1) % R][j >> 1], (j & 1) ? 0x7632 : 0x5410);
+      }
+#pragma unroll
+      for (int o = 0; o < R; ++o) dst[o] = make_uint4(out[4 * o], out[4 * o + 1], out[4 * o + 2], out[4 * o + 3]);
+    }
   }
 }
 
