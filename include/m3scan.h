@@ -78,6 +78,12 @@ typedef struct {
   const float *h0;        /* SsmState::h      [batch, heads, head_dim, d_state] or NULL */
   const float *last_u0;   /* SsmState::last_u [batch, heads, head_dim, d_state] or NULL */
   const float *angle0;    /* SsmState::angle  [batch, heads, d_state/2] or NULL */
+  /* ssd_chunked, src/ssm/scan.rs:116-126: the caller supplies the log decay a = dt*A and the
+   * diagonal / off-diagonal weights g, w themselves, all [batch, seq, heads].  When a_raw is
+   * set (then g_raw and w_raw must be too) dt, lambda and a_log are not read, theta must be
+   * NULL, h0 alone is the boundary value carried in (last_u0 is not read) and no last_u is
+   * produced.  The generic kernel family serves this form. */
+  const void *a_raw, *g_raw, *w_raw;
 } m3_scan_desc;
 
 /* ScanOutput, src/ssm/scan.rs:446-452.  Caller-allocated.  The three state
@@ -113,6 +119,8 @@ typedef struct {
   void *dx, *db, *dc, *ddt, *dlambda, *dtheta;   /* desc.dtype */
   float *da_log, *dd_skip;                        /* [heads]    */
   float *dh0, *dlast_u0, *dangle0;                /* float      */
+  void *da_raw, *dg_raw, *dw_raw;                 /* desc.dtype; written instead of ddt / dlambda /
+                                                     da_log when the forward used a_raw, g_raw, w_raw */
 } m3_scan_grads;
 
 /* Library version string "major.minor.patch". */

@@ -27,7 +27,8 @@ class ScanDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "batch", "seq", "heads", "head_dim", "d_state", "rank", "chunk", "dtype",
         "discretization", "dynamics", "want_state", "path")] + [(n, C.c_void_p) for n in (
-        "x", "b", "c", "dt", "lambda_", "theta", "a_log", "d_skip", "h0", "last_u0", "angle0")]
+        "x", "b", "c", "dt", "lambda_", "theta", "a_log", "d_skip", "h0", "last_u0", "angle0",
+        "a_raw", "g_raw", "w_raw")]
 
 
 class ScanOut(C.Structure):
@@ -40,7 +41,8 @@ class ScanBwdIn(C.Structure):
 
 class ScanGrads(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in (
-        "dx", "db", "dc", "ddt", "dlambda", "dtheta", "da_log", "dd_skip", "dh0", "dlast_u0", "dangle0")]
+        "dx", "db", "dc", "ddt", "dlambda", "dtheta", "da_log", "dd_skip", "dh0", "dlast_u0", "dangle0",
+        "da_raw", "dg_raw", "dw_raw")]
 
 
 # name -> (restype, argtypes); every symbol include/m3scan.h declares.

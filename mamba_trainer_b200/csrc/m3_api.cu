@@ -66,10 +66,17 @@ int make_dims(m3_ctx* ctx, const m3_scan_desc& s, m3::Dims* out) {
   if (s.dynamics == M3_ROTATIONAL && (s.d_state % 2))
     return fail(ctx, M3_ERR_CONFIG, "rotational dynamics require an even d_state");
   if (s.rank > 64) return fail(ctx, M3_ERR_UNSUPPORTED, "rank %d > 64", s.rank);
-  if (!s.x || !s.b || !s.c || !s.dt || !s.a_log) return fail(ctx, M3_ERR_NULL, "x, b, c, dt and a_log are required");
-  if (s.discretization == M3_LEARNED_TRAPEZOID && !s.lambda) return fail(ctx, M3_ERR_NULL, "learned trapezoid needs lambda");
+  const bool raw = s.a_raw != nullptr;
+  if (raw) {
+    if (!s.g_raw || !s.w_raw) return fail(ctx, M3_ERR_NULL, "a_raw needs g_raw and w_raw");
+    if (s.dynamics != M3_REAL || s.theta) return fail(ctx, M3_ERR_CONFIG, "the a/g/w form has no rotation");
+    if (!s.x || !s.b || !s.c) return fail(ctx, M3_ERR_NULL, "x, b and c are required");
+  } else {
+    if (!s.x || !s.b || !s.c || !s.dt || !s.a_log) return fail(ctx, M3_ERR_NULL, "x, b, c, dt and a_log are required");
+    if (s.discretization == M3_LEARNED_TRAPEZOID && !s.lambda) return fail(ctx, M3_ERR_NULL, "learned trapezoid needs lambda");
+    if ((s.h0 == nullptr) != (s.last_u0 == nullptr)) return fail(ctx, M3_ERR_NULL, "a carried state needs both h and last_u");
+  }
   if (s.dynamics == M3_ROTATIONAL && !s.theta) return fail(ctx, M3_ERR_NULL, "rotational dynamics need theta");
-  if ((s.h0 == nullptr) != (s.last_u0 == nullptr)) return fail(ctx, M3_ERR_NULL, "a carried state needs both h and last_u");
   if ((size_t)s.batch * s.heads > 65535u) return fail(ctx, M3_ERR_UNSUPPORTED, "batch * heads > 65535");
   m3::Dims d;
   d.B = s.batch; d.T = s.seq; d.H = s.heads; d.P = s.head_dim; d.N = s.d_state; d.R = s.rank;
@@ -84,6 +91,7 @@ int make_dims(m3_ctx* ctx, const m3_scan_desc& s, m3::Dims* out) {
   d.NH = d.rot ? s.d_state / 2 : 0;
   d.disc = s.discretization;
   d.LR = L * s.rank;
+  d.raw = raw ? 1 : 0;
   *out = d;
   return M3_OK;
 }
@@ -263,6 +271,7 @@ size_t m3_scan_scratch_bytes(const m3_scan_desc* desc, int for_backward) {
   if (s.discretization == M3_LEARNED_TRAPEZOID) s.lambda = &dummy;
   if (s.dynamics == M3_ROTATIONAL) s.theta = &dummy;
   s.h0 = s.last_u0 = nullptr;
+  if (s.a_raw) s.a_raw = s.g_raw = s.w_raw = &dummy;
   if (make_dims(nullptr, s, &d) != M3_OK || d.T == 0) return 0;
   size_t n = m3::generic_ws_layout(d, nullptr, nullptr);
   if (for_backward) n += m3::generic_bwd_ws_layout(d, nullptr, nullptr);
@@ -297,7 +306,7 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
     return M3_OK;
   }
   if (!out->y) return fail(ctx, M3_ERR_NULL, "y is required");
-  const bool tc_ok = m3::tc_supported(*desc);
+  const bool tc_ok = m3::tc_supported(*desc) && !d.raw;
   if (desc->path == M3_PATH_TENSOR && !tc_ok)
     return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family does not take this shape");
   if (tc_ok && desc->path != M3_PATH_GENERIC) {

@@ -16,6 +16,7 @@ struct Dims {
   int disc;      // m3_discretization
   int rot;       // 1 when rotational
   int LR;        // L * R rows per chunk
+  int raw;       // 1: a, g, w come from the caller (the ssd_chunked form)
 };
 
 __device__ __forceinline__ float ldf(const float* p, size_t i) { return p[i]; }

@@ -51,11 +51,11 @@ static cudaError_t backward_t(cudaStream_t st, const Dims& d, const m3_scan_desc
   T* ddt = want(M3_GRAD_DT, g.ddt) ? static_cast<T*>(g.ddt) : nullptr;
   T* dlam = (want(M3_GRAD_LAMBDA, g.dlambda) && d.disc == M3_LEARNED_TRAPEZOID) ? static_cast<T*>(g.dlambda) : nullptr;
   T* dth = (want(M3_GRAD_THETA, g.dtheta) && d.rot) ? static_cast<T*>(g.dtheta) : nullptr;
-  float* dalog = want(M3_GRAD_A_LOG, g.da_log) ? g.da_log : nullptr;
+  float* dalog = (want(M3_GRAD_A_LOG, g.da_log) && !d.raw) ? g.da_log : nullptr;
   float* ddsk = (want(M3_GRAD_D_SKIP, g.dd_skip) && desc.d_skip) ? g.dd_skip : nullptr;
   const bool has_state = desc.h0 != nullptr;
   float* dh0 = (has_state && want(M3_GRAD_H0, g.dh0)) ? g.dh0 : nullptr;
-  float* dlu0 = (has_state && want(M3_GRAD_LAST_U0, g.dlast_u0)) ? g.dlast_u0 : nullptr;
+  float* dlu0 = (has_state && !d.raw && want(M3_GRAD_LAST_U0, g.dlast_u0)) ? g.dlast_u0 : nullptr;
   float* dang0 = (d.rot && desc.angle0 && want(M3_GRAD_ANGLE0, g.dangle0)) ? g.dangle0 : nullptr;
 
   const int BH = d.B * d.H, PN = d.P * d.N;
@@ -72,7 +72,7 @@ static cudaError_t backward_t(cudaStream_t st, const Dims& d, const m3_scan_desc
   kb_rows<T><<<dim3(tiles_l, d.C, BH), 256, sm_rows, st>>>(d, dy, ws, bw);
   kb_dhloc<T><<<dim3(tiles_pn, d.C, BH), 256, sizeof(float) * (kGemmSmemFloats + d.L), st>>>(d, dy, ws, bw);
   kb_state_pass_rev<<<dim3((PN + 255) / 256, BH), 256, 0, st>>>(d, in.dh, ws, bw);
-  kb_dcd<<<dim3(d.C + 1, BH), 256, 0, st>>>(d, desc.last_u0, ws, bw);
+  kb_dcd<<<dim3(d.C + 1, BH), 256, 0, st>>>(d, d.raw ? nullptr : desc.last_u0, ws, bw);
   const size_t sm_cols = sizeof(float) * ((size_t)kGemmSmemFloats + 3 * d.L + 64 + 64 * (size_t)d.LR);
   e = cudaFuncSetAttribute(kb_cols<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_cols);
   if (e != cudaSuccess) return e;
@@ -95,7 +95,9 @@ static cudaError_t backward_t(cudaStream_t st, const Dims& d, const m3_scan_desc
   }
   kb_dx<T><<<gchunk, 256, 0, st>>>(d, x, dy, desc.d_skip, bw, dx);
   const size_t total = (size_t)d.B * d.T * d.H;
-  kb_final<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(d, dt, lam, desc.a_log, bw, has_state ? 1 : 0, ddt, dlam);
+  kb_final<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+      d, dt, lam, desc.a_log, bw, (has_state && !d.raw) ? 1 : 0, ddt, dlam, static_cast<T*>(g.da_raw),
+      static_cast<T*>(g.dg_raw), static_cast<T*>(g.dw_raw));
   n += 2;
   if (dh0 || dlu0) {
     kb_state_grads<T><<<dim3((PN + 255) / 256, BH), 256, 0, st>>>(d, dt, lam, bw, dh0, dlu0);
@@ -120,10 +122,11 @@ cudaError_t finalize_scalars(cudaStream_t st, const Dims& d, const m3_scan_desc&
   if (desc.dtype == M3_BF16) {
     using T = __nv_bfloat16;
     kb_final<T><<<grid, 256, 0, st>>>(d, static_cast<const T*>(desc.dt), static_cast<const T*>(desc.lambda), desc.a_log,
-                                      bw, has_state, static_cast<T*>(ddt), static_cast<T*>(dlam));
+                                      bw, has_state, static_cast<T*>(ddt), static_cast<T*>(dlam), nullptr, nullptr, nullptr);
   } else {
     kb_final<float><<<grid, 256, 0, st>>>(d, static_cast<const float*>(desc.dt), static_cast<const float*>(desc.lambda),
-                                          desc.a_log, bw, has_state, static_cast<float*>(ddt), static_cast<float*>(dlam));
+                                          desc.a_log, bw, has_state, static_cast<float*>(ddt), static_cast<float*>(dlam),
+                                          nullptr, nullptr, nullptr);
   }
   uint64_t n = 1;
   if (dalog || ddsk) {

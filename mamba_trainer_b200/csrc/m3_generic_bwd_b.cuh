@@ -60,7 +60,7 @@ __global__ void kb_scalars(Dims d, const T* __restrict__ dt, GenericWs ws, Gener
   for (int l = threadIdx.x; l < L; l += blockDim.x) {
     const int t = k * L + l;
     bw.da[tb + l] = s_da[l];
-    if (t < d.T) part += s_da[l] * ldf(dt, ((size_t)b * d.T + t) * d.H + h);
+    if (t < d.T && !d.raw) part += s_da[l] * ldf(dt, ((size_t)b * d.T + t) * d.H + h);
   }
   part = block_sum_256(part, red);
   if (threadIdx.x == 0) bw.partA[(size_t)bh * d.C + k] = part;
@@ -230,7 +230,8 @@ __global__ void __launch_bounds__(256) kb_dx(Dims d, const T* __restrict__ x, co
 template <class T>
 __global__ void kb_final(Dims d, const T* __restrict__ dt, const T* __restrict__ lam,
                          const float* __restrict__ a_log, GenericBwdWs bw, int has_state,
-                         T* __restrict__ ddt, T* __restrict__ dlam) {
+                         T* __restrict__ ddt, T* __restrict__ dlam, T* __restrict__ da_raw, T* __restrict__ dg_raw,
+                         T* __restrict__ dw_raw) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t total = (size_t)d.B * d.T * d.H;
   if (i >= total) return;
@@ -239,6 +240,12 @@ __global__ void kb_final(Dims d, const T* __restrict__ dt, const T* __restrict__
   const int b = i / ((size_t)d.H * d.T);
   const int bh = b * d.H + h;
   const size_t o = (size_t)bh * d.Tp + t;
+  if (d.raw) {  // the ssd_chunked form: gradients of the caller's a, g, w as they are
+    if (da_raw) stf(da_raw, i, bw.da[o]);
+    if (dg_raw) stf(dg_raw, i, bw.dg[o]);
+    if (dw_raw) stf(dw_raw, i, bw.dw[o]);
+    return;
+  }
   const float A = -expf(a_log[h]);
   const float vdt = ldf(dt, i), vl = lambda_at(lam, d.disc, i);
   const float gw = bw.dg[o] + bw.dw[o];
@@ -264,7 +271,7 @@ __global__ void kb_state_grads(Dims d, const T* __restrict__ dt, const T* __rest
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= PN) return;
   const size_t i0 = ((size_t)b * d.T) * d.H + h;
-  const float first = (1.0f - lambda_at(lam, d.disc, i0)) * ldf(dt, i0);
+  const float first = d.raw ? 0.0f : (1.0f - lambda_at(lam, d.disc, i0)) * ldf(dt, i0);
   const float v = bw.dHs[((size_t)bh * (d.C + 1) + d.C) * PN + e];
   if (dh0) dh0[(size_t)bh * PN + e] = v;
   if (dlu0) dlu0[(size_t)bh * PN + e] = first * v;

@@ -48,7 +48,8 @@ template <class T>
 __global__ void k_prep(Dims d, const T* __restrict__ x, const T* __restrict__ bm,
                        const T* __restrict__ cm, const T* __restrict__ dt,
                        const T* __restrict__ lam, const T* __restrict__ theta,
-                       const float* __restrict__ a_log, GenericWs ws, float* angle_out) {
+                       const float* __restrict__ a_log, const T* __restrict__ a_raw, const T* __restrict__ g_raw,
+                       const T* __restrict__ w_raw, GenericWs ws, float* angle_out) {
   extern __shared__ float sm[];
   float* s_dt = sm;                 // [L + 1]
   float* s_lam = sm + d.L + 1;      // [L + 1]
@@ -58,7 +59,7 @@ __global__ void k_prep(Dims d, const T* __restrict__ x, const T* __restrict__ bm
   for (int l = threadIdx.x; l <= d.L; l += blockDim.x) {
     const int t = t0 + l;
     float vdt = 0.0f, vl = 1.0f;
-    if (t < d.T) {
+    if (t < d.T && !d.raw) {
       const size_t i = ((size_t)b * d.T + t) * d.H + h;
       vdt = ldf(dt, i);
       vl = lambda_at(lam, d.disc, i);
@@ -68,12 +69,17 @@ __global__ void k_prep(Dims d, const T* __restrict__ x, const T* __restrict__ bm
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    const float A = -expf(a_log[h]);
+    const float A = d.raw ? 0.0f : -expf(a_log[h]);
     float run = 0.0f;
     for (int l = 0; l < d.L; ++l) {
       const int t = t0 + l;
       float gv = 0.0f, wv = 0.0f, av = 0.0f;
-      if (t < d.T) {
+      if (t < d.T && d.raw) {  // scan.rs:116-126: the caller's own a, g, w
+        const size_t i = ((size_t)b * d.T + t) * d.H + h;
+        av = ldf(a_raw, i);
+        gv = ldf(g_raw, i);
+        wv = ldf(w_raw, i);
+      } else if (t < d.T) {
         av = s_dt[l] * A;
         gv = s_lam[l] * s_dt[l];
         const float f = (t + 1 < d.T) ? (1.0f - s_lam[l + 1]) * s_dt[l + 1] : 0.0f;
@@ -200,9 +206,11 @@ __global__ void k_state_pass(Dims d, const T* __restrict__ dt, const T* __restri
   const int lane = threadIdx.x & 31;
   float carry = 0.0f;
   if (live && h0) {
-    const size_t i0 = ((size_t)b * d.T) * d.H + h;
-    const float first = (1.0f - lambda_at(lam, d.disc, i0)) * ldf(dt, i0);
-    carry = h0[(size_t)bh * PN + e] + first * lu0[(size_t)bh * PN + e];
+    carry = h0[(size_t)bh * PN + e];
+    if (lu0) {
+      const size_t i0 = ((size_t)b * d.T) * d.H + h;
+      carry += (1.0f - lambda_at(lam, d.disc, i0)) * ldf(dt, i0) * lu0[(size_t)bh * PN + e];
+    }
   }
   float* Hs = ws.Hs + (size_t)bh * (d.C + 1) * PN;
   for (int k0 = 0; k0 < d.C; k0 += 32) {
@@ -364,11 +372,12 @@ static cudaError_t forward_t(cudaStream_t st, const Dims& d, const m3_scan_desc&
     n += 2;
   }
   k_prep<T><<<gchunk, 256, sizeof(float) * 2 * (d.L + 1), st>>>(
-      d, x, bm, cm, dt, lam, th, desc.a_log, ws, desc.want_state ? out.angle : nullptr);
+      d, x, bm, cm, dt, lam, th, desc.a_log, static_cast<const T*>(desc.a_raw), static_cast<const T*>(desc.g_raw),
+      static_cast<const T*>(desc.w_raw), ws, desc.want_state ? out.angle : nullptr);
   const int tiles = ((d.P + 63) / 64) * ((d.N + 63) / 64);
   k_chunk_state<<<dim3(tiles, d.C, BH), 256, sizeof(float) * (kGemmSmemFloats + d.L), st>>>(d, ws);
   k_state_pass<T><<<dim3((PN + 255) / 256, BH), 256, 0, st>>>(
-      d, dt, lam, desc.h0, desc.last_u0, ws, desc.want_state ? out.h : nullptr);
+      d, dt, lam, desc.h0, d.raw ? nullptr : desc.last_u0, ws, desc.want_state ? out.h : nullptr);
   const size_t smem = chunk_out_smem(d);
   cudaError_t e = cudaFuncSetAttribute(k_chunk_out<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
@@ -376,7 +385,7 @@ static cudaError_t forward_t(cudaStream_t st, const Dims& d, const m3_scan_desc&
   k_chunk_out<T><<<dim3((d.L + TL - 1) / TL, d.C, BH), 256, smem, st>>>(
       d, x, desc.d_skip, ws, static_cast<T*>(out.y));
   n += 4;
-  if (desc.want_state && out.last_u) {
+  if (desc.want_state && out.last_u && !d.raw) {
     k_last_u<<<dim3((PN + 255) / 256, BH), 256, 0, st>>>(d, ws, out.last_u);
     n += 1;
   }

@@ -242,6 +242,101 @@ class _FusedScan(torch.autograd.Function):
         return (None,) + tuple(grads.get(n) for n in names)
 
 
+class _FusedSsd(torch.autograd.Function):
+    """`ssd_chunked` as one node: the caller's own a, g, w (src/ssm/scan.rs:116-291)."""
+
+    @staticmethod
+    def forward(fctx, opts, x, b, c, a, g, w, h0):
+        ctx = Context.for_device(x.device)
+        B, T, H, P = x.shape
+        N = b.shape[3]
+        desc = _ffi.ScanDesc(
+            batch=B, seq=T, heads=H, head_dim=P, d_state=N, rank=1, chunk=int(opts["chunk"]),
+            dtype=_DTYPES[x.dtype], discretization=int(Discretization.LearnedTrapezoid), dynamics=0,
+            want_state=1 if opts["want_state"] else 0, path=_ffi.PATH_GENERIC,
+            x=_ptr(x), b=_ptr(b), c=_ptr(c), h0=_ptr(h0), a_raw=_ptr(a), g_raw=_ptr(g), w_raw=_ptr(w))
+        y = torch.empty_like(x)
+        h = torch.empty((B, H, P, N), device=x.device, dtype=torch.float32) if opts["want_state"] else None
+        out = _ffi.ScanOut(y=_ptr(y), h=_ptr(h))
+        track = any(fctx.needs_input_grad)
+        saved = C.c_void_p()
+        ctx.check(ctx.lib.m3_scan_forward(ctx.handle, C.byref(desc), C.byref(out),
+                                          C.byref(saved) if track else None))
+        if track:
+            fctx.m3 = ctx
+            fctx.saved = _Saved(ctx, saved)
+            tensors = (x, b, c, a, g, w, h0)
+            fctx.save_for_backward(*[t for t in tensors if t is not None])
+            fctx.present = [t is not None for t in tensors]
+            fctx.set_materialize_grads(False)
+        return (y, h) if h is not None else (y,)
+
+    @staticmethod
+    def backward(fctx, dy, dh=None):
+        ctx = fctx.m3
+        ctx.bind_current_stream()
+        it = iter(fctx.saved_tensors)
+        x, b, c, a, g, w, h0 = (next(it) if p else None for p in fctx.present)
+        if dy is None:
+            dy = torch.zeros_like(x)
+        need = fctx.needs_input_grad[1:]
+        tensors = (x, b, c, a, g, w, h0)
+        grads = [torch.empty_like(t) if (t is not None and need[i]) else None for i, t in enumerate(tensors)]
+        mask = sum(bit for bit, gr in zip((_ffi.GRAD_X, _ffi.GRAD_B, _ffi.GRAD_C, _ffi.GRAD_DT, _ffi.GRAD_DT,
+                                           _ffi.GRAD_DT, _ffi.GRAD_H0), grads) if gr is not None)
+        dy = dy.contiguous()
+        dh = dh.contiguous() if dh is not None else None
+        bin_ = _ffi.ScanBwdIn(dy=_ptr(dy), dh=_ptr(dh))
+        gout = _ffi.ScanGrads(dx=_ptr(grads[0]), db=_ptr(grads[1]), dc=_ptr(grads[2]), da_raw=_ptr(grads[3]),
+                              dg_raw=_ptr(grads[4]), dw_raw=_ptr(grads[5]), dh0=_ptr(grads[6]))
+        ctx.check(ctx.lib.m3_scan_backward(ctx.handle, fctx.saved.handle, C.byref(bin_), C.c_uint32(mask | 0xFF),
+                                           C.byref(gout)))
+        return (None,) + tuple(grads)
+
+
+def ssd_chunked(x, b, c, a, g, w, initial_state=None, chunk_size: int = 64, want_state: bool = True):
+    """The core one-channel scan with caller-supplied weights (src/ssm/scan.rs:116-126).
+
+    x [B,T,H,P]; b, c [B,T,H,N]; a (log decay per step), g (diagonal weight), w (off-diagonal
+    weight) [B,T,H]; initial_state [B,H,P,N].  Returns (y [B,T,H,P], state [B,H,P,N] or None).
+    """
+    _expect_rank(x, 4)                                   # scan.rs:127-128
+    _expect_rank(b, 4)
+    B, T, H, P = x.shape
+    N = b.shape[3]
+    if x.dtype not in _DTYPES:
+        raise UnsupportedError(f"element type {x.dtype}: float32 and bfloat16 are served")
+    if tuple(b.shape) != (B, T, H, N) or tuple(c.shape) != (B, T, H, N):
+        raise ShapeError(f"b {tuple(b.shape)} / c {tuple(c.shape)} do not match x {tuple(x.shape)}")
+    for name, t in (("a", a), ("g", g), ("w", w)):
+        if tuple(t.shape) != (B, T, H):
+            raise ShapeError(f"{name} has shape {tuple(t.shape)}, expected {(B, T, H)}")
+    if initial_state is not None and tuple(initial_state.shape) != (B, H, P, N):
+        raise ShapeError(f"initial_state has shape {tuple(initial_state.shape)}, expected {(B, H, P, N)}")
+    if T == 0:                                           # scan.rs:134-144
+        st = None
+        if want_state:
+            st = initial_state if initial_state is not None else torch.zeros((B, H, P, N), device=x.device)
+        return x, st
+    el = x.dtype
+    big = lambda t: t.to(el).contiguous()
+    h0 = initial_state.to(torch.float32).contiguous() if initial_state is not None else None
+    outs = _FusedSsd.apply({"chunk": chunk_size, "want_state": bool(want_state)},
+                           x.contiguous(), big(b), big(c), big(a), big(g), big(w), h0)
+    return outs[0], (outs[1] if want_state else None)
+
+
+def shift_left(x: torch.Tensor, axis: int) -> torch.Tensor:
+    """Shift along `axis` towards smaller indices, zero-filling the last slot (scan.rs:64-75)."""
+    n = x.shape[axis]
+    if n == 0:
+        return x
+    pad = torch.zeros_like(x.narrow(axis, 0, 1))
+    if n == 1:
+        return pad
+    return torch.cat([x.narrow(axis, 1, n - 1), pad], dim=axis)
+
+
 def _expect_rank(t: torch.Tensor, rank: int) -> None:
     if t.dim() != rank:
         raise RankError(rank, t.dim(), t.shape)

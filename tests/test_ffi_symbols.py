@@ -28,11 +28,11 @@ def test_library_builds_loads_and_exports_every_symbol():
 
 
 def test_struct_layouts_match_the_header():
-    # 12 int32 then 11 pointers; 4, 4 and 11 pointers.
-    assert ctypes.sizeof(_ffi.ScanDesc) == 12 * 4 + 11 * 8
+    # 12 int32 then 14 pointers; 4, 4 and 14 pointers.
+    assert ctypes.sizeof(_ffi.ScanDesc) == 12 * 4 + 14 * 8
     assert ctypes.sizeof(_ffi.ScanOut) == 4 * 8
     assert ctypes.sizeof(_ffi.ScanBwdIn) == 4 * 8
-    assert ctypes.sizeof(_ffi.ScanGrads) == 11 * 8
+    assert ctypes.sizeof(_ffi.ScanGrads) == 14 * 8
 
 
 def test_scratch_size_query_needs_no_gpu():

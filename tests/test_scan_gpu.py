@@ -289,3 +289,40 @@ def test_tensor_core_backward(rank, rot, seq, state, disc):
           "last_u": torch.randn(w.batch, w.heads, 64, 128, generator=g) * 0.1,
           "angle": torch.randn(w.batch, w.heads, 64, generator=g) * 0.1 if rot else None}
     compare_all(t, w.chunk, check_bf16, True, ds, discretization=disc, path=2)
+
+
+# ---- ssd_chunked with the caller's own a, g, w (the reference's direct entry) ------------------------
+
+def test_ssd_chunked_entry_matches_golden_and_oracle():
+    """The reference port's golden vectors (tests/golden) through the CUDA path, values and all six
+    gradients; then a carried state and a state gradient against the oracle."""
+    from pathlib import Path
+    from mamba_trainer_b200.ssm import ssd_chunked, shift_left
+    from oracle import m3_oracle as O
+    gold = Path(__file__).resolve().parent / "golden"
+    for name in ("ssd_chunked_even", "ssd_chunked_ragged", "ssd_chunked_one_chunk"):
+        z = np.load(gold / f"{name}.npz")
+        leaves = [torch.tensor(z[k], dtype=torch.float32, device="cuda", requires_grad=True) for k in "xbcagw"]
+        y, st = ssd_chunked(*leaves, None, int(z["chunk"]), True)
+        check_f32("y " + name, y, torch.tensor(z["y"]))
+        grads = torch.autograd.grad((y * torch.tensor(z["dy"], dtype=torch.float32, device="cuda")).sum(), leaves)
+        for k, gr in zip("xbcagw", grads):
+            check_f32(f"d{k} {name}", gr, torch.tensor(z[f"d{k}"]))
+    # w built the reference's way: g + shift_left((1 - lambda) dt)   (tests/ssm.rs:176-184)
+    case = Case(2, 12, 2, 3, 4)
+    f = lambda v: torch.tensor(v, dtype=torch.float64)
+    dt, lam = f(case.dt), f(case.lam)
+    a, g = dt * f(case.a_head).view(1, 1, -1), lam * dt
+    w = g + shift_left((1 - lam) * dt, 1)
+    h0 = torch.randn(2, 2, 3, 4, dtype=torch.float64, generator=torch.Generator().manual_seed(2))
+    dh = torch.randn(2, 2, 3, 4, dtype=torch.float64, generator=torch.Generator().manual_seed(3))
+    cpu = [t.clone().requires_grad_(True) for t in (f(case.x), f(case.b), f(case.c), a, g, w, h0)]
+    ey, est = O.ssd_chunked(*cpu[:6], cpu[6], 4, True)
+    eg = torch.autograd.grad(ey.sum() + (est * dh).sum(), cpu)
+    dev = [t.detach().float().cuda().requires_grad_(True) for t in cpu]
+    y, st = ssd_chunked(*dev[:6], dev[6], 4, True)
+    gg = torch.autograd.grad(y.sum() + (st * dh.float().cuda()).sum(), dev)
+    check_f32("y", y, ey.detach())
+    check_f32("state", st, est.detach())
+    for n, a_, e_ in zip(("x", "b", "c", "a", "g", "w", "h0"), gg, eg):
+        check_f32("d" + n, a_, e_)
