@@ -109,9 +109,6 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
     const size_t tok0 = ((size_t)b * T + t0) * H + h;
     const bool last_tile = (k == ntiles - 1);
     const int l_end = T - 1 - t0;  // row of the final token when last_tile
-    if (k > 0)  // warm L2 with the tile after this one
-      prefetch_tile_l2<R, ROT>(p.b, p.c, p.x, p.dy, p.theta, p.ckpt_h + ((size_t)bh * ntiles + k - 1) * kN * kP,
-                               tok0 - (size_t)LT * H, H, T, t0 - LT);
     // ---- 1. every global load of the tile in flight, then scalars and angles ---------------------
     RawBC<R, ROT> raw_bc;
     RawPX<R> raw_x, raw_dy;
@@ -150,6 +147,11 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
     tc_fence_before();
     __syncthreads();
     TICK(2);
+#ifndef M3_NO_L2_PREFETCH
+    if (k > 0)  // warm L2 with the tile after this one (behind this tile's own loads)
+      prefetch_tile_l2<R, ROT>(p.b, p.c, p.x, p.dy, p.theta, p.ckpt_h + ((size_t)bh * ntiles + k - 1) * kN * kP,
+                               tok0 - (size_t)LT * H, H, T, t0 - LT);
+#endif
     // ---- 4. MMA phase A ------------------------------------------------------------------------
     if (tid == 0) {
       tc_fence_after();
@@ -304,7 +306,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
       issue_theta<R>(th2, p.theta, tok0, H, T, t0);
       commit_theta<R>(th2, sPhi);
       __syncthreads();
-      tile_angles_smem<R>(sPhi, s_q, s_carry, ts.dt, T, t0, nullptr);
+      tile_angles_smem<R, true>(sPhi, s_q, s_carry, ts.dt, T, t0, nullptr);  // (cos, sin) table this time
       __syncthreads();
     }
     TICK(6);
@@ -402,8 +404,9 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               dphi[16 * mc + j] += g1[j] * o2[j] - g2[j] * o1[j];
-              float sn, cs;
-              sincos_poly(sPhi[phi_idx(rl, m0 + j)], &sn, &cs);
+              const uint32_t cw = __float_as_uint(sPhi[phi_idx(rl, m0 + j)]);
+              const float2 csn = __half22float2(*reinterpret_cast<const __half2*>(&cw));
+              const float cs = csn.x, sn = csn.y;
               const float u1 = g1[j] * cs - g2[j] * sn, u2 = g1[j] * sn + g2[j] * cs;
               g1[j] = u1; g2[j] = u2;
             }
@@ -412,15 +415,20 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) stage_store16<kN>(stg, row, gcol(q4), g[q4]);
       };
+      TICK(11);
       finish(gq, sB, sXw, true);     // sigma_w X~ and exp(acum) dY~ are spent: 32 KB to stage dB
+      TICK(12);
       tmem_wait_ld();
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) tmem_ld_fence(gc[q4]);
       finish(gc, sC, sDG, false);    // dG is spent: its buffer stages dC
+      TICK(13);
       __syncthreads();
+      TICK(14);
       if (p.dx) copy_out<R, kP>(sHS, p.dx, tok0, H, T, t0);
       if (p.db) copy_out<R, kN>(sXw, p.db, tok0, H, T, t0);
       if (p.dc) copy_out<R, kN>(sDG, p.dc, tok0, H, T, t0);
+      TICK(15);
       __syncthreads();
       if (ROT) {
         // d phi of a time step sums its R rows (adjacent lanes); it then overwrites dG's buffer,

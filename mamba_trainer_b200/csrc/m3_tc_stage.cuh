@@ -2,6 +2,8 @@
 // cumulative angle of a tile, and staging of rotated / de-interleaved bf16 operands.
 // 256 threads per CTA; LT = 128 / R time steps per tile; head_dim 64, d_state 128.
 #pragma once
+#include <cuda_fp16.h>
+
 #include "m3_tc_common.cuh"
 
 namespace m3tc {
@@ -329,7 +331,9 @@ __device__ __forceinline__ void commit_theta(const RawTheta<R>& raw, float* sPhi
 
 // As tile_angles, but theta comes from the raw rows commit_theta left in the angle buffer
 // (they are consumed before any angle is written: one __syncthreads separates the passes).
-template <int R>
+// With TABLE the buffer receives half2(cos phi, sin phi) words instead of the angles, for readers
+// that need the rotation many times per angle.
+template <int R, bool TABLE = false>
 __device__ __forceinline__ float tile_angles_smem(float* sPhi, float* s_q, const float* carry, const float* s_dt,
                                                   int T, int t0, float* angle_out_bh) {
   constexpr int LT = kRows / R, LQ = LT / 4;
@@ -351,7 +355,14 @@ __device__ __forceinline__ float tile_angles_smem(float* sPhi, float* s_q, const
   for (int i = 0; i < LQ; ++i) {
     const int l = q * LQ + i;
     const float wv = wrap2pi(loc[i] + off);
-    sPhi[phi_idx(l, m)] = wv;
+    if (TABLE) {
+      float sn, cs;
+      sincos_poly(wv, &sn, &cs);
+      const __half2 h2 = __floats2half2_rn(cs, sn);
+      sPhi[phi_idx(l, m)] = __uint_as_float(*reinterpret_cast<const uint32_t*>(&h2));
+    } else {
+      sPhi[phi_idx(l, m)] = wv;
+    }
     if (angle_out_bh && t0 + l == T - 1) angle_out_bh[m] = wv;
   }
   return wrap2pi(off + s_q[3 * 64 + m]);
@@ -390,34 +401,33 @@ __device__ __forceinline__ void stage_store16(uint8_t* stg, int row, int col0, c
   *reinterpret_cast<uint4*>(stg + stg_off<C>(row, (col0 >> 3) + 1)) = q1;
 }
 // Tile rows (l * R + r) -> g[(tok0 + l * H) * C * R + c * R + r], tokens t0 + l < T only.
-// An item is (time step, 8-column chunk): it reads that chunk from each of the R rank rows and
-// writes R consecutive 16-byte pieces, interleaving the ranks with byte permutes in registers.
+// One item per 16 output bytes, consecutive items -> consecutive addresses, so every store
+// instruction of a warp writes 512 contiguous bytes whatever the rank.  The ranks are interleaved
+// in registers: output word w of a token's chunk holds elements (j, r), (j, r + 1) with
+// j = 2w / R, r = 2w % R, i.e. one 16-bit half from each of two neighbouring rank rows.
 template <int R, int C>
 __device__ __forceinline__ void copy_out(const uint8_t* stg, __nv_bfloat16* g, size_t tok0, int H, int T, int t0) {
-  constexpr int LT = kRows / R, CPR = C / 8;  // chunks per row
+  constexpr int LT = kRows / R, CPR = C / 8;  // source chunks per row
 #pragma unroll
-  for (int i = 0; i < LT * CPR / 256; ++i) {
-    const int it = threadIdx.x + 256 * i, l = it / CPR, c = it % CPR;
+  for (int i = 0; i < LT * CPR * R / 256; ++i) {
+    const int it = threadIdx.x + 256 * i;
+    const int o = it % R, c = (it / R) % CPR, l = it / (R * CPR);
     if (t0 + l >= T) continue;
-    uint32_t in[R][4];
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const uint4 q = *reinterpret_cast<const uint4*>(stg + stg_off<C>(l * R + r, c));
-      in[r][0] = q.x; in[r][1] = q.y; in[r][2] = q.z; in[r][3] = q.w;
-    }
-    uint4* dst = reinterpret_cast<uint4*>(g + (tok0 + (size_t)l * H) * C * R + (size_t)c * 8 * R);
+    uint4 q;
     if (R == 1) {
-      dst[0] = make_uint4(in[0][0], in[0][1], in[0][2], in[0][3]);
+      q = *reinterpret_cast<const uint4*>(stg + stg_off<C>(l, c));
     } else {
-      uint32_t out[4 * R];
+      uint32_t w4[4];
 #pragma unroll
-      for (int w = 0; w < 4 * R; ++w) {  // output word w holds elements (j, r), (j, r + 1)
-        const int j = (2 * w) / R, r = (2 * w) % R;
-        out[w] = __byte_perm(in[r][j >> 1], in[(r + 1) % R][j >> 1], (j & 1) ? 0x7632 : 0x5410);
+      for (int wi = 0; wi < 4; ++wi) {
+        const int w = 4 * o + wi, j = (2 * w) / R, r = (2 * w) % R;
+        const uint32_t lo = *reinterpret_cast<const uint32_t*>(stg + stg_off<C>(l * R + r, c) + ((j >> 1) << 2));
+        const uint32_t hi = *reinterpret_cast<const uint32_t*>(stg + stg_off<C>(l * R + r + 1, c) + ((j >> 1) << 2));
+        w4[wi] = __byte_perm(lo, hi, (j & 1) ? 0x7632 : 0x5410);
       }
-#pragma unroll
-      for (int o = 0; o < R; ++o) dst[o] = make_uint4(out[4 * o], out[4 * o + 1], out[4 * o + 2], out[4 * o + 3]);
+      q = make_uint4(w4[0], w4[1], w4[2], w4[3]);
     }
+    *reinterpret_cast<uint4*>(g + (tok0 + (size_t)l * H) * C * R + (size_t)c * 8 * R + (size_t)o * 8) = q;
   }
 }
 
