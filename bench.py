@@ -245,24 +245,18 @@ def main():
                                                    for i in range(args.steps - 1))) / args.steps
     value = world * w.tokens / (ms_step * 1e-3) / 1e6
 
-    # End to end: every step copies its inputs (and dy) from pinned host memory, runs
-    # forward + backward, and reads y and every input gradient back to pinned host memory.
+    # End to end: every step starts from pinned HOST tensors (inputs and dy), runs forward +
+    # backward through the package's host pipeline (batch slices; copies overlap the kernels) and
+    # ends with y and every input gradient back in pinned host memory.
+    from mamba_trainer_b200.host_pipeline import HostScanPipeline
     big = [n for n in ("x", "b", "c", "dt", "lam", "theta", "dy") if t.get(n) is not None]
     host = {n: t[n].detach().cpu().pin_memory() for n in big}
-    devbuf = {n: torch.empty_like(t[n].detach()) for n in big}
-    y0, g0 = step(t)
-    host_out = [torch.empty(v.shape, dtype=v.dtype).pin_memory() for v in (y0, *g0)]
-    h2d = sum(v.numel() * v.element_size() for v in host.values())
-    d2h = sum(v.numel() * v.element_size() for v in host_out)
+    params = {"a_log": t["a_log"], "d_skip": t["d_skip"]}
+    pipe = HostScanPipeline(host, w.chunk, w.discretization, dev, slices=4)
+    h2d, d2h = pipe.h2d_bytes, pipe.d2h_bytes
 
     def e2e_step():
-        src = dict(t)
-        for n in big:
-            devbuf[n].copy_(host[n], non_blocking=True)
-            src[n] = devbuf[n].detach().requires_grad_(n != "dy")
-        y, grads = step(src)
-        for dst, v in zip(host_out, (y, *grads)):
-            dst.copy_(v, non_blocking=True)
+        pipe.run(host, params)
 
     for _ in range(3):
         e2e_step()
