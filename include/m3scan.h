@@ -162,6 +162,23 @@ int m3_scan_backward(m3_ctx *ctx, const m3_saved *saved, const m3_scan_bwd_in *i
 
 int m3_saved_free(m3_ctx *ctx, m3_saved *saved);
 
+/* mamba3_step, src/ssm/scan.rs:649-712: one decoding step.  Shapes are ScanInputs' with seq = 1
+ * and no time axis: x [batch, heads, head_dim, rank]; b, c [batch, heads, d_state, rank]; dt,
+ * lambda [batch, heads]; theta [batch, heads, d_state/2]; the state is read from (h, last_u,
+ * angle) and the new one written to m3_step_out (distinct buffers: inputs are never written). */
+typedef struct {
+  int32_t batch, heads, head_dim, d_state, rank;
+  int32_t dtype, discretization, dynamics;
+  const void *x, *b, *c, *dt, *lambda, *theta;
+  const float *a_log, *d_skip;
+  const float *h, *last_u, *angle;   /* angle may be NULL (zero) */
+} m3_step_desc;
+typedef struct {
+  void *y;                            /* [batch, heads, head_dim, rank], desc.dtype */
+  float *h, *last_u, *angle;          /* the state after the step */
+} m3_step_out;
+int m3_step_forward(m3_ctx *ctx, const m3_step_desc *desc, const m3_step_out *out);
+
 /* No counterpart in the reference.  The forward scan (inference form: no saved
  * context) for hosts that must not allocate device memory while they run - a server
  * that gave the whole GPU to its own arena at start-up, a latency-bound decode loop

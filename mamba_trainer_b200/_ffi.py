@@ -45,6 +45,16 @@ class ScanGrads(C.Structure):
         "da_raw", "dg_raw", "dw_raw")]
 
 
+class StepDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("batch", "heads", "head_dim", "d_state", "rank", "dtype",
+                                         "discretization", "dynamics")] + [(n, C.c_void_p) for n in (
+        "x", "b", "c", "dt", "lambda_", "theta", "a_log", "d_skip", "h", "last_u", "angle")]
+
+
+class StepOut(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("y", "h", "last_u", "angle")]
+
+
 # name -> (restype, argtypes); every symbol include/m3scan.h declares.
 SYMBOLS = {
     "m3_version": (C.c_char_p, []),
@@ -62,6 +72,7 @@ SYMBOLS = {
     "m3_scan_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(ScanBwdIn), C.c_uint32, C.POINTER(ScanGrads)]),
     "m3_saved_free": (C.c_int, [C.c_void_p, C.c_void_p]),
     "m3_scan_scratch_bytes": (C.c_size_t, [C.POINTER(ScanDesc), C.c_int]),
+    "m3_step_forward": (C.c_int, [C.c_void_p, C.POINTER(StepDesc), C.POINTER(StepOut)]),
     "m3_scan_forward_noalloc": (C.c_int, [C.c_void_p, C.POINTER(ScanDesc), C.POINTER(ScanOut)]),
 }
 

@@ -326,6 +326,44 @@ def ssd_chunked(x, b, c, a, g, w, initial_state=None, chunk_size: int = 64, want
     return outs[0], (outs[1] if want_state else None)
 
 
+def mamba3_step(x, b, c, dt, lambda_, a_log, theta, d_skip, state: SsmState,
+                discretization: Discretization = Discretization.LearnedTrapezoid):
+    """One decoding step (src/ssm/scan.rs:649-712), as a single launch; not differentiable.
+
+    x [B,H,P,R]; b, c [B,H,N,R]; dt, lambda_ [B,H]; theta [B,H,N/2] or None; returns (y, SsmState).
+    """
+    _expect_rank(x, 4)
+    B, H, P, R = x.shape
+    N = b.shape[2]
+    if x.dtype not in _DTYPES:
+        raise UnsupportedError(f"element type {x.dtype}: float32 and bfloat16 are served")
+    if tuple(b.shape) != (B, H, N, R) or tuple(c.shape) != (B, H, N, R):
+        raise ShapeError(f"b {tuple(b.shape)} / c {tuple(c.shape)} do not match x {tuple(x.shape)}")
+    if theta is not None and N % 2:
+        raise ConfigError("rotational dynamics require an even d_state")
+    disc = Discretization(discretization)
+    if disc is Discretization.LearnedTrapezoid and lambda_ is None:
+        raise NullError("LearnedTrapezoid needs a lambda tensor")
+    ctx = Context.for_device(x.device)
+    el = x.dtype
+    big = lambda t: None if t is None else t.detach().to(el).contiguous()
+    f32 = lambda t: None if t is None else t.detach().to(torch.float32).contiguous()
+    xs, bs, cs, dts, lams, ths = big(x), big(b), big(c), big(dt), big(lambda_), big(theta)
+    al, dk, h, lu = f32(a_log), f32(d_skip), f32(state.h), f32(state.last_u)
+    ang = f32(state.angle) if (theta is not None and state.angle is not None) else None
+    y = torch.empty_like(xs)
+    h2, lu2 = torch.empty_like(h), torch.empty_like(lu)
+    ang2 = torch.empty((B, H, N // 2), device=x.device, dtype=torch.float32) if theta is not None else None
+    desc = _ffi.StepDesc(batch=B, heads=H, head_dim=P, d_state=N, rank=R, dtype=_DTYPES[el],
+                         discretization=int(disc), dynamics=1 if theta is not None else 0,
+                         x=_ptr(xs), b=_ptr(bs), c=_ptr(cs), dt=_ptr(dts),
+                         lambda_=_ptr(lams) if disc is Discretization.LearnedTrapezoid else None, theta=_ptr(ths),
+                         a_log=_ptr(al), d_skip=_ptr(dk), h=_ptr(h), last_u=_ptr(lu), angle=_ptr(ang))
+    out = _ffi.StepOut(y=_ptr(y), h=_ptr(h2), last_u=_ptr(lu2), angle=_ptr(ang2))
+    ctx.check(ctx.lib.m3_step_forward(ctx.handle, C.byref(desc), C.byref(out)))
+    return y, SsmState(h2, lu2, ang2)
+
+
 def shift_left(x: torch.Tensor, axis: int) -> torch.Tensor:
     """Shift along `axis` towards smaller indices, zero-filling the last slot (scan.rs:64-75)."""
     n = x.shape[axis]

@@ -345,3 +345,34 @@ def test_host_pipeline_matches_one_call():
         assert torch.equal(out["d" + n], g[n].cpu()), n
     check_f32("da_log", out["da_log"], g["a_log"].cpu())     # summed over slices in a different order
     check_f32("dd_skip", out["dd_skip"], g["d_skip"].cpu())
+
+
+# ---- decode step ------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("rank,dtype", [(1, torch.float32), (2, torch.float32), (4, torch.bfloat16)])
+def test_step_matches_the_chunked_scan(rank, dtype):
+    """tests/ssm.rs:312-380: mamba3_step token by token equals the scan (rotation + D skip), and the
+    state it ends in equals the scan's."""
+    from mamba_trainer_b200.ssm import mamba3_step
+    g = torch.Generator().manual_seed(rank)
+    B, T, H, P, N = 2, 9, 2, (3 if dtype == torch.float32 else 64), (4 if dtype == torch.float32 else 128)
+    r = lambda *s: torch.randn(*s, generator=g)
+    u = lambda *s: torch.rand(*s, generator=g)
+    t = {"x": r(B, T, H, P, rank), "b": r(B, T, H, N, rank) / N ** 0.5, "c": r(B, T, H, N, rank) / N ** 0.5,
+         "dt": u(B, T, H) * 0.5 + 0.05, "lam": u(B, T, H), "a_log": u(H), "theta": u(B, T, H, N // 2) * 3,
+         "d_skip": torch.tensor([0.3, -0.2])}
+    for k in ("x", "b", "c", "dt", "lam", "theta"):
+        t[k] = t[k].to(dtype)
+    y_scan, st_scan, _ = fused_run(t, 4, True, False)
+    dev = {k: v.cuda() for k, v in t.items()}
+    state = SsmState.zeros(B, H, P, N, True, "cuda")
+    ys = []
+    for i in range(T):
+        y, state = mamba3_step(dev["x"][:, i], dev["b"][:, i], dev["c"][:, i], dev["dt"][:, i], dev["lam"][:, i],
+                               dev["a_log"], dev["theta"][:, i], dev["d_skip"], state)
+        ys.append(y.unsqueeze(1))
+    y_step = torch.cat(ys, 1)
+    tol = 3e-4 if dtype == torch.float32 else 2e-2
+    assert ref_metric(y_step.float(), y_scan.float()) <= tol
+    assert ref_metric(state.h, st_scan.h) <= tol and ref_metric(state.last_u, st_scan.last_u) <= tol
+    assert angle_close(state.angle, st_scan.angle, 1e-3)
