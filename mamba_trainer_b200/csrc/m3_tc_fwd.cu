@@ -23,7 +23,7 @@ namespace {
 constexpr uint32_t OFF_C = 0, OFF_B = 32768, OFF_X = 65536, OFF_XW = 81920, OFF_H = 98304, OFF_PHI = 114688,
                    OFF_SC = 147456;
 // scalar arrays: dt, lam, a, ac, g, w, sw, eac ; then carry[64], quarter sums[4][64]
-constexpr uint32_t kSmemBytes = OFF_SC + (kNumScal * kScal + 64 + 256) * 4 + 64;
+constexpr uint32_t kSmemBytes = OFF_SC + (2 * kNumScal * kScal + 64 + 256) * 4 + 64;
 constexpr uint32_t TM_G = 0, TM_Y = 128, TM_H = 192, TM_COLS = 256;
 
 #ifdef M3_TC_TIMING
@@ -46,10 +46,13 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
   uint8_t* sH = smem + OFF_H;    // bf16 H [p][n]
   float* sPhi = reinterpret_cast<float*>(smem + OFF_PHI);
   float* sc = reinterpret_cast<float*>(smem + OFF_SC);
-  TileScalars ts{sc, sc + kScal, sc + 2 * kScal, sc + 3 * kScal, sc + 4 * kScal, sc + 5 * kScal, sc + 6 * kScal,
-                 sc + 7 * kScal, sc + 8 * kScal};
-  float *s_ac = ts.ac, *s_eac = ts.eac;
-  float* s_carry = sc + kNumScal * kScal;  // [64] running angle
+  // Two sets of per-token scalars: the next tile's are computed while this tile's products run.
+  auto scal_set = [&](int i) {
+    float* q = sc + i * kNumScal * kScal;
+    return TileScalars{q, q + kScal, q + 2 * kScal, q + 3 * kScal, q + 4 * kScal, q + 5 * kScal, q + 6 * kScal,
+                       q + 7 * kScal, q + 8 * kScal};
+  };
+  float* s_carry = sc + 2 * kNumScal * kScal;  // [64] running angle
   float* s_q = s_carry + 64;             // [4][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_q + 256);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
@@ -120,12 +123,33 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
     issue_px<R>(raw_x, p.x, tok_first, H, T, 0);
     if (ROT) issue_theta<R>(raw_th, p.theta, tok_first, H, T, 0);
   }
+  // Scalars and angles always run one tile ahead, inside the waits for the tensor core.
+  auto prepare_scalars = [&](int k1) {
+    tile_scalars<R>(scal_set(k1 & 1), nx_dt, nx_lam, A, T, k1 * LT);
+    load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, (k1 + 1) * LT);
+  };
+  auto prepare_angles = [&](int k1) {  // needs raw_th of tile k1 and the scalars of tile k1
+    if (ROT) {
+      commit_theta<R>(raw_th, sPhi);
+      if (p.ckpt_angle && tid < kNH) p.ckpt_angle[((size_t)bh * ntiles + k1) * kNH + tid] = s_carry[tid];
+      __syncthreads();
+      const float ncarry = tile_angles_smem<R>(sPhi, s_q, s_carry, scal_set(k1 & 1).dt, T, k1 * LT,
+                                               p.angle_out ? p.angle_out + (size_t)bh * kNH : nullptr);
+      __syncthreads();
+      if ((tid >> 6) == 3) s_carry[tid & 63] = ncarry;
+    }
+  };
+  prepare_scalars(0);
+  prepare_angles(0);
+  __syncthreads();
 #ifdef M3_TC_TIMING
   long long tick_ = clock64();
   long long tock_ = clock64();
 #endif
   for (int k = 0; k < ntiles; ++k) {
     const int t0 = k * LT;
+    const TileScalars ts = scal_set(k & 1);
+    float *s_ac = ts.ac, *s_eac = ts.eac;
     TICK(0);
     const size_t tok0 = ((size_t)b * T + t0) * H + h;  // token-head index of l = 0 (stride H per step)
     // ---- 1. the tile's raw inputs were put in flight one tile ago -----------------------------
@@ -136,21 +160,7 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
       for (int i = 0; i < 4; ++i) dst[tid + 256 * i] = src[tid + 256 * i];
     }
     TICK(1);
-    // ---- 2. per-token scalars and the wrapped cumulative angle ------------------------------
-    tile_scalars<R>(ts, nx_dt, nx_lam, A, T, t0);
-    load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, t0 + LT);
     TICK(2);
-    if (ROT) {
-      commit_theta<R>(raw_th, sPhi);
-      if (p.ckpt_angle && tid < kNH) p.ckpt_angle[((size_t)bh * ntiles + k) * kNH + tid] = s_carry[tid];
-      __syncthreads();
-      const float ncarry = tile_angles_smem<R>(sPhi, s_q, s_carry, ts.dt, T, t0,
-                                               p.angle_out ? p.angle_out + (size_t)bh * kNH : nullptr);
-      __syncthreads();
-      if ((tid >> 6) == 3) s_carry[tid & 63] = ncarry;
-    } else {
-      __syncthreads();
-    }
     TICK(3);
     // ---- 3. convert and store the operands -----------------------------------------------------
     commit_bc<R, ROT>(raw_bc, sB, sC, sPhi);
@@ -172,6 +182,7 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
       issue_bc<R, ROT>(raw_bc, p.b, p.c, tok1, H, T, t0 + LT);
       issue_px<R>(raw_x, p.x, tok1, H, T, t0 + LT);
       if (ROT) issue_theta<R>(raw_th, p.theta, tok1, H, T, t0 + LT);
+      prepare_scalars(k + 1);   // while G and Yoff are being computed
     }
     {
       const bool ok = mbar_wait(&bars[0], k & 1);
@@ -259,6 +270,7 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
       gemm_issue(tm + TM_H, mn_major(smem_u32(sB), kN), mn_major(smem_u32(sXw), kP), make_idesc(64, 1, 1), kRows, true);
       umma_commit(&bars[1]);
     }
+    if (k + 1 < ntiles) prepare_angles(k + 1);  // while Y and the state update are being computed
     {
       const bool ok = mbar_wait(&bars[1], k & 1);
       if (__syncthreads_or(!ok)) { failed = true; break; }
