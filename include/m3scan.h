@@ -198,6 +198,43 @@ int m3_step_forward(m3_ctx *ctx, const m3_step_desc *desc, const m3_step_out *ou
 #define M3_NOALLOC_SCRATCH_BYTES (16u << 20)
 int m3_scan_forward_noalloc(m3_ctx *ctx, const m3_scan_desc *desc, const m3_scan_out *out);
 
+/* Forward + backward for tensors that live in HOST memory: the reference's
+ * Tensor::from_f32 ... mamba3_scan ... backward ... to_data sequence
+ * (src/tensor/base.rs:21-199 around src/ssm/scan.rs:458-618) for a caller that owns
+ * host buffers only.  The call is cut into `slices` contiguous batch slices (every
+ * batch row is an independent recurrence) that move through three stages on three
+ * streams - host-to-device copy, forward + backward on the context's stream,
+ * device-to-host copy - with two sets of device buffers, so the copies of one slice
+ * hide behind the kernels and the opposite-direction copies of its neighbours, within
+ * a run and across consecutive runs.  Results equal one call on the whole batch; the
+ * per-head gradients are summed over the slices in slice order.
+ *
+ * m3_host_in / m3_host_out hold HOST pointers, shaped like the corresponding fields of
+ * m3_scan_desc / m3_scan_out / m3_scan_grads; they should be page-locked
+ * (m3_host_alloc, or any cudaHostAlloc / cudaHostRegister memory) or the copies do not
+ * overlap.  `shape` gives the extents, dtype, discretization, dynamics, chunk and path
+ * and the DEVICE pointers a_log and d_skip (d_skip may be NULL); its other pointers are
+ * ignored.  lambda / theta (and their gradients) are used only by the learned
+ * trapezoid / rotational dynamics.  A NULL field of m3_host_out skips that copy. */
+typedef struct m3_host_pipe m3_host_pipe;
+typedef struct {
+  const void *x, *b, *c, *dt, *lambda, *theta, *dy;
+} m3_host_in;
+typedef struct {
+  void *y, *dx, *db, *dc, *ddt, *dlambda, *dtheta; /* desc.dtype */
+  float *da_log, *dd_skip;                         /* [heads]    */
+} m3_host_out;
+int m3_host_alloc(size_t bytes, void **out_host);
+int m3_host_free(void *host_ptr);
+int m3_host_pipe_create(m3_ctx *ctx, const m3_scan_desc *shape, int slices, m3_host_pipe **out);
+/* Enqueue one run and return at once.  Inputs must stay unchanged, and outputs must not
+ * be read, until m3_host_pipe_wait returns for the ticket written to *ticket (may be
+ * NULL).  Runs complete in order. */
+int m3_host_pipe_run(m3_host_pipe *pipe, const m3_host_in *in, const m3_host_out *out, uint64_t *ticket);
+/* Block until the run with this ticket has delivered its outputs to host memory. */
+int m3_host_pipe_wait(m3_host_pipe *pipe, uint64_t ticket);
+int m3_host_pipe_destroy(m3_host_pipe *pipe);
+
 /* Bytes of device scratch a forward with this descriptor allocates (kept until
  * m3_saved_free when `saved` is requested). */
 size_t m3_scan_scratch_bytes(const m3_scan_desc *desc, int for_backward);

@@ -55,6 +55,14 @@ class StepOut(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("y", "h", "last_u", "angle")]
 
 
+class HostIn(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("x", "b", "c", "dt", "lambda_", "theta", "dy")]
+
+
+class HostOut(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("y", "dx", "db", "dc", "ddt", "dlambda", "dtheta", "da_log", "dd_skip")]
+
+
 # name -> (restype, argtypes); every symbol include/m3scan.h declares.
 SYMBOLS = {
     "m3_version": (C.c_char_p, []),
@@ -74,6 +82,12 @@ SYMBOLS = {
     "m3_scan_scratch_bytes": (C.c_size_t, [C.POINTER(ScanDesc), C.c_int]),
     "m3_step_forward": (C.c_int, [C.c_void_p, C.POINTER(StepDesc), C.POINTER(StepOut)]),
     "m3_scan_forward_noalloc": (C.c_int, [C.c_void_p, C.POINTER(ScanDesc), C.POINTER(ScanOut)]),
+    "m3_host_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
+    "m3_host_free": (C.c_int, [C.c_void_p]),
+    "m3_host_pipe_create": (C.c_int, [C.c_void_p, C.POINTER(ScanDesc), C.c_int, C.POINTER(C.c_void_p)]),
+    "m3_host_pipe_run": (C.c_int, [C.c_void_p, C.POINTER(HostIn), C.POINTER(HostOut), C.POINTER(C.c_uint64)]),
+    "m3_host_pipe_wait": (C.c_int, [C.c_void_p, C.c_uint64]),
+    "m3_host_pipe_destroy": (C.c_int, [C.c_void_p]),
 }
 
 _lib = None

@@ -5,92 +5,121 @@ boundary that hands over host buffers) pays the PCIe copies around the op.  Beca
 row is an independent recurrence, the call is cut into batch slices and run as a three-stage
 pipeline - host-to-device copy, forward + backward, device-to-host copy - on three CUDA streams,
 so the copies of one slice hide behind the kernels and the opposite-direction copies of its
-neighbours.  Results are identical to one call on the whole batch (per-head parameter gradients
-are summed over the slices in a fixed order).
+neighbours.  The pipeline itself is native (m3_host_pipe_* in libm3scan): one library call enqueues
+a whole run, so the host thread is not the bottleneck.  Results are identical to one call on the
+whole batch (per-head parameter gradients are summed over the slices in a fixed order).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+import ctypes as C
+from typing import Dict, Optional
 
 import torch
 
+from . import _ffi
 from .ssm.config import Discretization
-from .ssm.scan import ScanInputs, mamba3_scan
+from .ssm.scan import Context, _DTYPES
 
 _PER_TOKEN = ("x", "b", "c", "dt", "lam", "theta", "dy")
 _PER_HEAD = ("a_log", "d_skip")
 
 
+def _hp(t: Optional[torch.Tensor]):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
 class HostScanPipeline:
     """Reusable pipeline for one problem shape.  `host` tensors must be pinned for the copies to
-    be asynchronous; outputs are written into pinned tensors owned by the pipeline."""
+    be asynchronous; outputs are written into pinned tensors owned by the pipeline (two sets,
+    used alternately, so the results of one run stay valid while the next run is in flight)."""
 
     def __init__(self, host: Dict[str, Optional[torch.Tensor]], chunk: int, discretization: Discretization,
-                 device, slices: int = 4):
+                 device, slices: int = 4, params: Optional[Dict[str, torch.Tensor]] = None,
+                 path: int = _ffi.PATH_AUTO):
         self.dev = torch.device(device)
         self.chunk, self.disc = chunk, Discretization(discretization)
         self.names = [n for n in _PER_TOKEN if host.get(n) is not None]
         if not self.disc.needs_lambda_projection() and "lam" in self.names:
             self.names.remove("lam")
-        B = host["x"].shape[0]
+        x = host["x"]
+        self.shape = tuple(x.shape)
+        B, T, H, P, R = x.shape
+        N = host["b"].shape[3]
+        self.rot = "theta" in self.names
         self.slices = max(1, min(slices, B))
-        bounds = [round(i * B / self.slices) for i in range(self.slices + 1)]
-        self.ranges = [(bounds[i], bounds[i + 1]) for i in range(self.slices)]
-        width = max(hi - lo for lo, hi in self.ranges)
-        self.stage = [{n: torch.empty((width,) + tuple(host[n].shape[1:]), dtype=host[n].dtype, device=self.dev)
-                       for n in self.names} for _ in range(2)]
         self.grad_names = [n for n in self.names if n != "dy"]
-        self.out = {"y": torch.empty(host["x"].shape, dtype=host["x"].dtype).pin_memory()}
-        for n in self.grad_names:
-            self.out["d" + n] = torch.empty(host[n].shape, dtype=host[n].dtype).pin_memory()
-        H = host["x"].shape[2]
-        for n in _PER_HEAD:   # per-head parameter gradients, float32 [heads]
-            self.out["d" + n] = torch.empty((H,), dtype=torch.float32).pin_memory()
-        self.s_in, self.s_out = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
+        self._outs = []
+        for _ in range(2):
+            out = {"y": torch.empty(x.shape, dtype=x.dtype).pin_memory()}
+            for n in self.grad_names:
+                out["d" + n] = torch.empty(host[n].shape, dtype=host[n].dtype).pin_memory()
+            for n in _PER_HEAD:   # per-head parameter gradients, float32 [heads]
+                out["d" + n] = torch.zeros((H,), dtype=torch.float32).pin_memory()
+            self._outs.append(out)
         self.h2d_bytes = sum(host[n].numel() * host[n].element_size() for n in self.names)
-        self.d2h_bytes = sum(v.numel() * v.element_size() for v in self.out.values())
+        self.d2h_bytes = sum(v.numel() * v.element_size() for v in self._outs[0].values())
+        self._desc_args = dict(
+            batch=B, seq=T, heads=H, head_dim=P, d_state=N, rank=R, chunk=int(chunk), dtype=_DTYPES[x.dtype],
+            discretization=int(self.disc.value), dynamics=1 if self.rot else 0, want_state=0, path=int(path))
+        self._ctx = Context.for_device(self.dev)
+        self._pipe = None
+        self._params = None
+        self._runs = 0
+        self._tickets = {}
+        if params is not None:
+            self._create(params)
 
-    def run(self, host: Dict[str, Optional[torch.Tensor]], params: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
-        """host: pinned per-token tensors; params: a_log / d_skip on the device (requires_grad)."""
-        main = torch.cuda.current_stream(self.dev)
-        done: List[torch.cuda.Event] = []
-        keep = []
-        psum = {n: None for n in _PER_HEAD if params.get(n) is not None}
-        for i, (lo, hi) in enumerate(self.ranges):
-            buf = self.stage[i % 2]
-            with torch.cuda.stream(self.s_in):
-                if i >= 2:
-                    self.s_in.wait_event(done[i - 2])          # the staging buffer is free again
-                elif i == 0:
-                    self.s_in.wait_stream(main)
-                for n in self.names:
-                    buf[n][: hi - lo].copy_(host[n][lo:hi], non_blocking=True)
-                ready = torch.cuda.Event()
-                ready.record(self.s_in)
-            main.wait_event(ready)
-            src = {n: buf[n][: hi - lo].detach().requires_grad_(n != "dy") for n in self.names}
-            inp = ScanInputs.new(src["x"], src["b"], src["c"], src["dt"], params["a_log"], src.get("lam"))
-            inp = inp.with_chunk_size(self.chunk).with_state_output(False).with_discretization(self.disc)
-            if src.get("theta") is not None:
-                inp = inp.with_theta(src["theta"])
-            if params.get("d_skip") is not None:
-                inp = inp.with_skip(params["d_skip"])
-            y = mamba3_scan(inp).y
-            wrt = [src[n] for n in self.grad_names] + [params[n] for n in psum]
-            grads = torch.autograd.grad(y, wrt, grad_outputs=src["dy"])
-            for n, gv in zip(psum, grads[len(self.grad_names):]):
-                psum[n] = gv if psum[n] is None else psum[n] + gv
-            ev = torch.cuda.Event()
-            ev.record(main)
-            done.append(ev)
-            with torch.cuda.stream(self.s_out):
-                self.s_out.wait_event(ev)
-                self.out["y"][lo:hi].copy_(y, non_blocking=True)
-                for n, gv in zip(self.grad_names, grads):
-                    self.out["d" + n][lo:hi].copy_(gv, non_blocking=True)
-            keep.append((y, grads))
-        for n, gv in psum.items():
-            self.out["d" + n].copy_(gv.float(), non_blocking=True)   # on the main stream, after the last slice
-        main.wait_stream(self.s_out)
-        self._keep = keep                                      # device results stay alive until the copies ran
-        return self.out
+    def _create(self, params: Dict[str, torch.Tensor]) -> None:
+        a_log, d_skip = params["a_log"].detach(), params.get("d_skip")
+        d_skip = d_skip.detach() if d_skip is not None else None
+        if a_log.dtype != torch.float32 or (d_skip is not None and d_skip.dtype != torch.float32):
+            raise TypeError("a_log and d_skip are float32 device tensors")
+        self._params = (a_log, d_skip)   # kept alive: the native pipeline holds their addresses
+        desc = _ffi.ScanDesc(a_log=_hp(a_log), d_skip=_hp(d_skip), **self._desc_args)
+        handle = C.c_void_p()
+        self._ctx.check(self._ctx.lib.m3_host_pipe_create(self._ctx.handle, C.byref(desc), self.slices, C.byref(handle)))
+        self._pipe = handle
+
+    def run(self, host: Dict[str, Optional[torch.Tensor]], params: Dict[str, torch.Tensor],
+            wait: bool = False) -> Dict[str, torch.Tensor]:
+        """Enqueue one run.  host: pinned per-token tensors; params: a_log / d_skip on the device.
+        Returns the pinned output tensors of this run; they are complete after `wait(outputs)`
+        (or at once with wait=True)."""
+        if self._pipe is None:
+            self._create(params)
+        elif params["a_log"].data_ptr() != self._params[0].data_ptr() or (
+                self._params[1] is not None and params["d_skip"].data_ptr() != self._params[1].data_ptr()):
+            raise ValueError("the pipeline was created for other parameter tensors")
+        self._ctx.bind_current_stream()
+        out = self._outs[self._runs % 2]
+        hin = _ffi.HostIn(x=_hp(host["x"]), b=_hp(host["b"]), c=_hp(host["c"]), dt=_hp(host["dt"]),
+                          lambda_=_hp(host.get("lam")) if "lam" in self.names else None,
+                          theta=_hp(host.get("theta")) if self.rot else None, dy=_hp(host["dy"]))
+        hout = _ffi.HostOut(y=_hp(out["y"]), dx=_hp(out["dx"]), db=_hp(out["db"]), dc=_hp(out["dc"]),
+                            ddt=_hp(out["ddt"]), dlambda=_hp(out.get("dlam")), dtheta=_hp(out.get("dtheta")),
+                            da_log=_hp(out["da_log"]), dd_skip=_hp(out["dd_skip"]) if self._params[1] is not None else None)
+        ticket = C.c_uint64()
+        self._ctx.check(self._ctx.lib.m3_host_pipe_run(self._pipe, C.byref(hin), C.byref(hout), C.byref(ticket)))
+        self._tickets[id(out)] = ticket.value
+        self._runs += 1
+        if wait:
+            self.wait(out)
+        return out
+
+    def wait(self, out: Optional[Dict[str, torch.Tensor]] = None) -> None:
+        """Block until the run that produced `out` (default: the latest run) is in host memory."""
+        if self._pipe is None or not self._tickets:
+            return
+        ticket = self._tickets[id(out)] if out is not None else max(self._tickets.values())
+        self._ctx.check(self._ctx.lib.m3_host_pipe_wait(self._pipe, ticket))
+
+    def close(self) -> None:
+        if self._pipe is not None:
+            self._ctx.lib.m3_host_pipe_destroy(self._pipe)
+            self._pipe = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # interpreter shutdown
+            pass

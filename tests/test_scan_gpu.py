@@ -337,14 +337,44 @@ def test_host_pipeline_matches_one_call():
     params = {"a_log": t["a_log"].cuda().requires_grad_(True), "d_skip": t["d_skip"].cuda().requires_grad_(True)}
     pipe = HostScanPipeline(host, w.chunk, w.discretization, "cuda", slices=3)
     for _ in range(2):   # twice: buffers and streams are reused
-        out = pipe.run(host, params)
-        torch.cuda.synchronize()
+        out = pipe.run(host, params, wait=True)
     y, _, g = fused_run(t, w.chunk, False, True)
     assert torch.equal(out["y"], y.cpu())
     for n in ("x", "b", "c", "dt", "lam", "theta"):
         assert torch.equal(out["d" + n], g[n].cpu()), n
     check_f32("da_log", out["da_log"], g["a_log"].cpu())     # summed over slices in a different order
     check_f32("dd_skip", out["dd_skip"], g["d_skip"].cpu())
+    # Two runs in flight at once: each delivers into its own output set.
+    host2 = dict(host, dy=(t["dy"] * 2).pin_memory())
+    out1 = pipe.run(host, params)
+    out2 = pipe.run(host2, params)
+    pipe.wait(out1)
+    assert torch.equal(out1["dx"], g["x"].cpu())
+    pipe.wait(out2)
+    assert torch.equal(out2["y"], y.cpu())
+    assert torch.equal(out2["dx"], (g["x"] * 2).cpu())       # the adjoint is linear in dy (a power of two is exact)
+    pipe.close()
+
+
+def test_host_pipeline_single_slice_f32_generic_path():
+    """One slice, float32, no rotation, constant lambda: the generic family through the same pipeline."""
+    from mamba_trainer_b200.host_pipeline import HostScanPipeline
+    t, _ = small_inputs(3, 37, 2, 8, 6, 2, False, False, seed=5)
+    host = {n: t[n].pin_memory() for n in ("x", "b", "c", "dt", "dy")}
+    params = {"a_log": t["a_log"].cuda().requires_grad_(True), "d_skip": t["d_skip"].cuda().requires_grad_(True)}
+    pipe = HostScanPipeline(host, 16, Discretization.Trapezoid, "cuda", slices=1)
+    out = pipe.run(host, params, wait=True)
+    dev = {k: (v.cuda() if isinstance(v, torch.Tensor) else v) for k, v in t.items()}
+    for k in ("x", "b", "c", "dt", "a_log", "d_skip"):
+        dev[k] = dev[k].detach().requires_grad_(True)
+    inp = ScanInputs.new(dev["x"], dev["b"], dev["c"], dev["dt"], dev["a_log"], None).with_chunk_size(16)
+    inp = inp.with_state_output(False).with_discretization(Discretization.Trapezoid).with_skip(dev["d_skip"])
+    y = mamba3_scan(inp).y
+    gr = torch.autograd.grad(y, [dev[k] for k in ("x", "b", "c", "dt", "a_log", "d_skip")], grad_outputs=dev["dy"])
+    assert torch.equal(out["y"], y.detach().cpu())
+    for n, gv in zip(("x", "b", "c", "dt", "a_log", "d_skip"), gr):
+        assert torch.equal(out["d" + n], gv.cpu()), n
+    pipe.close()
 
 
 # ---- decode step ------------------------------------------------------------------------------------
