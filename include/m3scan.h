@@ -67,6 +67,15 @@ typedef struct {
   int32_t dynamics;       /* m3_dynamics */
   int32_t want_state;     /* ScanInputs::want_state */
   int32_t path;           /* m3_path */
+  int32_t reverse_heads;  /* the LAST reverse_heads heads walk time right to left: the fused form of
+                           * the bidirectional mixer (src/models/mamba3.rs:97-112), which reverses the
+                           * backward half of x, B, C, dt, lambda, theta in time before the scan
+                           * (:352-370) and the backward heads' y after it (:548-556).  Here those
+                           * heads read and write their tokens in reverse order instead; inputs,
+                           * outputs and gradients all stay in ordinary time.  0 = none; heads/2 for
+                           * the bidirectional mixer.  The carried state of such a head enters at the
+                           * last token and the returned one is the state after token 0. */
+  int32_t reserved0;      /* must be 0 */
   const void *x;          /* [batch, seq, heads, head_dim, rank] */
   const void *b;          /* [batch, seq, heads, d_state, rank]  */
   const void *c;          /* [batch, seq, heads, d_state, rank]  */

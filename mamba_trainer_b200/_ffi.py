@@ -26,9 +26,10 @@ NOALLOC_SCRATCH_BYTES = 16 << 20   # M3_NOALLOC_SCRATCH_BYTES
 class ScanDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "batch", "seq", "heads", "head_dim", "d_state", "rank", "chunk", "dtype",
-        "discretization", "dynamics", "want_state", "path")] + [(n, C.c_void_p) for n in (
-        "x", "b", "c", "dt", "lambda_", "theta", "a_log", "d_skip", "h0", "last_u0", "angle0",
-        "a_raw", "g_raw", "w_raw")]
+        "discretization", "dynamics", "want_state", "path", "reverse_heads", "reserved0")] + [
+        (n, C.c_void_p) for n in (
+            "x", "b", "c", "dt", "lambda_", "theta", "a_log", "d_skip", "h0", "last_u0", "angle0",
+            "a_raw", "g_raw", "w_raw")]
 
 
 class ScanOut(C.Structure):

@@ -66,6 +66,8 @@ int make_dims(m3_ctx* ctx, const m3_scan_desc& s, m3::Dims* out) {
   if (s.dynamics == M3_ROTATIONAL && (s.d_state % 2))
     return fail(ctx, M3_ERR_CONFIG, "rotational dynamics require an even d_state");
   if (s.rank > 64) return fail(ctx, M3_ERR_UNSUPPORTED, "rank %d > 64", s.rank);
+  if (s.reverse_heads < 0 || s.reverse_heads > s.heads)
+    return fail(ctx, M3_ERR_CONFIG, "reverse_heads %d outside [0, heads = %d]", s.reverse_heads, s.heads);
   const bool raw = s.a_raw != nullptr;
   if (raw) {
     if (!s.g_raw || !s.w_raw) return fail(ctx, M3_ERR_NULL, "a_raw needs g_raw and w_raw");
@@ -92,6 +94,7 @@ int make_dims(m3_ctx* ctx, const m3_scan_desc& s, m3::Dims* out) {
   d.disc = s.discretization;
   d.LR = L * s.rank;
   d.raw = raw ? 1 : 0;
+  d.rev = s.reverse_heads;
   *out = d;
   return M3_OK;
 }
@@ -135,7 +138,7 @@ int tc_backward_call(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* i
   p.dlu0 = (has_state && want(M3_GRAD_LAST_U0, g->dlast_u0)) ? g->dlast_u0 : nullptr;
   p.dangle0 = (d.rot && desc.angle0 && want(M3_GRAD_ANGLE0, g->dangle0)) ? g->dangle0 : nullptr;
   p.err = ctx->dev_err;
-  p.B = d.B; p.T = d.T; p.H = d.H; p.R = d.R; p.disc = d.disc;
+  p.B = d.B; p.T = d.T; p.H = d.H; p.R = d.R; p.disc = d.disc; p.rev = d.rev;
   p.stagger = m3::tc_stagger_cycles(true);
   cudaError_t e = m3::tc_backward(ctx->stream, p, d.rot != 0);
   if (e == cudaSuccess) {
@@ -320,7 +323,7 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
     p.lu_out = desc->want_state ? out->last_u : nullptr;
     p.angle_out = (desc->want_state && d.rot) ? out->angle : nullptr;
     p.err = ctx->dev_err;
-    p.B = d.B; p.T = d.T; p.H = d.H; p.R = d.R; p.disc = d.disc;
+    p.B = d.B; p.T = d.T; p.H = d.H; p.R = d.R; p.disc = d.disc; p.rev = d.rev;
     p.stagger = m3::tc_stagger_cycles(false);
     char* base = nullptr;
     size_t bytes = 0;

@@ -17,7 +17,15 @@ struct Dims {
   int rot;       // 1 when rotational
   int LR;        // L * R rows per chunk
   int raw;       // 1: a, g, w come from the caller (the ssd_chunked form)
+  int rev;       // the last `rev` heads walk time right to left (bidirectional mixer)
 };
+
+// Token-head index (row of a [B, T, H, ...] tensor) of scan position t of head h: heads that
+// walk right to left (src/models/mamba3.rs:352-370, :548-556) see position t at time T-1-t.
+__host__ __device__ __forceinline__ size_t tok_index(const Dims& d, int b, int t, int h) {
+  const int tm = (h >= d.H - d.rev) ? d.T - 1 - t : t;
+  return ((size_t)b * d.T + tm) * d.H + h;
+}
 
 __device__ __forceinline__ float ldf(const float* p, size_t i) { return p[i]; }
 __device__ __forceinline__ float ldf(const __nv_bfloat16* p, size_t i) { return __bfloat162float(p[i]); }

@@ -14,11 +14,12 @@ namespace m3 {
 template <class T>
 struct DyRows {
   const T* dy;
-  int b, h, k, T_, H, P, R, L;
+  int b, h, k, T_, H, P, R, L, rev;
   __device__ __forceinline__ float operator()(int rho, int p) const {
     const int l = rho / R, r = rho - l * R, t = k * L + l;
     if (t >= T_ || p >= P) return 0.0f;
-    return ldf(dy, (((size_t)b * T_ + t) * H + h) * P * R + (size_t)p * R + r);
+    const int tm = rev ? T_ - 1 - t : t;  // right-to-left heads: scan position t is time T-1-t
+    return ldf(dy, (((size_t)b * T_ + tm) * H + h) * P * R + (size_t)p * R + r);
   }
 };
 
@@ -66,7 +67,7 @@ __global__ void __launch_bounds__(256) kb_rows(Dims d, const T* __restrict__ dy,
   const float* Hk = ws.Hs + ((size_t)bh * (d.C + 1) + k) * P * N;
   float* dC = bw.dCh + tb * R * N;
   float* dBand = bw.dBand + ((size_t)bh * d.C + k) * L * L;
-  const DyRows<T> dyf{dy, b, h, k, d.T, d.H, P, R, L};
+  const DyRows<T> dyf{dy, b, h, k, d.T, d.H, P, R, L, h >= d.H - d.rev};
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float acc[4][4], acc2[4][4];
   for (int n0 = 0; n0 < ncols; n0 += CW) {
@@ -159,7 +160,7 @@ __global__ void __launch_bounds__(256) kb_dhloc(Dims d, const T* __restrict__ dy
   __syncthreads();
   const float* Cm = ws.Ch + tb * d.R * d.N;
   const int P = d.P, N = d.N, R = d.R;
-  const DyRows<T> dyf{dy, b, h, k, d.T, d.H, P, R, d.L};
+  const DyRows<T> dyf{dy, b, h, k, d.T, d.H, P, R, d.L, h >= d.H - d.rev};
   float acc[4][4];
   zero_acc(acc);
   gemm_tile<false, false>(
@@ -257,7 +258,7 @@ __global__ void __launch_bounds__(256) kb_cols(Dims d, const T* __restrict__ dy,
   const float* dS = bw.dHs + ((size_t)bh * (d.C + 1) + k) * P * N;
   float* dX = bw.dXh + tb * R * P;
   float* dB = bw.dBh + tb * R * N;
-  const DyRows<T> dyf{dy, b, h, k, d.T, d.H, P, R, L};
+  const DyRows<T> dyf{dy, b, h, k, d.T, d.H, P, R, L, h >= d.H - d.rev};
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float acc[4][4], acc2[4][4];
   // pass 1: W = (G o band)^T rows of this tile, then dX~

@@ -60,7 +60,7 @@ __global__ void kb_scalars(Dims d, const T* __restrict__ dt, GenericWs ws, Gener
   for (int l = threadIdx.x; l < L; l += blockDim.x) {
     const int t = k * L + l;
     bw.da[tb + l] = s_da[l];
-    if (t < d.T && !d.raw) part += s_da[l] * ldf(dt, ((size_t)b * d.T + t) * d.H + h);
+    if (t < d.T && !d.raw) part += s_da[l] * ldf(dt, tok_index(d, b, t, h));
   }
   part = block_sum_256(part, red);
   if (threadIdx.x == 0) bw.partA[(size_t)bh * d.C + k] = part;
@@ -105,7 +105,7 @@ __global__ void kb_unrotate(Dims d, GenericWs ws, GenericBwdWs bw, const float* 
       float sn, cs;
       sincosf(ws.phi[((size_t)bh * d.Tp + t) * NH + m], &sn, &cs);
       float dphi = 0.0f;
-      const size_t ob = (((size_t)b * d.T + t) * d.H + h) * N * R;
+      const size_t ob = tok_index(d, b, t, h) * N * R;
       for (int r = 0; r < R; ++r) {
         const size_t row = ((size_t)bh * d.Tp * R + (size_t)t * R + r) * N;
         {
@@ -135,7 +135,7 @@ __global__ void kb_unrotate(Dims d, GenericWs ws, GenericBwdWs bw, const float* 
       const int r = e % R, n = (e / R) % N, l = e / (R * N), t = t0 + l;
       if (t >= d.T) continue;
       const size_t row = ((size_t)bh * d.Tp * R + (size_t)t * R + r) * N + n;
-      const size_t o = (((size_t)b * d.T + t) * d.H + h) * N * R + (size_t)n * R + r;
+      const size_t o = tok_index(d, b, t, h) * N * R + (size_t)n * R + r;
       if (db) stf(db, o, bw.dBh[row]);
       if (dc) stf(dc, o, bw.dCh[row]);
     }
@@ -181,7 +181,7 @@ __global__ void kb_dstep(Dims d, const T* __restrict__ dt, const T* __restrict__
       run += bw.dphi[o];
       bw.dphi[o] = run;  // dstep
       if (t < d.T && dtheta) {
-        const size_t i = ((size_t)b * d.T + t) * d.H + h;
+        const size_t i = tok_index(d, b, t, h);
         stf(dtheta, i * NH + m, run * ldf(dt, i));
       }
     }
@@ -191,7 +191,7 @@ __global__ void kb_dstep(Dims d, const T* __restrict__ dt, const T* __restrict__
     const int t = t0 + l;
     float s = 0.0f;
     if (t < d.T) {
-      const size_t i = ((size_t)b * d.T + t) * d.H + h;
+      const size_t i = tok_index(d, b, t, h);
       for (int m = 0; m < NH; ++m) s += bw.dphi[((size_t)bh * d.Tp + t) * NH + m] * ldf(theta, i * NH + m);
     }
     bw.ddt_rot[(size_t)bh * d.Tp + t] = s;
@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(256) kb_dx(Dims d, const T* __restrict__ x, co
   for (int e = threadIdx.x; e < L * P * R; e += blockDim.x) {
     const int r = e % R, p = (e / R) % P, l = e / (R * P), t = t0 + l;
     if (t >= d.T) continue;
-    const size_t o = (((size_t)b * d.T + t) * d.H + h) * P * R + (size_t)p * R + r;
+    const size_t o = tok_index(d, b, t, h) * P * R + (size_t)p * R + r;
     float v = bw.dXh[((size_t)bh * d.Tp * R + (size_t)t * R + r) * P + p];
     if (d_skip) {
       const float gy = ldf(dy, o);
@@ -239,15 +239,16 @@ __global__ void kb_final(Dims d, const T* __restrict__ dt, const T* __restrict__
   const int t = (i / d.H) % d.T;
   const int b = i / ((size_t)d.H * d.T);
   const int bh = b * d.H + h;
-  const size_t o = (size_t)bh * d.Tp + t;
+  const size_t o = (size_t)bh * d.Tp + t;        // scratch is in scan order: t is the scan position
+  const size_t ti = tok_index(d, b, t, h);        // and this is its token in memory
   if (d.raw) {  // the ssd_chunked form: gradients of the caller's a, g, w as they are
-    if (da_raw) stf(da_raw, i, bw.da[o]);
-    if (dg_raw) stf(dg_raw, i, bw.dg[o]);
-    if (dw_raw) stf(dw_raw, i, bw.dw[o]);
+    if (da_raw) stf(da_raw, ti, bw.da[o]);
+    if (dg_raw) stf(dg_raw, ti, bw.dg[o]);
+    if (dw_raw) stf(dw_raw, ti, bw.dw[o]);
     return;
   }
   const float A = -expf(a_log[h]);
-  const float vdt = ldf(dt, i), vl = lambda_at(lam, d.disc, i);
+  const float vdt = ldf(dt, ti), vl = lambda_at(lam, d.disc, ti);
   const float gw = bw.dg[o] + bw.dw[o];
   const float dwm1 = t > 0 ? bw.dw[o - 1] : 0.0f;
   float vdl = gw * vdt - dwm1 * vdt;
@@ -258,8 +259,8 @@ __global__ void kb_final(Dims d, const T* __restrict__ dt, const T* __restrict__
     vdl -= vdt * ip;
     vdd += (1.0f - vl) * ip;
   }
-  if (ddt) stf(ddt, i, vdd);
-  if (dlam) stf(dlam, i, vdl);
+  if (ddt) stf(ddt, ti, vdd);
+  if (dlam) stf(dlam, ti, vdl);
 }
 
 // ---- seed-state gradients: dh0 = dH_0, dlast_u0 = (1 - lambda_0) dt_0 dH_0
@@ -270,7 +271,7 @@ __global__ void kb_state_grads(Dims d, const T* __restrict__ dt, const T* __rest
   const int PN = d.P * d.N;
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= PN) return;
-  const size_t i0 = ((size_t)b * d.T) * d.H + h;
+  const size_t i0 = tok_index(d, b, 0, h);
   const float first = d.raw ? 0.0f : (1.0f - lambda_at(lam, d.disc, i0)) * ldf(dt, i0);
   const float v = bw.dHs[((size_t)bh * (d.C + 1) + d.C) * PN + e];
   if (dh0) dh0[(size_t)bh * PN + e] = v;

@@ -20,7 +20,7 @@ __global__ void k_angle_sum(Dims d, const T* __restrict__ dt, const T* __restric
     for (int l = 0; l < d.L; ++l) {
       const int t = k * d.L + l;
       if (t >= d.T) break;
-      const size_t i = ((size_t)b * d.T + t) * d.H + h;
+      const size_t i = tok_index(d, b, t, h);
       s += ldf(dt, i) * ldf(theta, i * d.NH + m);
     }
     abase[((size_t)bh * d.C + k) * d.NH + m] = s;
@@ -60,7 +60,7 @@ __global__ void k_prep(Dims d, const T* __restrict__ x, const T* __restrict__ bm
     const int t = t0 + l;
     float vdt = 0.0f, vl = 1.0f;
     if (t < d.T && !d.raw) {
-      const size_t i = ((size_t)b * d.T + t) * d.H + h;
+      const size_t i = tok_index(d, b, t, h);
       vdt = ldf(dt, i);
       vl = lambda_at(lam, d.disc, i);
     }
@@ -75,7 +75,7 @@ __global__ void k_prep(Dims d, const T* __restrict__ x, const T* __restrict__ bm
       const int t = t0 + l;
       float gv = 0.0f, wv = 0.0f, av = 0.0f;
       if (t < d.T && d.raw) {  // scan.rs:116-126: the caller's own a, g, w
-        const size_t i = ((size_t)b * d.T + t) * d.H + h;
+        const size_t i = tok_index(d, b, t, h);
         av = ldf(a_raw, i);
         gv = ldf(g_raw, i);
         wv = ldf(w_raw, i);
@@ -99,7 +99,7 @@ __global__ void k_prep(Dims d, const T* __restrict__ x, const T* __restrict__ bm
         const int t = t0 + l;
         float ph = 0.0f;
         if (t < d.T) {
-          const size_t i = ((size_t)b * d.T + t) * d.H + h;
+          const size_t i = tok_index(d, b, t, h);
           run += s_dt[l] * ldf(theta, i * d.NH + m);
           ph = wrap_angle(run);
           if (angle_out && t == d.T - 1) angle_out[(size_t)bh * d.NH + m] = ph;
@@ -115,7 +115,7 @@ __global__ void k_prep(Dims d, const T* __restrict__ x, const T* __restrict__ bm
     const int r = e % d.R, p = (e / d.R) % d.P, l = e / (d.R * d.P);
     const int t = t0 + l;
     float v = 0.0f;
-    if (t < d.T) v = ldf(x, (((size_t)b * d.T + t) * d.H + h) * d.P * d.R + (size_t)p * d.R + r);
+    if (t < d.T) v = ldf(x, tok_index(d, b, t, h) * d.P * d.R + (size_t)p * d.R + r);
     ws.Xh[((size_t)bh * d.Tp * d.R + (size_t)t * d.R + r) * d.P + p] = v;
   }
   if (d.rot) {
@@ -125,7 +125,7 @@ __global__ void k_prep(Dims d, const T* __restrict__ x, const T* __restrict__ bm
       const int t = t0 + l;
       float b1 = 0.f, b2 = 0.f, c1 = 0.f, c2 = 0.f;
       if (t < d.T) {
-        const size_t base = (((size_t)b * d.T + t) * d.H + h) * d.N * d.R;
+        const size_t base = tok_index(d, b, t, h) * d.N * d.R;
         const float vb1 = ldf(bm, base + (size_t)m * d.R + r);
         const float vb2 = ldf(bm, base + (size_t)(m + d.NH) * d.R + r);
         const float vc1 = ldf(cm, base + (size_t)m * d.R + r);
@@ -146,7 +146,7 @@ __global__ void k_prep(Dims d, const T* __restrict__ x, const T* __restrict__ bm
       const int t = t0 + l;
       float vb = 0.f, vc = 0.f;
       if (t < d.T) {
-        const size_t i = (((size_t)b * d.T + t) * d.H + h) * d.N * d.R + (size_t)n * d.R + r;
+        const size_t i = tok_index(d, b, t, h) * d.N * d.R + (size_t)n * d.R + r;
         vb = ldf(bm, i);
         vc = ldf(cm, i);
       }
@@ -208,7 +208,7 @@ __global__ void k_state_pass(Dims d, const T* __restrict__ dt, const T* __restri
   if (live && h0) {
     carry = h0[(size_t)bh * PN + e];
     if (lu0) {
-      const size_t i0 = ((size_t)b * d.T) * d.H + h;
+      const size_t i0 = tok_index(d, b, 0, h);
       carry += (1.0f - lambda_at(lam, d.disc, i0)) * ldf(dt, i0) * lu0[(size_t)bh * PN + e];
     }
   }
@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(256) k_chunk_out(Dims d, const T* __restrict__
         if (m < rows && p < P) {
           const int l = l0 + m / R, r = m % R, t = k * d.L + l;
           if (t < d.T) {
-            const size_t o = (((size_t)b * d.T + t) * d.H + h) * P * R + (size_t)p * R + r;
+            const size_t o = tok_index(d, b, t, h) * P * R + (size_t)p * R + r;
             float v = acc[i][j];
             if (d_skip) v += dsk * ldf(x, o);
             stf(y, o, v);

@@ -29,6 +29,7 @@ struct TcFwdParams {
   float* ckpt_angle;  // [BH, tiles, 64] angle entering each tile, or NULL
   int* err;           // device flag set when a bounded wait gave up
   int B, T, H, R, disc;
+  int rev;            // the last `rev` heads walk time right to left
   int stagger;        // cycles of start delay per CTA group (blockIdx & 3), 0 = none
 };
 
@@ -47,6 +48,7 @@ struct TcBwdParams {
   float *dh0, *dlu0, *dangle0;           // NULL skips the store
   int* err;
   int B, T, H, R, disc;
+  int rev;            // the last `rev` heads walk time right to left
   int stagger;
 };
 

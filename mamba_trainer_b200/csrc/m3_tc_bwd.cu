@@ -63,6 +63,10 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
   const int T = p.T, H = p.H;
+  // Right-to-left heads: scan position s is time T-1-s, reached with a negative token stride.
+  const bool rev = h >= H - p.rev;
+  const int Hs = rev ? -H : H;
+  auto tok_at = [&](int s) { return ((size_t)b * T + (rev ? T - 1 - s : s)) * H + h; };
   const int ntiles = (T + LT - 1) / LT;
   const int Tp = ntiles * LT;
   const float A = -expf(p.a_log[h]);
@@ -100,13 +104,13 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
   }
   bool failed = false;
   float nx_dt, nx_lam;  // dt / lambda of the next tile to process, loaded one tile ahead
-  load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, (ntiles - 1) * LT);
+  load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, (ntiles - 1) * LT, rev);
 #ifdef M3_TC_TIMING
   long long tick_ = clock64();
 #endif
   for (int k = ntiles - 1, it = 0; k >= 0; --k, ++it) {
     const int t0 = k * LT;
-    const size_t tok0 = ((size_t)b * T + t0) * H + h;
+    const size_t tok0 = tok_at(t0);
     const bool last_tile = (k == ntiles - 1);
     const int l_end = T - 1 - t0;  // row of the final token when last_tile
     // ---- 1. every global load of the tile in flight, then scalars and angles ---------------------
@@ -114,10 +118,10 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
     RawPX<R> raw_x, raw_dy;
     RawTheta<R> raw_th;
     uint4 raw_h[4];
-    issue_bc<R, ROT>(raw_bc, p.b, p.c, tok0, H, T, t0);
-    issue_px<R>(raw_x, p.x, tok0, H, T, t0);
-    issue_px<R>(raw_dy, p.dy, tok0, H, T, t0);
-    if (ROT) issue_theta<R>(raw_th, p.theta, tok0, H, T, t0);
+    issue_bc<R, ROT>(raw_bc, p.b, p.c, tok0, Hs, T, t0);
+    issue_px<R>(raw_x, p.x, tok0, Hs, T, t0);
+    issue_px<R>(raw_dy, p.dy, tok0, Hs, T, t0);
+    if (ROT) issue_theta<R>(raw_th, p.theta, tok0, Hs, T, t0);
     {
       const uint4* src = reinterpret_cast<const uint4*>(p.ckpt_h + ((size_t)bh * ntiles + k) * kN * kP);
 #pragma unroll
@@ -125,7 +129,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
     }
     TICK(0);
     tile_scalars<R>(ts, nx_dt, nx_lam, A, T, t0);
-    load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, t0 - LT);
+    load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, t0 - LT, rev);
     if (ROT) {
       if (tid < kNH) s_carry[tid] = p.ckpt_angle[((size_t)bh * ntiles + k) * kNH + tid];
       commit_theta<R>(raw_th, sPhi);
@@ -150,7 +154,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
 #ifndef M3_NO_L2_PREFETCH
     if (k > 0)  // warm L2 with the tile after this one (behind this tile's own loads)
       prefetch_tile_l2<R, ROT>(p.b, p.c, p.x, p.dy, p.theta, p.ckpt_h + ((size_t)bh * ntiles + k - 1) * kN * kP,
-                               tok0 - (size_t)LT * H, H, T, t0 - LT);
+                               tok0 - (size_t)LT * Hs, Hs, T, t0 - LT);
 #endif
     // ---- 4. MMA phase A ------------------------------------------------------------------------
     if (tid == 0) {
@@ -303,7 +307,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
     // ---- 7. epilogue B -------------------------------------------------------------------------
     if (ROT) {  // the angles again (their buffer held M in between)
       RawTheta<R> th2;
-      issue_theta<R>(th2, p.theta, tok0, H, T, t0);
+      issue_theta<R>(th2, p.theta, tok0, Hs, T, t0);
       commit_theta<R>(th2, sPhi);
       __syncthreads();
       tile_angles_smem<R, true>(sPhi, s_q, s_carry, ts.dt, T, t0, nullptr);  // (cos, sin) table this time
@@ -425,9 +429,9 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
       TICK(13);
       __syncthreads();
       TICK(14);
-      if (p.dx) copy_out<R, kP>(sHS, p.dx, tok0, H, T, t0);
-      if (p.db) copy_out<R, kN>(sXw, p.db, tok0, H, T, t0);
-      if (p.dc) copy_out<R, kN>(sDG, p.dc, tok0, H, T, t0);
+      if (p.dx) copy_out<R, kP>(sHS, p.dx, tok0, Hs, T, t0);
+      if (p.db) copy_out<R, kN>(sXw, p.db, tok0, Hs, T, t0);
+      if (p.dc) copy_out<R, kN>(sDG, p.dc, tok0, Hs, T, t0);
       TICK(15);
       __syncthreads();
       if (ROT) {
@@ -461,7 +465,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
         const int it = tid + 256 * i, l = it >> 3, mg = it & 7;
-        thq[i] = (t0 + l < T) ? __ldg(reinterpret_cast<const uint4*>(p.theta + (tok0 + (size_t)l * H) * kNH + mg * 8))
+        thq[i] = (t0 + l < T) ? __ldg(reinterpret_cast<const uint4*>(p.theta + (tok0 + (size_t)l * Hs) * kNH + mg * 8))
                               : make_uint4(0u, 0u, 0u, 0u);
       }
       float run = 0.0f;
@@ -502,7 +506,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
         if (t0 + l < T && p.dtheta) {
           uint4 qv;
           qv.x = pack_bf16(o[0], o[1]); qv.y = pack_bf16(o[2], o[3]); qv.z = pack_bf16(o[4], o[5]); qv.w = pack_bf16(o[6], o[7]);
-          *reinterpret_cast<uint4*>(p.dtheta + (tok0 + (size_t)l * H) * kNH + mg * 8) = qv;
+          *reinterpret_cast<uint4*>(p.dtheta + (tok0 + (size_t)l * Hs) * kNH + mg * 8) = qv;
         }
 #pragma unroll
         for (int o_ = 1; o_ < 8; o_ <<= 1) prod += __shfl_xor_sync(0xffffffffu, prod, o_);
@@ -580,7 +584,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
   if (!failed) {
     float first = 0.0f;
     if (p.h0) {
-      const size_t i0 = ((size_t)b * T) * H + h;
+      const size_t i0 = tok_at(0);
       const float l0 = p.disc == 0 ? 1.0f : (p.disc == 1 ? 0.5f : bf(p.lam, i0));
       first = (1.0f - l0) * bf(p.dt, i0);
     }

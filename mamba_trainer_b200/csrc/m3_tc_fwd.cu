@@ -60,6 +60,11 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
   const int T = p.T, H = p.H;
+  // A head that walks right to left sees scan position s at time T-1-s: its rows are reached
+  // with a negative token stride, everything else (tiles, scalars, checkpoints) is in scan order.
+  const bool rev = h >= H - p.rev;
+  const int Hs = rev ? -H : H;
+  auto tok_at = [&](int s) { return ((size_t)b * T + (rev ? T - 1 - s : s)) * H + h; };
   const int ntiles = (T + LT - 1) / LT;
   const float A = -expf(p.a_log[h]);
   const float dsk = p.d_skip ? p.d_skip[h] : 0.0f;
@@ -82,7 +87,7 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
   {
     float first = 0.0f;
     if (p.h0) {
-      const size_t i0 = ((size_t)b * T) * H + h;
+      const size_t i0 = tok_at(0);
       const float l0 = p.disc == 0 ? 1.0f : (p.disc == 1 ? 0.5f : bf(p.lam, i0));
       first = (1.0f - l0) * bf(p.dt, i0);
     }
@@ -112,21 +117,21 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
   }
   bool failed = false;
   float nx_dt, nx_lam;  // dt / lambda of the next tile, loaded one tile ahead
-  load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, 0);
+  load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, 0, rev);
   // Raw inputs of the NEXT tile travel in registers while the current tile computes.
   RawBC<R, ROT> raw_bc;
   RawPX<R> raw_x;
   RawTheta<R> raw_th;
   {
-    const size_t tok_first = ((size_t)b * T) * H + h;
-    issue_bc<R, ROT>(raw_bc, p.b, p.c, tok_first, H, T, 0);
-    issue_px<R>(raw_x, p.x, tok_first, H, T, 0);
-    if (ROT) issue_theta<R>(raw_th, p.theta, tok_first, H, T, 0);
+    const size_t tok_first = tok_at(0);
+    issue_bc<R, ROT>(raw_bc, p.b, p.c, tok_first, Hs, T, 0);
+    issue_px<R>(raw_x, p.x, tok_first, Hs, T, 0);
+    if (ROT) issue_theta<R>(raw_th, p.theta, tok_first, Hs, T, 0);
   }
   // Scalars and angles always run one tile ahead, inside the waits for the tensor core.
   auto prepare_scalars = [&](int k1) {
     tile_scalars<R>(scal_set(k1 & 1), nx_dt, nx_lam, A, T, k1 * LT);
-    load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, (k1 + 1) * LT);
+    load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, (k1 + 1) * LT, rev);
   };
   auto prepare_angles = [&](int k1) {  // needs raw_th of tile k1 and the scalars of tile k1
     if (ROT) {
@@ -151,7 +156,7 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
     const TileScalars ts = scal_set(k & 1);
     float *s_ac = ts.ac, *s_eac = ts.eac;
     TICK(0);
-    const size_t tok0 = ((size_t)b * T + t0) * H + h;  // token-head index of l = 0 (stride H per step)
+    const size_t tok0 = tok_at(t0);  // token-head index of l = 0 (stride Hs per step)
     // ---- 1. the tile's raw inputs were put in flight one tile ago -----------------------------
     if (p.ckpt_h) {  // the bf16 state entering this tile, for the backward pass
       const uint4* src = reinterpret_cast<const uint4*>(sH);
@@ -178,10 +183,10 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
       umma_commit(&bars[0]);
     }
     if (k + 1 < ntiles) {  // next tile's loads: in flight during both products and epilogues
-      const size_t tok1 = tok0 + (size_t)LT * H;
-      issue_bc<R, ROT>(raw_bc, p.b, p.c, tok1, H, T, t0 + LT);
-      issue_px<R>(raw_x, p.x, tok1, H, T, t0 + LT);
-      if (ROT) issue_theta<R>(raw_th, p.theta, tok1, H, T, t0 + LT);
+      const size_t tok1 = tok0 + (size_t)LT * Hs;
+      issue_bc<R, ROT>(raw_bc, p.b, p.c, tok1, Hs, T, t0 + LT);
+      issue_px<R>(raw_x, p.x, tok1, Hs, T, t0 + LT);
+      if (ROT) issue_theta<R>(raw_th, p.theta, tok1, Hs, T, t0 + LT);
       prepare_scalars(k + 1);   // while G and Yoff are being computed
     }
     {
@@ -328,7 +333,7 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
       }
     }
     __syncthreads();
-    copy_out<R, kP>(sXw, p.y, tok0, H, T, t0);
+    copy_out<R, kP>(sXw, p.y, tok0, Hs, T, t0);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();

@@ -119,13 +119,13 @@ __device__ __forceinline__ float row_factor(float ac_l, float ac_e) {
 // the loads of the NEXT tile can be in flight while the current one computes.
 template <int R>
 __device__ __forceinline__ void load_dt_lam(float& vdt, float& vl, const __nv_bfloat16* dt, const __nv_bfloat16* lam,
-                                            int disc, int b, int h, int H, int T, int t0) {
+                                            int disc, int b, int h, int H, int T, int t0, bool rev) {
   constexpr int LT = kRows / R;
   const int tid = threadIdx.x, t = t0 + tid;
   vdt = 0.0f;
   vl = 1.0f;
   if (tid <= LT && t >= 0 && t < T) {
-    const size_t i = ((size_t)b * T + t) * H + h;
+    const size_t i = ((size_t)b * T + (rev ? T - 1 - t : t)) * H + h;  // t is a scan position
     vdt = bf(dt, i);
     vl = disc == 0 ? 1.0f : (disc == 1 ? 0.5f : bf(lam, i));
   }

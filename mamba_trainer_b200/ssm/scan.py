@@ -124,6 +124,11 @@ class ScanInputs:
     # Discretization::fixed_lambda skip reading it (lambda_ may then be None).
     discretization: Discretization = Discretization.LearnedTrapezoid
     path: int = _ffi.PATH_AUTO
+    # The fused form of the bidirectional mixer (models/mamba3.rs:97-112): the last
+    # `reverse_heads` heads walk time right to left.  The reference reverses those heads'
+    # inputs before the scan (:352-370) and their output after it (:548-556); here the
+    # kernels read and write those heads' tokens in reverse order instead.
+    reverse_heads: int = 0
 
     @staticmethod
     def new(x, b, c, dt, a_log, lambda_) -> "ScanInputs":
@@ -157,6 +162,10 @@ class ScanInputs:
         self.path = path
         return self
 
+    def with_reverse_heads(self, reverse_heads: int) -> "ScanInputs":
+        self.reverse_heads = int(reverse_heads)
+        return self
+
 
 @dataclass
 class ScanOutput:
@@ -181,7 +190,7 @@ class _FusedScan(torch.autograd.Function):
             batch=B, seq=T, heads=H, head_dim=P, d_state=N, rank=R, chunk=int(opts["chunk"]),
             dtype=_DTYPES[x.dtype], discretization=int(opts["disc"]),
             dynamics=1 if theta is not None else 0, want_state=1 if opts["want_state"] else 0,
-            path=int(opts["path"]),
+            path=int(opts["path"]), reverse_heads=int(opts.get("rev", 0)),
             x=_ptr(x), b=_ptr(b), c=_ptr(c), dt=_ptr(dt), lambda_=_ptr(lam), theta=_ptr(theta),
             a_log=_ptr(a_log), d_skip=_ptr(d_skip), h0=_ptr(h0), last_u0=_ptr(last_u0), angle0=_ptr(angle0))
         y = torch.empty_like(x)
@@ -411,6 +420,8 @@ def mamba3_scan(inputs: ScanInputs) -> ScanOutput:
             raise ShapeError(f"theta has shape {tuple(theta.shape)}, expected {(B, T, H, N // 2)}")
     if inputs.d_skip is not None and tuple(inputs.d_skip.shape) != (H,):
         raise ShapeError(f"d_skip has shape {tuple(inputs.d_skip.shape)}, expected {(H,)}")
+    if not 0 <= inputs.reverse_heads <= H:
+        raise ConfigError(f"reverse_heads {inputs.reverse_heads} outside [0, heads = {H}]")
     st = inputs.state
     if st is not None:
         for name, t in (("h", st.h), ("last_u", st.last_u)):
@@ -429,7 +440,7 @@ def mamba3_scan(inputs: ScanInputs) -> ScanOutput:
     big = lambda t: None if t is None else t.to(el).contiguous()
     f32 = lambda t: None if t is None else t.to(torch.float32).contiguous()
     opts = {"chunk": inputs.chunk_size, "disc": int(disc), "want_state": bool(inputs.want_state),
-            "path": inputs.path}
+            "path": inputs.path, "rev": inputs.reverse_heads}
     outs = _FusedScan.apply(
         opts, x.contiguous(), big(b), big(c), big(inputs.dt), f32(inputs.a_log), big(lam), big(theta),
         f32(inputs.d_skip), f32(st.h) if st else None, f32(st.last_u) if st else None,

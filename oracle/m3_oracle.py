@@ -220,3 +220,23 @@ def mamba3_scan(x, b, c, dt, a_log, lam, theta=None, d_skip=None, state=None,
         last_u = torch.einsum("bhpr,bhnr->bhpn", x[:, T - 1], b_rot[:, T - 1])
         out_state = OracleState(h, last_u, end_angle)
     return y, out_state
+
+
+def reverse_bands_in_time(t: torch.Tensor, reverse_heads: int) -> torch.Tensor:
+    """Reverse the time axis (1) of the last `reverse_heads` heads (axis 2) of a [B,T,H,...] tensor:
+    what Tensor::reverse_bands does to the backward half of every direction-sensitive input of the
+    bidirectional mixer, src/models/mamba3.rs:352-370 (an involution)."""
+    if reverse_heads == 0:
+        return t
+    H = t.shape[2]
+    return torch.cat([t[:, :, :H - reverse_heads], t[:, :, H - reverse_heads:].flip(1)], dim=2)
+
+
+def mamba3_scan_bidirectional(x, b, c, dt, a_log, lam, theta=None, d_skip=None, state=None,
+                              chunk_size=64, want_state=True, reverse_heads=0):
+    """The scan as the bidirectional mixer runs it (src/models/mamba3.rs:352-370, :548-556): the last
+    `reverse_heads` heads see x, B, C, dt, lambda, theta reversed in time, and their y is reversed
+    back afterwards; the carried state is untouched (it is per head, not per token)."""
+    r = lambda t: None if t is None else reverse_bands_in_time(t, reverse_heads)
+    y, st = mamba3_scan(r(x), r(b), r(c), r(dt), a_log, r(lam), r(theta), d_skip, state, chunk_size, want_state)
+    return r(y), st

@@ -35,7 +35,7 @@ def allclose_excess(a, e, rtol, atol) -> float:
 
 
 def oracle_run(t: dict, chunk: int, want_state=True, dtype=torch.float64, grads=True,
-               dstate=None, use_lam=True):
+               dstate=None, use_lam=True, reverse_heads=0):
     """Run the composed oracle on CPU.  `t` holds x, b, c, dt, a_log, lam, theta, d_skip
     and optionally h0, last_u0, angle0, dy.  Inputs are upcast (a bf16 tensor is used
     at its rounded value).  Returns (y, state, {name: grad})."""
@@ -44,8 +44,8 @@ def oracle_run(t: dict, chunk: int, want_state=True, dtype=torch.float64, grads=
     st = None
     if "h0" in leaf:
         st = O.OracleState(leaf["h0"], leaf["last_u0"], leaf.get("angle0"))
-    y, out = O.mamba3_scan(leaf["x"], leaf["b"], leaf["c"], leaf["dt"], leaf["a_log"], leaf["lam"],
-                           leaf.get("theta"), leaf.get("d_skip"), st, chunk, want_state)
+    y, out = O.mamba3_scan_bidirectional(leaf["x"], leaf["b"], leaf["c"], leaf["dt"], leaf["a_log"], leaf["lam"],
+                                         leaf.get("theta"), leaf.get("d_skip"), st, chunk, want_state, reverse_heads)
     g = {}
     if grads:
         loss = (y * t["dy"].detach().cpu().to(dtype)).sum()
@@ -60,13 +60,13 @@ def oracle_run(t: dict, chunk: int, want_state=True, dtype=torch.float64, grads=
 
 
 def fused_run(t: dict, chunk: int, want_state=True, grads=True, dstate=None, discretization=None,
-              path=0, device="cuda"):
+              path=0, device="cuda", reverse_heads=0):
     """Run the fused op on the GPU through the public host API (and so the C ABI)."""
     from mamba_trainer_b200.ssm import Discretization, ScanInputs, SsmState, mamba3_scan
     names = [n for n in GRAD_NAMES if t.get(n) is not None]
     leaf = {n: t[n].detach().to(device).requires_grad_(grads) for n in names}
     inp = ScanInputs.new(leaf["x"], leaf["b"], leaf["c"], leaf["dt"], leaf["a_log"], leaf.get("lam"))
-    inp = inp.with_chunk_size(chunk).with_state_output(want_state).with_path(path)
+    inp = inp.with_chunk_size(chunk).with_state_output(want_state).with_path(path).with_reverse_heads(reverse_heads)
     if discretization is not None:
         inp = inp.with_discretization(discretization)
     if "theta" in leaf:

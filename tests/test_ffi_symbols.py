@@ -27,12 +27,35 @@ def test_library_builds_loads_and_exports_every_symbol():
     assert lib.m3_version().decode().count(".") == 2
 
 
-def test_struct_layouts_match_the_header():
-    # 12 int32 then 14 pointers; 4, 4 and 14 pointers.
-    assert ctypes.sizeof(_ffi.ScanDesc) == 12 * 4 + 14 * 8
-    assert ctypes.sizeof(_ffi.ScanOut) == 4 * 8
-    assert ctypes.sizeof(_ffi.ScanBwdIn) == 4 * 8
-    assert ctypes.sizeof(_ffi.ScanGrads) == 14 * 8
+def test_struct_layouts_match_the_header(tmp_path):
+    """Sizes and field offsets of every structure, as a C compiler lays out include/m3scan.h,
+    against the ctypes mirrors."""
+    import subprocess
+    pairs = [("m3_scan_desc", _ffi.ScanDesc, {"lambda": "lambda_"}), ("m3_scan_out", _ffi.ScanOut, {}),
+             ("m3_scan_bwd_in", _ffi.ScanBwdIn, {}), ("m3_scan_grads", _ffi.ScanGrads, {}),
+             ("m3_step_desc", _ffi.StepDesc, {"lambda": "lambda_"}), ("m3_step_out", _ffi.StepOut, {}),
+             ("m3_host_in", _ffi.HostIn, {"lambda": "lambda_"}), ("m3_host_out", _ffi.HostOut, {})]
+    inv = lambda ren: {v: k for k, v in ren.items()}
+    lines = ["#include <stdio.h>", "#include <stddef.h>", f'#include "{ROOT / "include" / "m3scan.h"}"', "int main(void) {"]
+    for cname, mirror, ren in pairs:
+        lines.append(f'  printf("{cname} size %zu\\n", sizeof({cname}));')
+        for fname, _ in mirror._fields_:
+            cf = inv(ren).get(fname, fname)
+            lines.append(f'  printf("{cname} {fname} %zu\\n", offsetof({cname}, {cf}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-std=c99", "-o", str(exe), str(src)], check=True)
+    got = {}
+    for ln in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines():
+        cname, field, val = ln.split()
+        got[(cname, field)] = int(val)
+    for cname, mirror, _ in pairs:
+        assert got[(cname, "size")] == ctypes.sizeof(mirror), cname
+        for fname, _ in mirror._fields_:
+            assert got[(cname, fname)] == getattr(mirror, fname).offset, (cname, fname)
+    assert ctypes.sizeof(_ffi.ScanDesc) == 14 * 4 + 14 * 8
 
 
 def test_scratch_size_query_needs_no_gpu():

@@ -128,6 +128,32 @@ def test_full_scan_matches_extended_recurrence(rank):
     assert rel_err(np.sin(out.angle.numpy()), np.sin(wa)) < 1e-9
 
 
+def test_bidirectional_form_walks_the_last_heads_right_to_left():
+    """models/mamba3.rs:352-370, :548-556: head by head, a reversed head equals the token-by-token
+    recurrence run over that head's tokens from the last to the first."""
+    rng = np.random.default_rng(7)
+    B, T, H, P, N, R = 2, 9, 4, 3, 4, 2
+    x, b, c = (rng.standard_normal((B, T, H, d, R)) for d in (P, N, N))
+    dt, lam = rng.uniform(0.05, 0.5, (B, T, H)), rng.uniform(0, 1, (B, T, H))
+    a_log, d_skip = rng.uniform(0, 1, H), rng.standard_normal(H)
+    theta = rng.uniform(0, 3, (B, T, H, N // 2))
+    h0, lu0 = rng.standard_normal((B, H, P, N)), rng.standard_normal((B, H, P, N))
+    ang0 = rng.uniform(-3, 3, (B, H, N // 2))
+    st = O.OracleState(T64(h0), T64(lu0), T64(ang0))
+    y, out = O.mamba3_scan_bidirectional(T64(x), T64(b), T64(c), T64(dt), T64(a_log), T64(lam), T64(theta),
+                                         T64(d_skip), st, 4, True, reverse_heads=2)
+    for h in range(H):
+        sl = slice(h, h + 1)
+        order = slice(None, None, -1) if h >= 2 else slice(None)
+        f = lambda v: np.ascontiguousarray(v[:, order][:, :, sl])
+        wy, wh, wu, wa = recurrence(f(x), f(b), f(c), f(dt), a_log[sl], f(lam), f(theta), d_skip[sl],
+                                    h0[:, sl], lu0[:, sl], ang0[:, sl])
+        assert rel_err(y[:, :, sl], wy[:, order]) < 1e-9, h
+        assert rel_err(out.h[:, sl], wh) < 1e-9 and rel_err(out.last_u[:, sl], wu) < 1e-9
+        assert rel_err(np.sin(out.angle[:, sl].numpy()), np.sin(wa)) < 1e-9
+    assert torch.equal(O.reverse_bands_in_time(O.reverse_bands_in_time(T64(x), 3), 3), T64(x))
+
+
 def test_split_windows_match_a_single_pass():
     """tests/ssm.rs:238-310."""
     case = Case(2, 12, 2, 3, 4)

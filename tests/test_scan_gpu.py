@@ -35,9 +35,9 @@ def check_bf16(name, a, e):
     assert rm <= 2e-2 * scale, f"{name}: reference metric {rm:.3e} (scale {scale:.2f})"
 
 
-def compare_all(t, chunk, check, want_state=True, dstate=None, discretization=None, path=0):
-    y, st, g = fused_run(t, chunk, want_state, True, dstate, discretization, path)
-    ey, est, eg = oracle_run(t, chunk, want_state, torch.float64, True, dstate)
+def compare_all(t, chunk, check, want_state=True, dstate=None, discretization=None, path=0, reverse_heads=0):
+    y, st, g = fused_run(t, chunk, want_state, True, dstate, discretization, path, reverse_heads=reverse_heads)
+    ey, est, eg = oracle_run(t, chunk, want_state, torch.float64, True, dstate, reverse_heads=reverse_heads)
     check("y", y, ey)
     if want_state:
         check("h", st.h, est.h.detach())
@@ -289,6 +289,50 @@ def test_tensor_core_backward(rank, rot, seq, state, disc):
           "last_u": torch.randn(w.batch, w.heads, 64, 128, generator=g) * 0.1,
           "angle": torch.randn(w.batch, w.heads, 64, generator=g) * 0.1 if rot else None}
     compare_all(t, w.chunk, check_bf16, True, ds, discretization=disc, path=2)
+
+
+# ---- bidirectional mixer: the last heads walk right to left (models/mamba3.rs:352-370, :548-556) -----
+
+@pytest.mark.parametrize("B,T,H,P,N,R,L,rot,state,rev", [
+    (2, 12, 4, 3, 4, 2, 4, True, True, 2),      # the mixer's own split: half the heads
+    (1, 13, 2, 3, 4, 1, 4, False, False, 2),    # every head reversed, ragged length
+    (2, 70, 3, 8, 16, 4, 32, True, True, 1),    # one trailing head, chunk cap in play
+    (1, 150, 2, 72, 80, 1, 64, False, True, 1),
+])
+def test_reversed_heads_match_the_oracle_f32(B, T, H, P, N, R, L, rot, state, rev):
+    t, ds = small_inputs(B, T, H, P, N, R, rot, state, seed=B * 100 + T + rev)
+    compare_all(t, L, check_f32, True, ds, reverse_heads=rev)
+
+
+@pytest.mark.parametrize("rank,rot,seq,state,rev", [
+    (1, False, 300, True, 1),
+    (1, True, 256, False, 2),
+    (2, True, 200, True, 1),
+    (4, True, 130, True, 1),
+])
+def test_reversed_heads_tensor_core(rank, rot, seq, state, rev):
+    w = tc_workload(rank, rot, seq, bc="rms" if rank == 1 else "scaled")
+    t = synthetic.make_inputs(w, seed=rank * 10 + seq + 7, with_state=state)
+    g = torch.Generator().manual_seed(seq)
+    ds = {"h": torch.randn(w.batch, w.heads, 64, 128, generator=g) * 0.1,
+          "last_u": torch.randn(w.batch, w.heads, 64, 128, generator=g) * 0.1,
+          "angle": torch.randn(w.batch, w.heads, 64, generator=g) * 0.1 if rot else None}
+    compare_all(t, w.chunk, check_bf16, True, ds, path=2, reverse_heads=rev)
+
+
+def test_reversed_heads_equal_flipped_inputs_bitwise():
+    """Walking a head right to left equals reversing that head's inputs, scanning left to right and
+    reversing its output: the same arithmetic in the same order, so the results are identical."""
+    from oracle.m3_oracle import reverse_bands_in_time as flip
+    w = tc_workload(2, True, 200)
+    t = synthetic.make_inputs(w, seed=3)
+    y, _, g = fused_run(t, w.chunk, False, True, reverse_heads=1)
+    tf = {k: (flip(v, 1) if k in ("x", "b", "c", "dt", "lam", "theta", "dy") else v) for k, v in t.items()}
+    yf, _, gf = fused_run(tf, w.chunk, False, True)
+    assert torch.equal(y.cpu(), flip(yf.cpu(), 1))
+    for n in ("x", "b", "c", "dt", "lam", "theta"):
+        assert torch.equal(g[n].cpu(), flip(gf[n].cpu(), 1)), n
+    assert torch.equal(g["a_log"], gf["a_log"]) and torch.equal(g["d_skip"], gf["d_skip"])
 
 
 # ---- ssd_chunked with the caller's own a, g, w (the reference's direct entry) ------------------------
