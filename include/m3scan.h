@@ -244,6 +244,33 @@ int m3_host_pipe_run(m3_host_pipe *pipe, const m3_host_in *in, const m3_host_out
 int m3_host_pipe_wait(m3_host_pipe *pipe, uint64_t ticket);
 int m3_host_pipe_destroy(m3_host_pipe *pipe);
 
+/* CausalConv1d::apply / apply_with_history (src/nn/conv.rs:143-213; kernels
+ * src/tensor/ops/fused.rs:780-1200) fused with the SiLU the mixer applies to its result
+ * (src/models/mamba3.rs:401): the step in front of the scan.
+ *   y[b,t,c] = act(bias[c] + sum_{delay < K} weight[K-1-delay, c] * x[b, t-delay, c])
+ * with x[t < 0] taken from `history` (the last K-1 inputs of the previous window) or zero.
+ * Rows may be strided: x is usually a column band of the input projection. */
+typedef struct {
+  int32_t batch, seq, channels;
+  int32_t kernel_size;   /* taps K, 1..8 */
+  int32_t dtype;         /* m3_dtype of x, history, y and their gradients */
+  int32_t activation;    /* 0 = none (the bare convolution), 1 = SiLU */
+  int64_t x_stride;      /* elements between consecutive time steps of x and dx; 0 = channels */
+  int64_t y_stride;      /* the same for y and dy; 0 = channels */
+  const void *x;         /* [batch, seq, channels] with row stride x_stride */
+  const void *history;   /* [batch, K-1, channels] dense, or NULL (zeros) */
+  const float *weight;   /* [K, channels] */
+  const float *bias;     /* [channels] or NULL */
+} m3_conv_desc;
+/* new_history (causal_conv1d_history): [batch, K-1, channels], the inputs the next window
+ * continues from; NULL skips it. */
+int m3_conv_forward(m3_ctx *ctx, const m3_conv_desc *desc, void *y, void *new_history);
+/* The adjoint; it recomputes the pre-activation from x, so the forward saves nothing.
+ * dx has x's strides; dweight [K, channels], dbias [channels] (float) and dhistory
+ * (like history) may each be NULL.  The parameter gradients are summed in a fixed order. */
+int m3_conv_backward(m3_ctx *ctx, const m3_conv_desc *desc, const void *dy, void *dx,
+                     float *dweight, float *dbias, void *dhistory);
+
 /* Bytes of device scratch a forward with this descriptor allocates (kept until
  * m3_saved_free when `saved` is requested). */
 size_t m3_scan_scratch_bytes(const m3_scan_desc *desc, int for_backward);

@@ -56,6 +56,11 @@ class StepOut(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("y", "h", "last_u", "angle")]
 
 
+class ConvDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("batch", "seq", "channels", "kernel_size", "dtype", "activation")] + [
+        ("x_stride", C.c_int64), ("y_stride", C.c_int64)] + [(n, C.c_void_p) for n in ("x", "history", "weight", "bias")]
+
+
 class HostIn(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("x", "b", "c", "dt", "lambda_", "theta", "dy")]
 
@@ -83,6 +88,9 @@ SYMBOLS = {
     "m3_scan_scratch_bytes": (C.c_size_t, [C.POINTER(ScanDesc), C.c_int]),
     "m3_step_forward": (C.c_int, [C.c_void_p, C.POINTER(StepDesc), C.POINTER(StepOut)]),
     "m3_scan_forward_noalloc": (C.c_int, [C.c_void_p, C.POINTER(ScanDesc), C.POINTER(ScanOut)]),
+    "m3_conv_forward": (C.c_int, [C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p]),
+    "m3_conv_backward": (C.c_int, [C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                   C.c_void_p]),
     "m3_host_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "m3_host_free": (C.c_int, [C.c_void_p]),
     "m3_host_pipe_create": (C.c_int, [C.c_void_p, C.POINTER(ScanDesc), C.c_int, C.POINTER(C.c_void_p)]),

@@ -1,0 +1,414 @@
+// Depthwise causal convolution over time followed by SiLU: the step in front of the scan
+// (CausalConv1d, src/nn/conv.rs:143-213, kernels src/tensor/ops/fused.rs:780-1200; the mixer
+// applies SiLU to its result, src/models/mamba3.rs:401).
+//
+//   pre[b,t,c] = bias[c] + sum_{delay < K} w[K-1-delay, c] * x[b, t-delay, c]      (x[t<0] = history or 0)
+//   y = silu(pre)  (or pre)
+//
+// HBM-bound: x is read once and y written once.  A thread owns one 16-byte vector of channels
+// and walks a run of time steps with the K-1 previous inputs in registers; the 32 lanes of a
+// warp cover 512 contiguous bytes of a row.  Rows may be strided (x is a column band of the
+// mixer's input projection).  The backward pass recomputes pre from x, so nothing is saved.
+#include <cuda_bf16.h>
+
+#include <initializer_list>
+
+#include "m3_internal.h"
+
+#define M3_CUDA(ctx, call)                                       \
+  do {                                                           \
+    cudaError_t e_ = (call);                                     \
+    if (e_ != cudaSuccess) return m3::cuda_fail(ctx, e_, #call); \
+  } while (0)
+
+namespace {
+
+constexpr int kMaxTaps = 8;
+constexpr int kRun = 16;     // time steps per thread
+constexpr int kLanesT = 8;   // threads of a block along time
+constexpr int kLanesC = 32;  // threads of a block along channel vectors
+
+template <class T, int V>
+struct Vec;
+template <>
+struct Vec<__nv_bfloat16, 8> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 q = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 q;
+    uint32_t* w = reinterpret_cast<uint32_t*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = q;
+  }
+};
+template <>
+struct Vec<float, 4> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 q = __ldg(reinterpret_cast<const float4*>(p));
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <class T>
+struct Vec<T, 1> {
+  static __device__ __forceinline__ void load(const T* p, float (&v)[1]) { v[0] = m3::ldf(p, 0); }
+  static __device__ __forceinline__ void store(T* p, const float (&v)[1]) { m3::stf(p, 0, v[0]); }
+};
+
+struct ConvDims {
+  int B, T, C, K;
+  long long xs, ys;  // elements between consecutive time steps of x (and dx) / of y (and dy)
+  int act;
+};
+
+__device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
+__device__ __forceinline__ float silu_grad(float v) {
+  const float s = 1.0f / (1.0f + __expf(-v));
+  return s * (1.0f + v * (1.0f - s));
+}
+
+// x of (b, t, channel vector c0): the sequence, the carried history for t < 0, or zero.
+template <class T, int V>
+__device__ __forceinline__ void load_x(const ConvDims& d, const T* x, const T* hist, int b, int t, int c0, float (&v)[V]) {
+  if (t >= 0 && t < d.T) {
+    Vec<T, V>::load(x + ((size_t)b * d.T + t) * d.xs + c0, v);
+  } else if (t < 0 && hist && t + (d.K - 1) >= 0) {
+    Vec<T, V>::load(hist + ((size_t)b * (d.K - 1) + (t + d.K - 1)) * d.C + c0, v);
+  } else {
+#pragma unroll
+    for (int i = 0; i < V; ++i) v[i] = 0.0f;
+  }
+}
+
+// The kernels are compiled for KT in {2, 4, 8} taps; a K-tap convolution runs as the KT-tap one
+// whose first KT-K taps are zero, so every loop over taps is static.
+template <class T, int V, int KT>
+__global__ void __launch_bounds__(kLanesT* kLanesC)
+    k_conv_fwd(ConvDims d, const T* __restrict__ x, const T* __restrict__ hist, const float* __restrict__ w,
+               const float* __restrict__ bias, T* __restrict__ y) {
+  const int c0 = (blockIdx.x * kLanesC + threadIdx.x) * V;
+  const int b = blockIdx.z;
+  const int t0 = (blockIdx.y * kLanesT + threadIdx.y) * kRun;
+  if (c0 >= d.C || t0 >= d.T) return;
+  const int pad = KT - d.K;
+  float wt[KT][V], bs[V], win[KT][V];  // win[k] pairs with tap k: x[t - (KT-1-k)]
+#pragma unroll
+  for (int k = 0; k < KT; ++k)
+#pragma unroll
+    for (int i = 0; i < V; ++i) wt[k][i] = (k >= pad) ? w[(size_t)(k - pad) * d.C + c0 + i] : 0.0f;
+#pragma unroll
+  for (int i = 0; i < V; ++i) bs[i] = bias ? bias[c0 + i] : 0.0f;
+#pragma unroll
+  for (int k = 0; k < KT - 1; ++k) load_x<T, V>(d, x, hist, b, t0 - (KT - 1) + k, c0, win[k + 1]);
+  const int t1 = min(t0 + kRun, d.T);
+#pragma unroll 4
+  for (int t = t0; t < t1; ++t) {
+#pragma unroll
+    for (int k = 0; k < KT - 1; ++k)
+#pragma unroll
+      for (int i = 0; i < V; ++i) win[k][i] = win[k + 1][i];
+    Vec<T, V>::load(x + ((size_t)b * d.T + t) * d.xs + c0, win[KT - 1]);
+    float acc[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = bs[i];
+#pragma unroll
+    for (int k = 0; k < KT; ++k)
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = fmaf(wt[k][i], win[k][i], acc[i]);
+    if (d.act) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = silu(acc[i]);
+    }
+    Vec<T, V>::store(y + ((size_t)b * d.T + t) * d.ys + c0, acc);
+  }
+}
+
+// The K-1 inputs a later window continues from (causal_conv1d_history): the tail of [history; x].
+template <class T>
+__global__ void k_conv_history(ConvDims d, const T* __restrict__ x, const T* __restrict__ hist, T* __restrict__ out) {
+  const size_t n = (size_t)d.B * (d.K - 1) * d.C;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = i % d.C, j = (i / d.C) % (d.K - 1), b = i / ((size_t)d.C * (d.K - 1));
+    const int t = d.T - (d.K - 1) + j;
+    float v = 0.0f;
+    if (t >= 0) v = m3::ldf(x, ((size_t)b * d.T + t) * d.xs + c);
+    else if (hist && t + (d.K - 1) >= 0) v = m3::ldf(hist, ((size_t)b * (d.K - 1) + (t + d.K - 1)) * d.C + c);
+    m3::stf(out, i, v);
+  }
+}
+
+// Backward: g = dy * act'(pre) with pre recomputed; dx[t] = sum_delay w[K-1-delay] g[t+delay];
+// per-block partial sums of dw[k] = sum g[t] x[t-(K-1-k)] and dbias = sum g[t].
+template <class T, int V, int KT>
+__global__ void __launch_bounds__(kLanesT* kLanesC)
+    k_conv_bwd(ConvDims d, const T* __restrict__ x, const T* __restrict__ hist, const float* __restrict__ w,
+               const float* __restrict__ bias, const T* __restrict__ dy, T* __restrict__ dx, T* __restrict__ dhist,
+               float* __restrict__ part) {
+  __shared__ float red[kLanesT][kLanesC * V + 1];
+  const int c0 = (blockIdx.x * kLanesC + threadIdx.x) * V;
+  const int b = blockIdx.z;
+  const int t0 = (blockIdx.y * kLanesT + threadIdx.y) * kRun;
+  const bool active = c0 < d.C && t0 < d.T;
+  const int pad = KT - d.K;
+  float pw[KT][V], pb[V];
+#pragma unroll
+  for (int k = 0; k < KT; ++k)
+#pragma unroll
+    for (int i = 0; i < V; ++i) pw[k][i] = 0.0f;
+#pragma unroll
+  for (int i = 0; i < V; ++i) pb[i] = 0.0f;
+  if (active) {
+    float wt[KT][V], bs[V], win[KT][V], gw[KT][V];  // gw[j] = g[s - (KT-1) + j] after step s
+#pragma unroll
+    for (int k = 0; k < KT; ++k)
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        wt[k][i] = (k >= pad) ? w[(size_t)(k - pad) * d.C + c0 + i] : 0.0f;
+        gw[k][i] = 0.0f;
+      }
+#pragma unroll
+    for (int i = 0; i < V; ++i) bs[i] = bias ? bias[c0 + i] : 0.0f;
+#pragma unroll
+    for (int k = 0; k < KT - 1; ++k) load_x<T, V>(d, x, hist, b, t0 - (KT - 1) + k, c0, win[k + 1]);
+    const int t1 = min(t0 + kRun, d.T);
+    // s walks the run plus KT-1 steps of look-ahead; dx[s-(KT-1)] is complete once g[s] is known.
+    const int s_end = t1 + KT - 1;
+    const int emit_from = (t0 == 0 && dhist) ? -(d.K - 1) : t0;
+    for (int s = t0; s < s_end; ++s) {
+#pragma unroll
+      for (int k = 0; k < KT - 1; ++k)
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          win[k][i] = win[k + 1][i];
+          gw[k][i] = gw[k + 1][i];
+        }
+      if (s < d.T) {
+        float gy[V], acc[V];
+        Vec<T, V>::load(x + ((size_t)b * d.T + s) * d.xs + c0, win[KT - 1]);
+        Vec<T, V>::load(dy + ((size_t)b * d.T + s) * d.ys + c0, gy);
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = bs[i];
+#pragma unroll
+        for (int k = 0; k < KT; ++k)
+#pragma unroll
+          for (int i = 0; i < V; ++i) acc[i] = fmaf(wt[k][i], win[k][i], acc[i]);
+#pragma unroll
+        for (int i = 0; i < V; ++i) gw[KT - 1][i] = d.act ? gy[i] * silu_grad(acc[i]) : gy[i];
+        if (s < t1) {  // this thread's own steps feed the parameter gradients (each step exactly once)
+#pragma unroll
+          for (int k = 0; k < KT; ++k)
+#pragma unroll
+            for (int i = 0; i < V; ++i) pw[k][i] = fmaf(gw[KT - 1][i], win[k][i], pw[k][i]);
+#pragma unroll
+          for (int i = 0; i < V; ++i) pb[i] += gw[KT - 1][i];
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) gw[KT - 1][i] = 0.0f;
+      }
+      const int te = s - (KT - 1);  // dx[te] = sum_delay w[KT-1-delay] g[te+delay] = sum_j w[KT-1-j] gw[j]
+      if (te >= emit_from && te < t1) {
+        float o[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) o[i] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < KT; ++j)
+#pragma unroll
+          for (int i = 0; i < V; ++i) o[i] = fmaf(wt[KT - 1 - j][i], gw[j][i], o[i]);
+        if (te >= 0) {
+          if (dx) Vec<T, V>::store(dx + ((size_t)b * d.T + te) * d.xs + c0, o);
+        } else {
+          Vec<T, V>::store(dhist + ((size_t)b * (d.K - 1) + (te + d.K - 1)) * d.C + c0, o);
+        }
+      }
+    }
+  }
+  if (!part) return;
+  // Block partials: sum the kLanesT time lanes in a fixed order, one (tap | bias) slice at a time.
+  const size_t blk = (size_t)blockIdx.z * gridDim.y + blockIdx.y;
+#pragma unroll
+  for (int k = 0; k <= KT; ++k) {
+    if (k < pad) continue;  // a padding tap has no gradient
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < V; ++i) red[threadIdx.y][threadIdx.x * V + i] = (k == KT) ? pb[i] : pw[k < KT ? k : 0][i];
+    __syncthreads();
+    if (threadIdx.y == 0 && c0 < d.C) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        float s = 0.0f;
+#pragma unroll
+        for (int ty = 0; ty < kLanesT; ++ty) s += red[ty][threadIdx.x * V + i];
+        part[(blk * (d.K + 1) + (k - pad)) * d.C + c0 + i] = s;
+      }
+    }
+  }
+}
+
+// dw[k, c] / dbias[c] = sum over the blocks' partials, in block order.
+__global__ void k_conv_reduce(int nblk, int K, int C, const float* __restrict__ part, float* __restrict__ dw,
+                              float* __restrict__ dbias) {
+  const size_t n = (size_t)(K + 1) * C;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float s = 0.0f;
+    for (int j = 0; j < nblk; ++j) s += part[(size_t)j * n + i];
+    const int k = i / C;
+    if (k < K) {
+      if (dw) dw[i] = s;
+    } else if (dbias) {
+      dbias[i - (size_t)K * C] = s;
+    }
+  }
+}
+
+int check(m3_ctx* ctx, const m3_conv_desc* c, ConvDims* d) {
+  if (!ctx || !c) return M3_ERR_NULL;
+  if (c->batch <= 0 || c->seq < 0 || c->channels <= 0)
+    return m3::fail(ctx, M3_ERR_SHAPE, "conv extents must be positive (batch %d seq %d channels %d)", c->batch, c->seq, c->channels);
+  if (c->kernel_size < 1 || c->kernel_size > kMaxTaps)
+    return m3::fail(ctx, M3_ERR_UNSUPPORTED, "kernel_size %d outside [1, %d]", c->kernel_size, kMaxTaps);
+  if (c->dtype != M3_F32 && c->dtype != M3_BF16) return m3::fail(ctx, M3_ERR_UNSUPPORTED, "dtype %d", c->dtype);
+  if (!c->x || !c->weight) return m3::fail(ctx, M3_ERR_NULL, "x and weight are required");
+  d->B = c->batch; d->T = c->seq; d->C = c->channels; d->K = c->kernel_size;
+  d->xs = c->x_stride ? c->x_stride : c->channels;
+  d->ys = c->y_stride ? c->y_stride : c->channels;
+  if (d->xs < c->channels || d->ys < c->channels) return m3::fail(ctx, M3_ERR_SHAPE, "row strides below the channel count");
+  d->act = c->activation ? 1 : 0;
+  return M3_OK;
+}
+
+bool vector_ok(const ConvDims& d, int V, int es, std::initializer_list<const void*> ptrs) {
+  if (d.C % V || d.xs % V || d.ys % V) return false;
+  for (const void* p : ptrs)
+    if (p && (reinterpret_cast<uintptr_t>(p) % (size_t)(V * es))) return false;
+  return true;
+}
+
+template <class T, int V>
+cudaError_t fwd_launch(cudaStream_t st, const ConvDims& d, const m3_conv_desc& c, void* y) {
+  const dim3 block(kLanesC, kLanesT);
+  const dim3 grid((d.C / V + kLanesC - 1) / kLanesC, (d.T + kLanesT * kRun - 1) / (kLanesT * kRun), d.B);
+  const T* x = static_cast<const T*>(c.x);
+  const T* h = static_cast<const T*>(c.history);
+  if (d.K <= 2) k_conv_fwd<T, V, 2><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<T*>(y));
+  else if (d.K <= 4) k_conv_fwd<T, V, 4><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<T*>(y));
+  else k_conv_fwd<T, V, kMaxTaps><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<T*>(y));
+  return cudaGetLastError();
+}
+
+template <class T, int V>
+cudaError_t bwd_launch(cudaStream_t st, const ConvDims& d, const m3_conv_desc& c, const void* dy, void* dx, void* dhist,
+                       float* part, dim3* grid_out) {
+  const dim3 block(kLanesC, kLanesT);
+  const dim3 grid((d.C / V + kLanesC - 1) / kLanesC, (d.T + kLanesT * kRun - 1) / (kLanesT * kRun), d.B);
+  *grid_out = grid;
+  const T* x = static_cast<const T*>(c.x);
+  const T* h = static_cast<const T*>(c.history);
+  if (d.K <= 2)
+    k_conv_bwd<T, V, 2><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<const T*>(dy), static_cast<T*>(dx),
+                                                 static_cast<T*>(dhist), part);
+  else if (d.K <= 4)
+    k_conv_bwd<T, V, 4><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<const T*>(dy), static_cast<T*>(dx),
+                                                 static_cast<T*>(dhist), part);
+  else
+    k_conv_bwd<T, V, kMaxTaps><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<const T*>(dy),
+                                                        static_cast<T*>(dx), static_cast<T*>(dhist), part);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" {
+
+int m3_conv_forward(m3_ctx* ctx, const m3_conv_desc* c, void* y, void* new_history) {
+  ConvDims d;
+  const int rc = check(ctx, c, &d);
+  if (rc != M3_OK) return rc;
+  if (!y) return m3::fail(ctx, M3_ERR_NULL, "y is required");
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaError_t e = cudaSuccess;
+  if (d.T > 0) {
+    if (c->dtype == M3_BF16) {
+      e = vector_ok(d, 8, 2, {c->x, c->history, y}) ? fwd_launch<__nv_bfloat16, 8>(ctx->stream, d, *c, y)
+                                                     : fwd_launch<__nv_bfloat16, 1>(ctx->stream, d, *c, y);
+    } else {
+      e = vector_ok(d, 4, 4, {c->x, c->history, y}) ? fwd_launch<float, 4>(ctx->stream, d, *c, y)
+                                                     : fwd_launch<float, 1>(ctx->stream, d, *c, y);
+    }
+    if (e != cudaSuccess) return m3::cuda_fail(ctx, e, "conv forward");
+    ctx->launches += 1;
+  }
+  if (new_history && d.K > 1) {
+    const size_t n = (size_t)d.B * (d.K - 1) * d.C;
+    const int blocks = (int)((n + 255) / 256 < 1024 ? (n + 255) / 256 : 1024);
+    if (c->dtype == M3_BF16)
+      k_conv_history<__nv_bfloat16><<<blocks, 256, 0, ctx->stream>>>(d, static_cast<const __nv_bfloat16*>(c->x),
+                                                                      static_cast<const __nv_bfloat16*>(c->history),
+                                                                      static_cast<__nv_bfloat16*>(new_history));
+    else
+      k_conv_history<float><<<blocks, 256, 0, ctx->stream>>>(d, static_cast<const float*>(c->x),
+                                                              static_cast<const float*>(c->history),
+                                                              static_cast<float*>(new_history));
+    M3_CUDA(ctx, cudaGetLastError());
+    ctx->launches += 1;
+  }
+  return M3_OK;
+}
+
+int m3_conv_backward(m3_ctx* ctx, const m3_conv_desc* c, const void* dy, void* dx, float* dweight, float* dbias,
+                     void* dhistory) {
+  ConvDims d;
+  const int rc = check(ctx, c, &d);
+  if (rc != M3_OK) return rc;
+  if (!dy) return m3::fail(ctx, M3_ERR_NULL, "dy is required");
+  if (dhistory && !c->history) return m3::fail(ctx, M3_ERR_NULL, "dhistory without a history");
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  const bool want_par = dweight || (dbias && c->bias);
+  if (d.T == 0) {
+    if (dweight) M3_CUDA(ctx, cudaMemsetAsync(dweight, 0, (size_t)d.K * d.C * sizeof(float), ctx->stream));
+    if (dbias) M3_CUDA(ctx, cudaMemsetAsync(dbias, 0, (size_t)d.C * sizeof(float), ctx->stream));
+    if (dhistory) M3_CUDA(ctx, cudaMemsetAsync(dhistory, 0, (size_t)d.B * (d.K - 1) * d.C * (c->dtype == M3_BF16 ? 2 : 4), ctx->stream));
+    return M3_OK;
+  }
+  const int nblk = d.B * ((d.T + kLanesT * kRun - 1) / (kLanesT * kRun));
+  float* part = nullptr;
+  if (want_par)
+    M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&part), (size_t)nblk * (d.K + 1) * d.C * sizeof(float), ctx->stream));
+  dim3 grid;
+  cudaError_t e;
+  if (c->dtype == M3_BF16) {
+    e = vector_ok(d, 8, 2, {c->x, c->history, dy, dx, dhistory})
+            ? bwd_launch<__nv_bfloat16, 8>(ctx->stream, d, *c, dy, dx, dhistory, part, &grid)
+            : bwd_launch<__nv_bfloat16, 1>(ctx->stream, d, *c, dy, dx, dhistory, part, &grid);
+  } else {
+    e = vector_ok(d, 4, 4, {c->x, c->history, dy, dx, dhistory})
+            ? bwd_launch<float, 4>(ctx->stream, d, *c, dy, dx, dhistory, part, &grid)
+            : bwd_launch<float, 1>(ctx->stream, d, *c, dy, dx, dhistory, part, &grid);
+  }
+  ctx->launches += 1;
+  if (e == cudaSuccess && want_par) {
+    const size_t n = (size_t)(d.K + 1) * d.C;
+    k_conv_reduce<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(nblk, d.K, d.C, part, dweight, c->bias ? dbias : nullptr);
+    e = cudaGetLastError();
+    ctx->launches += 1;
+  }
+  cudaError_t e2 = part ? cudaFreeAsync(part, ctx->stream) : cudaSuccess;
+  if (e != cudaSuccess) return m3::cuda_fail(ctx, e, "conv backward");
+  if (e2 != cudaSuccess) return m3::cuda_fail(ctx, e2, "cudaFreeAsync");
+  return M3_OK;
+}
+
+}  // extern "C"

@@ -30,12 +30,12 @@ def _hp(t: Optional[torch.Tensor]):
 
 class HostScanPipeline:
     """Reusable pipeline for one problem shape.  `host` tensors must be pinned for the copies to
-    be asynchronous; outputs are written into pinned tensors owned by the pipeline (two sets,
-    used alternately, so the results of one run stay valid while the next run is in flight)."""
+    be asynchronous; outputs are written into pinned tensors owned by the pipeline (`depth` sets,
+    used in turn, so the results of one run stay valid while the next depth-1 runs are in flight)."""
 
     def __init__(self, host: Dict[str, Optional[torch.Tensor]], chunk: int, discretization: Discretization,
                  device, slices: int = 4, params: Optional[Dict[str, torch.Tensor]] = None,
-                 path: int = _ffi.PATH_AUTO):
+                 path: int = _ffi.PATH_AUTO, depth: int = 2):
         self.dev = torch.device(device)
         self.chunk, self.disc = chunk, Discretization(discretization)
         self.names = [n for n in _PER_TOKEN if host.get(n) is not None]
@@ -48,8 +48,9 @@ class HostScanPipeline:
         self.rot = "theta" in self.names
         self.slices = max(1, min(slices, B))
         self.grad_names = [n for n in self.names if n != "dy"]
+        self.depth = max(1, int(depth))
         self._outs = []
-        for _ in range(2):
+        for _ in range(self.depth):
             out = {"y": torch.empty(x.shape, dtype=x.dtype).pin_memory()}
             for n in self.grad_names:
                 out["d" + n] = torch.empty(host[n].shape, dtype=host[n].dtype).pin_memory()
@@ -91,7 +92,7 @@ class HostScanPipeline:
                 self._params[1] is not None and params["d_skip"].data_ptr() != self._params[1].data_ptr()):
             raise ValueError("the pipeline was created for other parameter tensors")
         self._ctx.bind_current_stream()
-        out = self._outs[self._runs % 2]
+        out = self._outs[self._runs % self.depth]
         hin = _ffi.HostIn(x=_hp(host["x"]), b=_hp(host["b"]), c=_hp(host["c"]), dt=_hp(host["dt"]),
                           lambda_=_hp(host.get("lam")) if "lam" in self.names else None,
                           theta=_hp(host.get("theta")) if self.rot else None, dy=_hp(host["dy"]))

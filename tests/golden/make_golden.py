@@ -97,6 +97,59 @@ def mixer_tail_case(ref):
              **{f"d_{n}": v.numpy() for n, v in zip(names, grads)})
 
 
+def mixer_core_case(ref):
+    """Everything the reference's mixer port does between its two projections
+    (bench/torch_mamba3.py:165-207), run through the port's own Mamba3Mixer.forward in float64:
+    split, depthwise causal convolution (:175), SiLU, B/C bias + RMS norm, softplus / sigmoid,
+    angles and rotations, ssd_chunked, D skip, the SiLU(z) gate.  The projection's output and the
+    output projection's input are captured with hooks; parameters get non-trivial values."""
+    torch.manual_seed(0)
+    d_model, H, P, N, chunk, K = 16, 2, 4, 6, 4, 4
+    B, T = 2, 11
+    m = ref.Mamba3Mixer(d_model, H, P, N, chunk, conv_kernel=K).double()
+    noise = lambda shape, seed, s=1.0: torch.tensor(s * lcg_noise(int(np.prod(shape)), seed).reshape(shape), dtype=torch.float64)
+    with torch.no_grad():
+        m.conv.weight.copy_(noise(m.conv.weight.shape, 31, 0.6))
+        m.conv.bias.copy_(noise(m.conv.bias.shape, 32, 0.3))
+        m.dt_bias.copy_(noise((H,), 33) - 1.5)
+        m.a_log.copy_(noise((H,), 34, 0.5) + 0.5)
+        m.d_skip.copy_(noise((H,), 35))
+        m.b_bias.copy_(noise((H, N), 36, 0.4))
+        m.c_bias.copy_(noise((H, N), 37, 0.4))
+        m.bc_norm.weight.copy_(1.0 + noise((N,), 38, 0.3))
+    cap = {}
+    def grab_proj(_mod, _inp, out):
+        out.retain_grad()
+        cap["proj"] = out
+    def grab_gated(_mod, inp):
+        inp[0].retain_grad()
+        cap["gated"] = inp[0]
+    h1 = m.in_proj.register_forward_hook(grab_proj)
+    h2 = m.out_proj.register_forward_pre_hook(grab_gated)
+    u = noise((B, T, d_model), 39, 2.0)
+    m(u)
+    h1.remove(); h2.remove()
+    gated, proj = cap["gated"], cap["proj"]
+    dgated = noise(tuple(gated.shape), 40)
+    params = {"conv_w": m.conv.weight, "conv_b": m.conv.bias, "dt_bias": m.dt_bias, "a_log": m.a_log,
+              "d_skip": m.d_skip, "b_bias": m.b_bias, "c_bias": m.c_bias, "norm_w": m.bc_norm.weight}
+    grads = torch.autograd.grad((gated * dgated).sum(), [proj] + list(params.values()))
+    np.savez(HERE / "mixer_core.npz", dims=np.array([B, T, H, P, N]), chunk=chunk, kernel=K, eps=m.bc_norm.eps,
+             proj=proj.detach().numpy(), gated=gated.detach().numpy(), dgated=dgated.numpy(),
+             dproj=grads[0].numpy(),
+             **{n: v.detach().numpy() for n, v in params.items()},
+             **{f"d_{n}": g.numpy() for n, g in zip(params, grads[1:])})
+    # the convolution + SiLU step alone, as the port's forward applies it (:175-176)
+    d_inner, bc = H * P, H * N
+    xbc = proj.detach()[..., d_inner:2 * d_inner + 2 * bc].clone().requires_grad_(True)
+    y = torch.nn.functional.silu(m.conv(xbc.transpose(1, 2))[..., :T].transpose(1, 2))
+    dy = noise(tuple(y.shape), 41)
+    gx, gw, gb = torch.autograd.grad((y * dy).sum(), [xbc, m.conv.weight, m.conv.bias])
+    np.savez(HERE / "conv_silu.npz", x=xbc.detach().numpy(), w=m.conv.weight.detach().numpy(),
+             b=m.conv.bias.detach().numpy(), y=y.detach().numpy(), dy=dy.numpy(), dx=gx.numpy(), dw=gw.numpy(),
+             db=gb.numpy())
+
+
 def main():
     root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
     ref = load_reference(root)
@@ -106,6 +159,7 @@ def main():
     ssd_case(ref, "ssd_chunked_one_chunk", (1, 7, 2, 3, 4), 16)
     rotate_case(ref)
     mixer_tail_case(ref)
+    mixer_core_case(ref)
     print("wrote", sorted(p.name for p in HERE.glob("*.npz")))
 
 

@@ -1,0 +1,44 @@
+"""Pin the CPU restatement of the mixer steps around the scan against the reference port's outputs."""
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from oracle import mixer as M
+
+GOLD = Path(__file__).resolve().parent / "golden"
+T64 = lambda a, g=False: torch.tensor(np.asarray(a, dtype=np.float64), requires_grad=g)
+
+
+def rel_err(a, e):
+    a, e = np.asarray(a, dtype=np.float64), np.asarray(e, dtype=np.float64)
+    return float(np.max(np.abs(a - e) / (1.0 + np.abs(e)))) if a.size else 0.0
+
+
+def conv_golden():
+    z = np.load(GOLD / "conv_silu.npz")
+    # the port keeps the taps as nn.Conv1d does, [C, 1, K]; tap k of [K, C] is w[:, 0, k]
+    return z, np.ascontiguousarray(z["w"][:, 0, :].T)
+
+
+def test_conv_silu_matches_reference_port():
+    z, w = conv_golden()
+    x, wt, b = T64(z["x"], True), T64(w, True), T64(z["b"], True)
+    y, hist = M.causal_conv1d(x, wt, b)
+    assert rel_err(y.detach(), z["y"]) < 1e-13
+    dx, dw, db = torch.autograd.grad((y * T64(z["dy"])).sum(), [x, wt, b])
+    assert rel_err(dx, z["dx"]) < 1e-13 and rel_err(db, z["db"]) < 1e-13
+    assert rel_err(dw, z["dw"][:, 0, :].T) < 1e-12
+    assert torch.equal(hist, x.detach()[:, -3:])
+
+
+def test_conv_windows_with_history_equal_one_pass():
+    """tests of apply_with_history in the reference (src/nn/conv.rs:185-203): two windows, the
+    second continued from the first's history, equal the whole sequence."""
+    z, w = conv_golden()
+    x, wt, b = T64(z["x"]), T64(w), T64(z["b"])
+    full, _ = M.causal_conv1d(x, wt, b)
+    y1, h1 = M.causal_conv1d(x[:, :2], wt, b)          # shorter than the K-1 = 3 taps of history
+    y2, h2 = M.causal_conv1d(x[:, 2:7], wt, b, h1)
+    y3, _ = M.causal_conv1d(x[:, 7:], wt, b, h2)
+    assert rel_err(torch.cat([y1, y2, y3], 1), full) < 1e-14

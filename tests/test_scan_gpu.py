@@ -510,3 +510,79 @@ def test_step_matches_the_chunked_scan(rank, dtype):
     assert ref_metric(y_step.float(), y_scan.float()) <= tol
     assert ref_metric(state.h, st_scan.h) <= tol and ref_metric(state.last_u, st_scan.last_u) <= tol
     assert angle_close(state.angle, st_scan.angle, 1e-3)
+
+
+# ---- depthwise causal convolution + SiLU, the step in front of the scan (src/nn/conv.rs) ------------------
+
+def _conv_case(B, T, Cn, K, seed, dtype=torch.float32, history=True, bias=True):
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s: torch.randn(*s, generator=g)
+    t = {"x": r(B, T, Cn).to(dtype), "w": r(K, Cn) * 0.5, "b": r(Cn) * 0.3 if bias else None,
+         "h": r(B, K - 1, Cn).to(dtype) if history else None, "dy": r(B, T, Cn).to(dtype)}
+    return t
+
+
+def _conv_compare(t, activation, rtol, atol):
+    from mamba_trainer_b200.nn import causal_conv1d
+    from oracle.mixer import causal_conv1d as oracle_conv
+    names = [n for n in ("x", "w", "b", "h") if t[n] is not None]
+    dev = {n: t[n].cuda().requires_grad_(True) for n in names}
+    y, hist = causal_conv1d(dev["x"], dev["w"], dev.get("b"), dev.get("h"), activation, want_history=True)
+    gr = torch.autograd.grad(y, [dev[n] for n in names], grad_outputs=t["dy"].cuda())
+    cpu = {n: t[n].double().requires_grad_(True) for n in names}
+    ey, ehist = oracle_conv(cpu["x"], cpu["w"], cpu.get("b"), cpu.get("h"), activation)
+    eg = torch.autograd.grad(ey, [cpu[n] for n in names], grad_outputs=t["dy"].double())
+    assert allclose_excess(y.float(), ey.detach(), rtol, atol) <= 1.0, "y"
+    assert torch.equal(hist.cpu().double(), ehist.detach()), "history"
+    for n, a_, e_ in zip(names, gr, eg):
+        assert allclose_excess(a_.float(), e_, rtol, atol * max(1.0, float(e_.abs().max()))) <= 1.0, "d" + n
+
+
+@pytest.mark.parametrize("B,T,Cn,K,history,bias,activation", [
+    (2, 37, 24, 4, True, True, True),      # vector path, ragged run
+    (1, 300, 8, 4, False, True, True),     # several time blocks
+    (2, 2, 12, 4, True, False, True),      # shorter than the history
+    (3, 50, 10, 3, True, True, False),     # scalar path (channels not a multiple of the vector), bare convolution
+    (2, 19, 16, 1, False, True, True),     # a single tap
+    (1, 40, 8, 2, True, True, True),
+    (2, 33, 16, 7, True, True, True),      # the wide-kernel instantiation
+])
+def test_conv_silu_matches_the_oracle_f32(B, T, Cn, K, history, bias, activation):
+    _conv_compare(_conv_case(B, T, Cn, K, seed=T + K, history=history, bias=bias), activation, 1e-4, 1e-5)
+
+
+def test_conv_silu_bf16_on_a_column_band():
+    """bf16 activations, x a column band of a wider projection (row stride > channels)."""
+    from mamba_trainer_b200.nn import causal_conv1d
+    from oracle.mixer import causal_conv1d as oracle_conv
+    g = torch.Generator().manual_seed(9)
+    B, T, W, Cn, K = 2, 130, 96, 64, 4
+    proj = torch.randn(B, T, W, generator=g).bfloat16()
+    w, b = torch.randn(K, Cn, generator=g) * 0.5, torch.randn(Cn, generator=g) * 0.3
+    dy = torch.randn(B, T, Cn, generator=g).bfloat16()
+    pd = proj.cuda().requires_grad_(True)
+    wd, bd = w.cuda().requires_grad_(True), b.cuda().requires_grad_(True)
+    y = causal_conv1d(pd[..., 16:16 + Cn], wd, bd)
+    gp, gw, gb = torch.autograd.grad(y, [pd, wd, bd], grad_outputs=dy.cuda())
+    pc = proj.double().requires_grad_(True)
+    wc, bc = w.double().requires_grad_(True), b.double().requires_grad_(True)
+    ey, _ = oracle_conv(pc[..., 16:16 + Cn], wc, bc)
+    ep, ew, eb = torch.autograd.grad(ey, [pc, wc, bc], grad_outputs=dy.double())
+    check_bf16("y", y, ey.detach())
+    check_bf16("dx", gp, ep)
+    check_bf16("dw", gw, ew)
+    check_bf16("db", gb, eb)
+
+
+def test_conv_silu_replays_the_reference_ports_vectors():
+    from pathlib import Path
+    from mamba_trainer_b200.nn import causal_conv1d
+    z = np.load(Path(__file__).resolve().parent / "golden" / "conv_silu.npz")
+    f = lambda a: torch.tensor(np.asarray(a), dtype=torch.float32).cuda().requires_grad_(True)
+    x, w, b = f(z["x"]), f(np.ascontiguousarray(z["w"][:, 0, :].T)), f(z["b"])
+    y = causal_conv1d(x, w, b)
+    dx, dw, db = torch.autograd.grad(y, [x, w, b], grad_outputs=f(z["dy"]).detach())
+    check_f32("y", y, torch.tensor(z["y"]))
+    check_f32("dx", dx, torch.tensor(z["dx"]))
+    check_f32("dw", dw, torch.tensor(np.ascontiguousarray(z["dw"][:, 0, :].T)))
+    check_f32("db", db, torch.tensor(z["db"]))
