@@ -261,6 +261,14 @@ typedef struct {
   const void *history;   /* [batch, K-1, channels] dense, or NULL (zeros) */
   const float *weight;   /* [K, channels] */
   const float *bias;     /* [channels] or NULL */
+  /* Optional second output: channels [split, channels) go to y2 (the forward's second result,
+   * row stride y2_stride, 0 = channels - split) instead of y, and the backward reads their
+   * gradient from dy2 - the mixer's x | B C cut (src/models/mamba3.rs:403-406) without a copy.
+   * split = 0: everything in y / dy. */
+  int32_t split, reserved0;
+  int64_t y2_stride;
+  void *y2;
+  const void *dy2;
 } m3_conv_desc;
 /* new_history (causal_conv1d_history): [batch, K-1, channels], the inputs the next window
  * continues from; NULL skips it. */
@@ -270,6 +278,54 @@ int m3_conv_forward(m3_ctx *ctx, const m3_conv_desc *desc, void *y, void *new_hi
  * (like history) may each be NULL.  The parameter gradients are summed in a fixed order. */
 int m3_conv_backward(m3_ctx *ctx, const m3_conv_desc *desc, const void *dy, void *dx,
                      float *dweight, float *dbias, void *dhistory);
+
+/* B and C on their way from the convolution to the scan (src/models/mamba3.rs:409-436): expand
+ * groups to heads, add the per-head bias, RMS-normalise over d_state (RmsNorm, src/nn/norm.rs:95-105)
+ * and permute to the scan's rank-last layout - one launch per tensor instead of about six.
+ *   v = raw[b, t, h / (heads/groups), r, :] + bias[h, :];   out[b, t, h, :, r] = v * rsqrt(mean(v^2) + eps) * weight */
+typedef struct {
+  int32_t batch, seq, heads, groups, d_state, rank;
+  int32_t dtype;              /* m3_dtype of the raw rows, b, c and their gradients */
+  int32_t has_norm;           /* 0: no bc_norm (bias only) */
+  float eps;                  /* RmsNorm eps */
+  int32_t reserved0;
+  int64_t raw_stride;         /* elements between consecutive tokens of b_raw / c_raw; 0 = groups*rank*d_state */
+  const void *b_raw, *c_raw;  /* [batch, seq, groups, rank, d_state] with token stride raw_stride */
+  const float *b_bias, *c_bias; /* [heads, d_state] or NULL */
+  const float *norm_weight;   /* [d_state] or NULL (no gain) */
+} m3_bc_desc;
+/* b, c: [batch, seq, heads, d_state, rank], the layout m3_scan_desc wants. */
+int m3_bc_forward(m3_ctx *ctx, const m3_bc_desc *desc, void *b, void *c);
+/* db_raw / dc_raw have the raw rows' strides (the gradient of a group sums its heads); db_bias,
+ * dc_bias [heads, d_state] and dnorm_weight [d_state] (one gain shared by B and C) are float and
+ * may be NULL.  Sums run in a fixed order. */
+int m3_bc_backward(m3_ctx *ctx, const m3_bc_desc *desc, const void *db, const void *dc,
+                   void *db_raw, void *dc_raw, float *db_bias, float *dc_bias, float *dnorm_weight);
+
+/* dt = softplus(dt_raw + dt_bias[h]), lambda = sigmoid(lambda_raw) (src/models/mamba3.rs:440-446). */
+typedef struct {
+  int32_t batch, seq, heads;
+  int32_t dtype;
+  int64_t stride;             /* elements between consecutive tokens of dt_raw / lambda_raw; 0 = heads */
+  const void *dt_raw;         /* [batch, seq, heads] with token stride `stride` */
+  const void *lambda_raw;     /* likewise, or NULL */
+  const float *dt_bias;       /* [heads] or NULL */
+} m3_act_desc;
+int m3_dt_lambda_forward(m3_ctx *ctx, const m3_act_desc *desc, void *dt, void *lambda);
+int m3_dt_lambda_backward(m3_ctx *ctx, const m3_act_desc *desc, const void *ddt, const void *dlambda,
+                          void *ddt_raw, void *dlambda_raw, float *ddt_bias);
+
+/* The gate behind the scan: out = y * silu(z) (Mamba3Mixer::finish without post_gate_norm,
+ * src/models/mamba3.rs:475-484).  y, out, dout, dy are dense [batch, seq, channels]; z and dz
+ * may be column bands of the input projection (row stride z_stride, 0 = channels). */
+typedef struct {
+  int32_t batch, seq, channels;
+  int32_t dtype;
+  int64_t z_stride;
+  const void *y, *z;
+} m3_gate_desc;
+int m3_gate_forward(m3_ctx *ctx, const m3_gate_desc *desc, void *out);
+int m3_gate_backward(m3_ctx *ctx, const m3_gate_desc *desc, const void *dout, void *dy, void *dz);
 
 /* Bytes of device scratch a forward with this descriptor allocates (kept until
  * m3_saved_free when `saved` is requested). */

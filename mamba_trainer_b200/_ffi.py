@@ -58,7 +58,24 @@ class StepOut(C.Structure):
 
 class ConvDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("batch", "seq", "channels", "kernel_size", "dtype", "activation")] + [
-        ("x_stride", C.c_int64), ("y_stride", C.c_int64)] + [(n, C.c_void_p) for n in ("x", "history", "weight", "bias")]
+        ("x_stride", C.c_int64), ("y_stride", C.c_int64)] + [(n, C.c_void_p) for n in ("x", "history", "weight", "bias")] + [
+        ("split", C.c_int32), ("reserved0", C.c_int32), ("y2_stride", C.c_int64), ("y2", C.c_void_p), ("dy2", C.c_void_p)]
+
+
+class BcDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("batch", "seq", "heads", "groups", "d_state", "rank", "dtype", "has_norm")] + [
+        ("eps", C.c_float), ("reserved0", C.c_int32), ("raw_stride", C.c_int64)] + [
+        (n, C.c_void_p) for n in ("b_raw", "c_raw", "b_bias", "c_bias", "norm_weight")]
+
+
+class ActDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("batch", "seq", "heads", "dtype")] + [("stride", C.c_int64)] + [
+        (n, C.c_void_p) for n in ("dt_raw", "lambda_raw", "dt_bias")]
+
+
+class GateDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("batch", "seq", "channels", "dtype")] + [("z_stride", C.c_int64)] + [
+        (n, C.c_void_p) for n in ("y", "z")]
 
 
 class HostIn(C.Structure):
@@ -91,6 +108,12 @@ SYMBOLS = {
     "m3_conv_forward": (C.c_int, [C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p]),
     "m3_conv_backward": (C.c_int, [C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                    C.c_void_p]),
+    "m3_bc_forward": (C.c_int, [C.c_void_p, C.POINTER(BcDesc), C.c_void_p, C.c_void_p]),
+    "m3_bc_backward": (C.c_int, [C.c_void_p, C.POINTER(BcDesc)] + [C.c_void_p] * 7),
+    "m3_dt_lambda_forward": (C.c_int, [C.c_void_p, C.POINTER(ActDesc), C.c_void_p, C.c_void_p]),
+    "m3_dt_lambda_backward": (C.c_int, [C.c_void_p, C.POINTER(ActDesc)] + [C.c_void_p] * 5),
+    "m3_gate_forward": (C.c_int, [C.c_void_p, C.POINTER(GateDesc), C.c_void_p]),
+    "m3_gate_backward": (C.c_int, [C.c_void_p, C.POINTER(GateDesc), C.c_void_p, C.c_void_p, C.c_void_p]),
     "m3_host_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "m3_host_free": (C.c_int, [C.c_void_p]),
     "m3_host_pipe_create": (C.c_int, [C.c_void_p, C.POINTER(ScanDesc), C.c_int, C.POINTER(C.c_void_p)]),

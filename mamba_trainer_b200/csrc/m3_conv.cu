@@ -24,7 +24,7 @@
 namespace {
 
 constexpr int kMaxTaps = 8;
-constexpr int kRun = 16;     // time steps per thread
+constexpr int kRun = 8;      // time steps per thread
 constexpr int kLanesT = 8;   // threads of a block along time
 constexpr int kLanesC = 32;  // threads of a block along channel vectors
 
@@ -32,8 +32,11 @@ template <class T, int V>
 struct Vec;
 template <>
 struct Vec<__nv_bfloat16, 8> {
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
-    const uint4 q = __ldg(reinterpret_cast<const uint4*>(p));
+  using raw_t = uint4;
+  static __device__ __forceinline__ raw_t load_raw(const __nv_bfloat16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+  static __device__ __forceinline__ raw_t zero_raw() { return make_uint4(0u, 0u, 0u, 0u); }
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) { unpack(load_raw(p), v); }
+  static __device__ __forceinline__ void unpack(const raw_t& q, float (&v)[8]) {
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -53,9 +56,30 @@ struct Vec<__nv_bfloat16, 8> {
   }
 };
 template <>
+struct Vec<__nv_bfloat16, 4> {  // 8-byte vectors: half the registers per thread, for the backward pass
+  using raw_t = uint2;
+  static __device__ __forceinline__ raw_t load_raw(const __nv_bfloat16* p) { return __ldg(reinterpret_cast<const uint2*>(p)); }
+  static __device__ __forceinline__ raw_t zero_raw() { return make_uint2(0u, 0u); }
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) { unpack(load_raw(p), v); }
+  static __device__ __forceinline__ void unpack(const raw_t& q, float (&v)[4]) {
+    v[0] = __uint_as_float(q.x << 16); v[1] = __uint_as_float(q.x & 0xffff0000u);
+    v[2] = __uint_as_float(q.y << 16); v[3] = __uint_as_float(q.y & 0xffff0000u);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 q;
+    q.x = *reinterpret_cast<uint32_t*>(&a);
+    q.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = q;
+  }
+};
+template <>
 struct Vec<float, 4> {
-  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
-    const float4 q = __ldg(reinterpret_cast<const float4*>(p));
+  using raw_t = float4;
+  static __device__ __forceinline__ raw_t load_raw(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+  static __device__ __forceinline__ raw_t zero_raw() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) { unpack(load_raw(p), v); }
+  static __device__ __forceinline__ void unpack(const raw_t& q, float (&v)[4]) {
     v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
   }
   static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
@@ -64,6 +88,10 @@ struct Vec<float, 4> {
 };
 template <class T>
 struct Vec<T, 1> {
+  using raw_t = float;
+  static __device__ __forceinline__ raw_t load_raw(const T* p) { return m3::ldf(p, 0); }
+  static __device__ __forceinline__ raw_t zero_raw() { return 0.0f; }
+  static __device__ __forceinline__ void unpack(const raw_t& q, float (&v)[1]) { v[0] = q; }
   static __device__ __forceinline__ void load(const T* p, float (&v)[1]) { v[0] = m3::ldf(p, 0); }
   static __device__ __forceinline__ void store(T* p, const float (&v)[1]) { m3::stf(p, 0, v[0]); }
 };
@@ -72,7 +100,21 @@ struct ConvDims {
   int B, T, C, K;
   long long xs, ys;  // elements between consecutive time steps of x (and dx) / of y (and dy)
   int act;
+  int split;         // channels >= split live in a second output tensor (0: none)
+  long long y2s;     // its row stride
 };
+
+// Where channel vector c0 of the output (or of its gradient) lives: the first tensor, or the
+// second one for channels at and beyond the split.
+template <class T>
+__device__ __forceinline__ T* out_band(const ConvDims& d, T* y, T* y2, int c0, long long* stride) {
+  if (d.split > 0 && c0 >= d.split) {
+    *stride = d.y2s;
+    return y2 + (c0 - d.split);
+  }
+  *stride = d.ys;
+  return y + c0;
+}
 
 __device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
 __device__ __forceinline__ float silu_grad(float v) {
@@ -82,15 +124,12 @@ __device__ __forceinline__ float silu_grad(float v) {
 
 // x of (b, t, channel vector c0): the sequence, the carried history for t < 0, or zero.
 template <class T, int V>
-__device__ __forceinline__ void load_x(const ConvDims& d, const T* x, const T* hist, int b, int t, int c0, float (&v)[V]) {
-  if (t >= 0 && t < d.T) {
-    Vec<T, V>::load(x + ((size_t)b * d.T + t) * d.xs + c0, v);
-  } else if (t < 0 && hist && t + (d.K - 1) >= 0) {
-    Vec<T, V>::load(hist + ((size_t)b * (d.K - 1) + (t + d.K - 1)) * d.C + c0, v);
-  } else {
-#pragma unroll
-    for (int i = 0; i < V; ++i) v[i] = 0.0f;
-  }
+__device__ __forceinline__ typename Vec<T, V>::raw_t load_x(const ConvDims& d, const T* x, const T* hist, int b, int t,
+                                                            int c0) {
+  if (t >= 0 && t < d.T) return Vec<T, V>::load_raw(x + ((size_t)b * d.T + t) * d.xs + c0);
+  if (t < 0 && hist && t + (d.K - 1) >= 0)
+    return Vec<T, V>::load_raw(hist + ((size_t)b * (d.K - 1) + (t + d.K - 1)) * d.C + c0);
+  return Vec<T, V>::zero_raw();
 }
 
 // The kernels are compiled for KT in {2, 4, 8} taps; a K-tap convolution runs as the KT-tap one
@@ -98,11 +137,13 @@ __device__ __forceinline__ void load_x(const ConvDims& d, const T* x, const T* h
 template <class T, int V, int KT>
 __global__ void __launch_bounds__(kLanesT* kLanesC)
     k_conv_fwd(ConvDims d, const T* __restrict__ x, const T* __restrict__ hist, const float* __restrict__ w,
-               const float* __restrict__ bias, T* __restrict__ y) {
+               const float* __restrict__ bias, T* __restrict__ y, T* __restrict__ y2) {
   const int c0 = (blockIdx.x * kLanesC + threadIdx.x) * V;
   const int b = blockIdx.z;
   const int t0 = (blockIdx.y * kLanesT + threadIdx.y) * kRun;
   if (c0 >= d.C || t0 >= d.T) return;
+  long long ys;
+  T* yb = out_band<T>(d, y, y2, c0, &ys);
   const int pad = KT - d.K;
   float wt[KT][V], bs[V], win[KT][V];  // win[k] pairs with tap k: x[t - (KT-1-k)]
 #pragma unroll
@@ -111,16 +152,21 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
     for (int i = 0; i < V; ++i) wt[k][i] = (k >= pad) ? w[(size_t)(k - pad) * d.C + c0 + i] : 0.0f;
 #pragma unroll
   for (int i = 0; i < V; ++i) bs[i] = bias ? bias[c0 + i] : 0.0f;
+  // Every row this thread needs is requested before the first one is used.
+  typename Vec<T, V>::raw_t raw[kRun + KT - 1];  // raw[j] = x[t0 - (KT-1) + j]
 #pragma unroll
-  for (int k = 0; k < KT - 1; ++k) load_x<T, V>(d, x, hist, b, t0 - (KT - 1) + k, c0, win[k + 1]);
+  for (int j = 0; j < kRun + KT - 1; ++j) raw[j] = load_x<T, V>(d, x, hist, b, t0 - (KT - 1) + j, c0);
+#pragma unroll
+  for (int k = 0; k < KT - 1; ++k) Vec<T, V>::unpack(raw[k], win[k + 1]);
   const int t1 = min(t0 + kRun, d.T);
-#pragma unroll 4
-  for (int t = t0; t < t1; ++t) {
+#pragma unroll
+  for (int it = 0; it < kRun; ++it) {
+    const int t = t0 + it;
 #pragma unroll
     for (int k = 0; k < KT - 1; ++k)
 #pragma unroll
       for (int i = 0; i < V; ++i) win[k][i] = win[k + 1][i];
-    Vec<T, V>::load(x + ((size_t)b * d.T + t) * d.xs + c0, win[KT - 1]);
+    Vec<T, V>::unpack(raw[KT - 1 + it], win[KT - 1]);
     float acc[V];
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = bs[i];
@@ -132,7 +178,7 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
 #pragma unroll
       for (int i = 0; i < V; ++i) acc[i] = silu(acc[i]);
     }
-    Vec<T, V>::store(y + ((size_t)b * d.T + t) * d.ys + c0, acc);
+    if (t < t1) Vec<T, V>::store(yb + ((size_t)b * d.T + t) * ys, acc);
   }
 }
 
@@ -155,8 +201,8 @@ __global__ void k_conv_history(ConvDims d, const T* __restrict__ x, const T* __r
 template <class T, int V, int KT>
 __global__ void __launch_bounds__(kLanesT* kLanesC)
     k_conv_bwd(ConvDims d, const T* __restrict__ x, const T* __restrict__ hist, const float* __restrict__ w,
-               const float* __restrict__ bias, const T* __restrict__ dy, T* __restrict__ dx, T* __restrict__ dhist,
-               float* __restrict__ part) {
+               const float* __restrict__ bias, const T* __restrict__ dy, const T* __restrict__ dy2, T* __restrict__ dx,
+               T* __restrict__ dhist, float* __restrict__ part) {
   __shared__ float red[kLanesT][kLanesC * V + 1];
   const int c0 = (blockIdx.x * kLanesC + threadIdx.x) * V;
   const int b = blockIdx.z;
@@ -181,13 +227,24 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
       }
 #pragma unroll
     for (int i = 0; i < V; ++i) bs[i] = bias ? bias[c0 + i] : 0.0f;
+    // Every row this thread needs (its run, KT-1 steps behind for the taps and KT-1 ahead for the
+    // look-ahead of dx) is requested before the first one is used.
+    long long ys;
+    const T* gb = out_band<const T>(d, dy, dy2, c0, &ys);
+    typename Vec<T, V>::raw_t rx[kRun + 2 * (KT - 1)], rg[kRun + KT - 1];  // rx[j] = x[t0-(KT-1)+j], rg[j] = dy[t0+j]
 #pragma unroll
-    for (int k = 0; k < KT - 1; ++k) load_x<T, V>(d, x, hist, b, t0 - (KT - 1) + k, c0, win[k + 1]);
+    for (int j = 0; j < kRun + 2 * (KT - 1); ++j) rx[j] = load_x<T, V>(d, x, hist, b, t0 - (KT - 1) + j, c0);
+#pragma unroll
+    for (int j = 0; j < kRun + KT - 1; ++j)
+      rg[j] = (t0 + j < d.T) ? Vec<T, V>::load_raw(gb + ((size_t)b * d.T + t0 + j) * ys) : Vec<T, V>::zero_raw();
+#pragma unroll
+    for (int k = 0; k < KT - 1; ++k) Vec<T, V>::unpack(rx[k], win[k + 1]);
     const int t1 = min(t0 + kRun, d.T);
     // s walks the run plus KT-1 steps of look-ahead; dx[s-(KT-1)] is complete once g[s] is known.
-    const int s_end = t1 + KT - 1;
     const int emit_from = (t0 == 0 && dhist) ? -(d.K - 1) : t0;
-    for (int s = t0; s < s_end; ++s) {
+#pragma unroll
+    for (int it = 0; it < kRun + KT - 1; ++it) {
+      const int s = t0 + it;
 #pragma unroll
       for (int k = 0; k < KT - 1; ++k)
 #pragma unroll
@@ -195,10 +252,12 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
           win[k][i] = win[k + 1][i];
           gw[k][i] = gw[k + 1][i];
         }
-      if (s < d.T) {
+      {
         float gy[V], acc[V];
-        Vec<T, V>::load(x + ((size_t)b * d.T + s) * d.xs + c0, win[KT - 1]);
-        Vec<T, V>::load(dy + ((size_t)b * d.T + s) * d.ys + c0, gy);
+        Vec<T, V>::unpack(rx[KT - 1 + it], win[KT - 1]);
+        Vec<T, V>::unpack(rg[it], gy);
+        const bool valid = s < d.T;
+        const float own = s < t1 ? 1.0f : 0.0f;  // own steps feed the parameter gradients, each exactly once
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = bs[i];
 #pragma unroll
@@ -206,18 +265,13 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
 #pragma unroll
           for (int i = 0; i < V; ++i) acc[i] = fmaf(wt[k][i], win[k][i], acc[i]);
 #pragma unroll
-        for (int i = 0; i < V; ++i) gw[KT - 1][i] = d.act ? gy[i] * silu_grad(acc[i]) : gy[i];
-        if (s < t1) {  // this thread's own steps feed the parameter gradients (each step exactly once)
+        for (int i = 0; i < V; ++i) gw[KT - 1][i] = valid ? (d.act ? gy[i] * silu_grad(acc[i]) : gy[i]) : 0.0f;
 #pragma unroll
-          for (int k = 0; k < KT; ++k)
+        for (int k = 0; k < KT; ++k)
 #pragma unroll
-            for (int i = 0; i < V; ++i) pw[k][i] = fmaf(gw[KT - 1][i], win[k][i], pw[k][i]);
+          for (int i = 0; i < V; ++i) pw[k][i] = fmaf(own * gw[KT - 1][i], win[k][i], pw[k][i]);
 #pragma unroll
-          for (int i = 0; i < V; ++i) pb[i] += gw[KT - 1][i];
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < V; ++i) gw[KT - 1][i] = 0.0f;
+        for (int i = 0; i < V; ++i) pb[i] = fmaf(own, gw[KT - 1][i], pb[i]);
       }
       const int te = s - (KT - 1);  // dx[te] = sum_delay w[KT-1-delay] g[te+delay] = sum_j w[KT-1-j] gw[j]
       if (te >= emit_from && te < t1) {
@@ -285,13 +339,21 @@ int check(m3_ctx* ctx, const m3_conv_desc* c, ConvDims* d) {
   d->B = c->batch; d->T = c->seq; d->C = c->channels; d->K = c->kernel_size;
   d->xs = c->x_stride ? c->x_stride : c->channels;
   d->ys = c->y_stride ? c->y_stride : c->channels;
-  if (d->xs < c->channels || d->ys < c->channels) return m3::fail(ctx, M3_ERR_SHAPE, "row strides below the channel count");
+  if (d->xs < c->channels || d->ys < (c->split > 0 ? c->split : c->channels))
+    return m3::fail(ctx, M3_ERR_SHAPE, "row strides below the channel count");
   d->act = c->activation ? 1 : 0;
+  d->split = c->split;
+  d->y2s = 0;
+  if (c->split < 0 || c->split >= c->channels) return m3::fail(ctx, M3_ERR_SHAPE, "split %d outside [0, channels)", c->split);
+  if (c->split > 0) {
+    d->y2s = c->y2_stride ? c->y2_stride : c->channels - c->split;
+    if (d->y2s < c->channels - c->split) return m3::fail(ctx, M3_ERR_SHAPE, "y2_stride below the second band's width");
+  }
   return M3_OK;
 }
 
 bool vector_ok(const ConvDims& d, int V, int es, std::initializer_list<const void*> ptrs) {
-  if (d.C % V || d.xs % V || d.ys % V) return false;
+  if (d.C % V || d.xs % V || d.ys % V || d.split % V || d.y2s % V) return false;
   for (const void* p : ptrs)
     if (p && (reinterpret_cast<uintptr_t>(p) % (size_t)(V * es))) return false;
   return true;
@@ -299,13 +361,14 @@ bool vector_ok(const ConvDims& d, int V, int es, std::initializer_list<const voi
 
 template <class T, int V>
 cudaError_t fwd_launch(cudaStream_t st, const ConvDims& d, const m3_conv_desc& c, void* y) {
+  T* y2 = static_cast<T*>(c.y2);
   const dim3 block(kLanesC, kLanesT);
   const dim3 grid((d.C / V + kLanesC - 1) / kLanesC, (d.T + kLanesT * kRun - 1) / (kLanesT * kRun), d.B);
   const T* x = static_cast<const T*>(c.x);
   const T* h = static_cast<const T*>(c.history);
-  if (d.K <= 2) k_conv_fwd<T, V, 2><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<T*>(y));
-  else if (d.K <= 4) k_conv_fwd<T, V, 4><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<T*>(y));
-  else k_conv_fwd<T, V, kMaxTaps><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<T*>(y));
+  if (d.K <= 2) k_conv_fwd<T, V, 2><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<T*>(y), y2);
+  else if (d.K <= 4) k_conv_fwd<T, V, 4><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<T*>(y), y2);
+  else k_conv_fwd<T, V, kMaxTaps><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<T*>(y), y2);
   return cudaGetLastError();
 }
 
@@ -318,14 +381,14 @@ cudaError_t bwd_launch(cudaStream_t st, const ConvDims& d, const m3_conv_desc& c
   const T* x = static_cast<const T*>(c.x);
   const T* h = static_cast<const T*>(c.history);
   if (d.K <= 2)
-    k_conv_bwd<T, V, 2><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<const T*>(dy), static_cast<T*>(dx),
+    k_conv_bwd<T, V, 2><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<const T*>(dy), static_cast<const T*>(c.dy2), static_cast<T*>(dx),
                                                  static_cast<T*>(dhist), part);
   else if (d.K <= 4)
-    k_conv_bwd<T, V, 4><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<const T*>(dy), static_cast<T*>(dx),
+    k_conv_bwd<T, V, 4><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<const T*>(dy), static_cast<const T*>(c.dy2), static_cast<T*>(dx),
                                                  static_cast<T*>(dhist), part);
   else
     k_conv_bwd<T, V, kMaxTaps><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<const T*>(dy),
-                                                        static_cast<T*>(dx), static_cast<T*>(dhist), part);
+                                                        static_cast<const T*>(c.dy2), static_cast<T*>(dx), static_cast<T*>(dhist), part);
   return cudaGetLastError();
 }
 
@@ -338,14 +401,15 @@ int m3_conv_forward(m3_ctx* ctx, const m3_conv_desc* c, void* y, void* new_histo
   const int rc = check(ctx, c, &d);
   if (rc != M3_OK) return rc;
   if (!y) return m3::fail(ctx, M3_ERR_NULL, "y is required");
+  if (c->split > 0 && !c->y2) return m3::fail(ctx, M3_ERR_NULL, "split needs y2");
   M3_CUDA(ctx, cudaSetDevice(ctx->device));
   cudaError_t e = cudaSuccess;
   if (d.T > 0) {
     if (c->dtype == M3_BF16) {
-      e = vector_ok(d, 8, 2, {c->x, c->history, y}) ? fwd_launch<__nv_bfloat16, 8>(ctx->stream, d, *c, y)
+      e = vector_ok(d, 8, 2, {c->x, c->history, y, c->y2}) ? fwd_launch<__nv_bfloat16, 8>(ctx->stream, d, *c, y)
                                                      : fwd_launch<__nv_bfloat16, 1>(ctx->stream, d, *c, y);
     } else {
-      e = vector_ok(d, 4, 4, {c->x, c->history, y}) ? fwd_launch<float, 4>(ctx->stream, d, *c, y)
+      e = vector_ok(d, 4, 4, {c->x, c->history, y, c->y2}) ? fwd_launch<float, 4>(ctx->stream, d, *c, y)
                                                      : fwd_launch<float, 1>(ctx->stream, d, *c, y);
     }
     if (e != cudaSuccess) return m3::cuda_fail(ctx, e, "conv forward");
@@ -374,6 +438,7 @@ int m3_conv_backward(m3_ctx* ctx, const m3_conv_desc* c, const void* dy, void* d
   const int rc = check(ctx, c, &d);
   if (rc != M3_OK) return rc;
   if (!dy) return m3::fail(ctx, M3_ERR_NULL, "dy is required");
+  if (c->split > 0 && !c->dy2) return m3::fail(ctx, M3_ERR_NULL, "split needs dy2");
   if (dhistory && !c->history) return m3::fail(ctx, M3_ERR_NULL, "dhistory without a history");
   M3_CUDA(ctx, cudaSetDevice(ctx->device));
   const bool want_par = dweight || (dbias && c->bias);
@@ -390,11 +455,11 @@ int m3_conv_backward(m3_ctx* ctx, const m3_conv_desc* c, const void* dy, void* d
   dim3 grid;
   cudaError_t e;
   if (c->dtype == M3_BF16) {
-    e = vector_ok(d, 8, 2, {c->x, c->history, dy, dx, dhistory})
-            ? bwd_launch<__nv_bfloat16, 8>(ctx->stream, d, *c, dy, dx, dhistory, part, &grid)
+    e = vector_ok(d, 4, 2, {c->x, c->history, dy, c->dy2, dx, dhistory})
+            ? bwd_launch<__nv_bfloat16, 4>(ctx->stream, d, *c, dy, dx, dhistory, part, &grid)
             : bwd_launch<__nv_bfloat16, 1>(ctx->stream, d, *c, dy, dx, dhistory, part, &grid);
   } else {
-    e = vector_ok(d, 4, 4, {c->x, c->history, dy, dx, dhistory})
+    e = vector_ok(d, 4, 4, {c->x, c->history, dy, c->dy2, dx, dhistory})
             ? bwd_launch<float, 4>(ctx->stream, d, *c, dy, dx, dhistory, part, &grid)
             : bwd_launch<float, 1>(ctx->stream, d, *c, dy, dx, dhistory, part, &grid);
   }

@@ -1,0 +1,530 @@
+// Mixer-side steps either side of the scan, each as one launch instead of the reference's chain of
+// primitives (src/models/mamba3.rs:403-461, :475-484):
+//   m3_bc_*        B / C: group -> head expansion, per-head bias, RMS norm over d_state, and the
+//                  permute to the scan's rank-last layout (:409-436)
+//   m3_dt_lambda_* dt = softplus(dt_raw + dt_bias), lambda = sigmoid(lambda_raw) (:440-446)
+//   m3_gate_*      y * silu(z) (:475-484, without post_gate_norm)
+// All are HBM-bound streaming kernels; inputs may be column bands of a wider row (the input
+// projection / the convolution's output), outputs of the forward are dense.
+#include <cuda_bf16.h>
+
+#include <initializer_list>
+
+#include "m3_internal.h"
+
+#define M3_CUDA(ctx, call)                                       \
+  do {                                                           \
+    cudaError_t e_ = (call);                                     \
+    if (e_ != cudaSuccess) return m3::cuda_fail(ctx, e_, #call); \
+  } while (0)
+
+namespace {
+
+using m3::ldf;
+using m3::stf;
+
+constexpr int kBcWarps = 8;      // warps per block
+constexpr int kBcTokens = 64;    // tokens per block (8 per warp)
+constexpr int kMaxPerLane = 8;   // d_state <= 32 * kMaxPerLane = 256 on the fast path
+
+struct BcDims {
+  int B, T, H, G, N, R, PG;      // PG = heads per group
+  long long rs;                  // token stride of the raw rows (elements)
+  float eps;
+  int has_norm;
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ---- B / C forward: one warp per (token, head); lanes stride over d_state ---------------------------
+template <class T>
+__global__ void __launch_bounds__(kBcWarps * 32)
+    k_bc_fwd(BcDims d, const T* __restrict__ raw, const float* __restrict__ bias, const float* __restrict__ gain,
+             T* __restrict__ out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t row = (size_t)blockIdx.x * kBcWarps + warp;  // (b * T + t) * H + h
+  if (row >= (size_t)d.B * d.T * d.H) return;
+  const int h = row % d.H;
+  const size_t bt = row / d.H;
+  const int g = h / d.PG;
+  const T* src = raw + bt * d.rs + (size_t)g * d.R * d.N;
+  T* dst = out + row * d.N * d.R;
+  for (int r = 0; r < d.R; ++r) {
+    float v[kMaxPerLane];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int n = lane + 32 * j;
+      v[j] = 0.0f;
+      if (n < d.N) {
+        v[j] = ldf(src, (size_t)r * d.N + n) + (bias ? bias[(size_t)h * d.N + n] : 0.0f);
+        ss += v[j] * v[j];
+      }
+    }
+    float scale = 1.0f;
+    if (d.has_norm) scale = rsqrtf(warp_sum(ss) / (float)d.N + d.eps);
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int n = lane + 32 * j;
+      if (n < d.N) stf(dst, (size_t)n * d.R + r, v[j] * scale * ((d.has_norm && gain) ? gain[n] : 1.0f));
+    }
+  }
+}
+
+// ---- B / C backward: a block owns one group and kBcTokens tokens; a warp walks tokens, sums the
+// gradient of the raw row over the heads of the group, and keeps private partial sums of the bias
+// and gain gradients in shared memory (no atomics: every sum has a fixed order).
+template <class T>
+__global__ void __launch_bounds__(kBcWarps * 32)
+    k_bc_bwd(BcDims d, const T* __restrict__ raw, const float* __restrict__ bias, const float* __restrict__ gain,
+             const T* __restrict__ dout, T* __restrict__ draw, float* __restrict__ part) {
+  extern __shared__ float sm[];  // [warps][PG + 1][N]: bias partials per head of the group, then gain
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = blockIdx.y;
+  const size_t ntok = (size_t)d.B * d.T;
+  const size_t tok0 = (size_t)blockIdx.x * kBcTokens;
+  float* mine = sm + (size_t)warp * (d.PG + 1) * d.N;
+  for (int i = lane; i < (d.PG + 1) * d.N; i += 32) mine[i] = 0.0f;
+  __syncwarp();
+  for (int it = warp; it < kBcTokens; it += kBcWarps) {
+    const size_t bt = tok0 + it;
+    if (bt >= ntok) break;
+    const T* src = raw + bt * d.rs + (size_t)g * d.R * d.N;
+    for (int r = 0; r < d.R; ++r) {
+      float acc[kMaxPerLane];
+#pragma unroll
+      for (int j = 0; j < kMaxPerLane; ++j) acc[j] = 0.0f;
+      for (int hg = 0; hg < d.PG; ++hg) {
+        const int h = g * d.PG + hg;
+        const T* go = dout + (bt * d.H + h) * d.N * d.R;
+        float v[kMaxPerLane], dxh[kMaxPerLane];
+        float ss = 0.0f, dot = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kMaxPerLane; ++j) {
+          const int n = lane + 32 * j;
+          v[j] = dxh[j] = 0.0f;
+          if (n < d.N) {
+            v[j] = ldf(src, (size_t)r * d.N + n) + (bias ? bias[(size_t)h * d.N + n] : 0.0f);
+            const float gy = ldf(go, (size_t)n * d.R + r);
+            dxh[j] = gy * ((d.has_norm && gain) ? gain[n] : 1.0f);
+            ss += v[j] * v[j];
+            if (!d.has_norm) dxh[j] = gy;
+          }
+        }
+        float rstd = 1.0f, mean_dot = 0.0f;
+        if (d.has_norm) {
+          rstd = rsqrtf(warp_sum(ss) / (float)d.N + d.eps);
+#pragma unroll
+          for (int j = 0; j < kMaxPerLane; ++j) dot += dxh[j] * v[j] * rstd;
+          mean_dot = warp_sum(dot) / (float)d.N;
+        }
+#pragma unroll
+        for (int j = 0; j < kMaxPerLane; ++j) {
+          const int n = lane + 32 * j;
+          if (n < d.N) {
+            const float xh = v[j] * rstd;
+            const float dv = d.has_norm ? rstd * (dxh[j] - xh * mean_dot) : dxh[j];
+            acc[j] += dv;
+            mine[(size_t)hg * d.N + n] += dv;                                          // d bias[h, n]
+            if (d.has_norm && gain) mine[(size_t)d.PG * d.N + n] += ldf(go, (size_t)n * d.R + r) * xh;  // d gain[n]
+          }
+        }
+      }
+      if (draw) {
+        T* dr = draw + bt * d.rs + (size_t)g * d.R * d.N;
+#pragma unroll
+        for (int j = 0; j < kMaxPerLane; ++j) {
+          const int n = lane + 32 * j;
+          if (n < d.N) stf(dr, (size_t)r * d.N + n, acc[j]);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (!part) return;
+  const size_t blk = (size_t)blockIdx.x * gridDim.y + g;
+  const int width = (d.PG + 1) * d.N;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float s = 0.0f;
+    for (int w = 0; w < kBcWarps; ++w) s += sm[(size_t)w * width + i];
+    part[blk * width + i] = s;
+  }
+}
+
+// d bias[h, n] = sum over token blocks of the partial of (group(h), h % PG); d gain[n] = sum over
+// token blocks and groups; block order.
+__global__ void k_bc_reduce(BcDims d, int nblk_tok, const float* __restrict__ part, float* __restrict__ dbias,
+                            float* __restrict__ dgain, int accumulate_gain) {
+  const int width = (d.PG + 1) * d.N;
+  const size_t n_bias = (size_t)d.H * d.N;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_bias + d.N; i += (size_t)gridDim.x * blockDim.x) {
+    if (i < n_bias) {
+      if (!dbias) continue;
+      const int h = i / d.N, n = i % d.N, g = h / d.PG, hg = h % d.PG;
+      float s = 0.0f;
+      for (int bk = 0; bk < nblk_tok; ++bk) s += part[((size_t)bk * d.G + g) * width + (size_t)hg * d.N + n];
+      dbias[i] = s;
+    } else if (dgain) {
+      const int n = i - n_bias;
+      float s = accumulate_gain ? dgain[n] : 0.0f;
+      for (int bk = 0; bk < nblk_tok; ++bk)
+        for (int g = 0; g < d.G; ++g) s += part[((size_t)bk * d.G + g) * width + (size_t)d.PG * d.N + n];
+      dgain[n] = s;
+    }
+  }
+}
+
+// ---- dt / lambda ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float softplus(float v) { return v > 20.0f ? v : log1pf(__expf(v)); }
+__device__ __forceinline__ float sigmoid(float v) { return 1.0f / (1.0f + __expf(-v)); }
+
+template <class T>
+__global__ void k_act_fwd(int ntok, int H, long long stride, const T* __restrict__ dt_raw, const T* __restrict__ lam_raw,
+                          const float* __restrict__ dt_bias, T* __restrict__ dt, T* __restrict__ lam) {
+  const size_t n = (size_t)ntok * H;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int h = i % H;
+    const size_t bt = i / H;
+    stf(dt, i, softplus(ldf(dt_raw, bt * stride + h) + (dt_bias ? dt_bias[h] : 0.0f)));
+    if (lam_raw && lam) stf(lam, i, sigmoid(ldf(lam_raw, bt * stride + h)));
+  }
+}
+
+constexpr int kActBlocks = 64;
+// One block per slice of tokens; thread h' strides over heads, so each head's partial sum of the
+// bias gradient has a fixed order.
+template <class T>
+__global__ void k_act_bwd(int ntok, int H, long long stride, const T* __restrict__ dt_raw, const T* __restrict__ lam_raw,
+                          const float* __restrict__ dt_bias, const T* __restrict__ ddt, const T* __restrict__ dlam,
+                          T* __restrict__ ddt_raw, T* __restrict__ dlam_raw, float* __restrict__ part) {
+  const int per = (ntok + gridDim.x - 1) / gridDim.x;
+  const int lo = blockIdx.x * per, hi = min(ntok, lo + per);
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float s = 0.0f;
+    for (int bt = lo; bt < hi; ++bt) {
+      const size_t i = (size_t)bt * H + h, j = (size_t)bt * stride + h;
+      const float g = ldf(ddt, i) * sigmoid(ldf(dt_raw, j) + (dt_bias ? dt_bias[h] : 0.0f));
+      if (ddt_raw) stf(ddt_raw, j, g);
+      s += g;
+      if (lam_raw && dlam && dlam_raw) {
+        const float l = sigmoid(ldf(lam_raw, j));
+        stf(dlam_raw, j, ldf(dlam, i) * l * (1.0f - l));
+      }
+    }
+    if (part) part[(size_t)blockIdx.x * H + h] = s;
+  }
+}
+
+__global__ void k_act_reduce(int nblk, int H, const float* __restrict__ part, float* __restrict__ dbias) {
+  for (int h = blockIdx.x * blockDim.x + threadIdx.x; h < H; h += gridDim.x * blockDim.x) {
+    float s = 0.0f;
+    for (int b = 0; b < nblk; ++b) s += part[(size_t)b * H + h];
+    dbias[h] = s;
+  }
+}
+
+// ---- gate -----------------------------------------------------------------------------------------------
+__device__ __forceinline__ float silu(float v) { return v * sigmoid(v); }
+__device__ __forceinline__ float silu_grad(float v) {
+  const float s = sigmoid(v);
+  return s * (1.0f + v * (1.0f - s));
+}
+
+// 8 elements per thread step when everything is 16-byte aligned (VEC), else one.
+template <class T, bool VEC>
+__global__ void k_gate_fwd(size_t ntok, int Cn, long long zs, const T* __restrict__ y, const T* __restrict__ z,
+                           T* __restrict__ out) {
+  constexpr int V = VEC ? (int)(16 / sizeof(T)) : 1;
+  const int per_row = Cn / V;
+  const size_t n = ntok * per_row;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t bt = i / per_row;
+    const int c = (int)(i % per_row) * V;
+    if (VEC) {
+      const uint4 qy = __ldg(reinterpret_cast<const uint4*>(y + bt * Cn + c));
+      const uint4 qz = __ldg(reinterpret_cast<const uint4*>(z + bt * zs + c));
+      uint4 qo;
+      const T* py = reinterpret_cast<const T*>(&qy);
+      const T* pz = reinterpret_cast<const T*>(&qz);
+      T* po = reinterpret_cast<T*>(&qo);
+#pragma unroll
+      for (int k = 0; k < V; ++k) stf(po, k, ldf(py, k) * silu(ldf(pz, k)));
+      *reinterpret_cast<uint4*>(out + bt * Cn + c) = qo;
+    } else {
+      stf(out, bt * Cn + c, ldf(y, bt * Cn + c) * silu(ldf(z, bt * zs + c)));
+    }
+  }
+}
+
+template <class T, bool VEC>
+__global__ void k_gate_bwd(size_t ntok, int Cn, long long zs, const T* __restrict__ y, const T* __restrict__ z,
+                           const T* __restrict__ dout, T* __restrict__ dy, T* __restrict__ dz) {
+  constexpr int V = VEC ? (int)(16 / sizeof(T)) : 1;
+  const int per_row = Cn / V;
+  const size_t n = ntok * per_row;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t bt = i / per_row;
+    const int c = (int)(i % per_row) * V;
+    if (VEC) {
+      const uint4 qy = __ldg(reinterpret_cast<const uint4*>(y + bt * Cn + c));
+      const uint4 qz = __ldg(reinterpret_cast<const uint4*>(z + bt * zs + c));
+      const uint4 qg = __ldg(reinterpret_cast<const uint4*>(dout + bt * Cn + c));
+      uint4 o1, o2;
+      const T* py = reinterpret_cast<const T*>(&qy);
+      const T* pz = reinterpret_cast<const T*>(&qz);
+      const T* pg = reinterpret_cast<const T*>(&qg);
+      T* p1 = reinterpret_cast<T*>(&o1);
+      T* p2 = reinterpret_cast<T*>(&o2);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float zv = ldf(pz, k), gv = ldf(pg, k);
+        stf(p1, k, gv * silu(zv));
+        stf(p2, k, gv * ldf(py, k) * silu_grad(zv));
+      }
+      if (dy) *reinterpret_cast<uint4*>(dy + bt * Cn + c) = o1;
+      if (dz) *reinterpret_cast<uint4*>(dz + bt * zs + c) = o2;
+    } else {
+      const float zv = ldf(z, bt * zs + c), gv = ldf(dout, bt * Cn + c);
+      if (dy) stf(dy, bt * Cn + c, gv * silu(zv));
+      if (dz) stf(dz, bt * zs + c, gv * ldf(y, bt * Cn + c) * silu_grad(zv));
+    }
+  }
+}
+
+int bc_dims(m3_ctx* ctx, const m3_bc_desc* s, BcDims* d) {
+  if (!ctx || !s) return M3_ERR_NULL;
+  if (s->batch <= 0 || s->seq < 0 || s->heads <= 0 || s->groups <= 0 || s->d_state <= 0 || s->rank <= 0)
+    return m3::fail(ctx, M3_ERR_SHAPE, "B/C prologue: extents must be positive");
+  if (s->heads % s->groups) return m3::fail(ctx, M3_ERR_CONFIG, "heads %d not a multiple of groups %d", s->heads, s->groups);
+  if (s->d_state > 32 * kMaxPerLane) return m3::fail(ctx, M3_ERR_UNSUPPORTED, "d_state %d > %d", s->d_state, 32 * kMaxPerLane);
+  if (s->dtype != M3_F32 && s->dtype != M3_BF16) return m3::fail(ctx, M3_ERR_UNSUPPORTED, "dtype %d", s->dtype);
+  if (!s->b_raw || !s->c_raw) return m3::fail(ctx, M3_ERR_NULL, "b_raw and c_raw are required");
+  d->B = s->batch; d->T = s->seq; d->H = s->heads; d->G = s->groups; d->N = s->d_state; d->R = s->rank;
+  d->PG = s->heads / s->groups;
+  const long long dense = (long long)s->groups * s->rank * s->d_state;
+  d->rs = s->raw_stride ? s->raw_stride : dense;
+  if (d->rs < dense) return m3::fail(ctx, M3_ERR_SHAPE, "raw_stride below groups * rank * d_state");
+  d->eps = s->eps;
+  d->has_norm = s->has_norm ? 1 : 0;
+  return M3_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int m3_bc_forward(m3_ctx* ctx, const m3_bc_desc* s, void* b, void* c) {
+  BcDims d;
+  const int rc = bc_dims(ctx, s, &d);
+  if (rc != M3_OK) return rc;
+  if (!b || !c) return m3::fail(ctx, M3_ERR_NULL, "b and c are required");
+  if (d.T == 0) return M3_OK;
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  const size_t rows = (size_t)d.B * d.T * d.H;
+  const unsigned grid = (unsigned)((rows + kBcWarps - 1) / kBcWarps);
+  if (s->dtype == M3_BF16) {
+    using T = __nv_bfloat16;
+    k_bc_fwd<T><<<grid, kBcWarps * 32, 0, ctx->stream>>>(d, static_cast<const T*>(s->b_raw), s->b_bias, s->norm_weight, static_cast<T*>(b));
+    k_bc_fwd<T><<<grid, kBcWarps * 32, 0, ctx->stream>>>(d, static_cast<const T*>(s->c_raw), s->c_bias, s->norm_weight, static_cast<T*>(c));
+  } else {
+    k_bc_fwd<float><<<grid, kBcWarps * 32, 0, ctx->stream>>>(d, static_cast<const float*>(s->b_raw), s->b_bias, s->norm_weight, static_cast<float*>(b));
+    k_bc_fwd<float><<<grid, kBcWarps * 32, 0, ctx->stream>>>(d, static_cast<const float*>(s->c_raw), s->c_bias, s->norm_weight, static_cast<float*>(c));
+  }
+  M3_CUDA(ctx, cudaGetLastError());
+  ctx->launches += 2;
+  return M3_OK;
+}
+
+int m3_bc_backward(m3_ctx* ctx, const m3_bc_desc* s, const void* db, const void* dc, void* db_raw, void* dc_raw,
+                   float* db_bias, float* dc_bias, float* dnorm_weight) {
+  BcDims d;
+  const int rc = bc_dims(ctx, s, &d);
+  if (rc != M3_OK) return rc;
+  if (!db || !dc) return m3::fail(ctx, M3_ERR_NULL, "db and dc are required");
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  const size_t nb = (size_t)d.H * d.N * sizeof(float);
+  if (d.T == 0) {
+    if (db_bias) M3_CUDA(ctx, cudaMemsetAsync(db_bias, 0, nb, ctx->stream));
+    if (dc_bias) M3_CUDA(ctx, cudaMemsetAsync(dc_bias, 0, nb, ctx->stream));
+    if (dnorm_weight) M3_CUDA(ctx, cudaMemsetAsync(dnorm_weight, 0, d.N * sizeof(float), ctx->stream));
+    return M3_OK;
+  }
+  const int nblk_tok = (int)(((size_t)d.B * d.T + kBcTokens - 1) / kBcTokens);
+  const int width = (d.PG + 1) * d.N;
+  const size_t smem = (size_t)kBcWarps * width * sizeof(float);
+  if (smem > 200 * 1024) return m3::fail(ctx, M3_ERR_UNSUPPORTED, "heads per group %d x d_state %d needs %zu bytes of shared memory", d.PG, d.N, smem);
+  float* part = nullptr;
+  M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&part), (size_t)nblk_tok * d.G * width * sizeof(float), ctx->stream));
+  const dim3 grid(nblk_tok, d.G);
+  cudaError_t e = cudaSuccess;
+  for (int which = 0; which < 2 && e == cudaSuccess; ++which) {
+    const void* raw = which ? s->c_raw : s->b_raw;
+    const float* bias = which ? s->c_bias : s->b_bias;
+    const void* go = which ? dc : db;
+    void* draw = which ? dc_raw : db_raw;
+    float* dbias = bias ? (which ? dc_bias : db_bias) : nullptr;
+    if (s->dtype == M3_BF16) {
+      using T = __nv_bfloat16;
+      if (smem > 48 * 1024) e = cudaFuncSetAttribute(k_bc_bwd<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e == cudaSuccess)
+        k_bc_bwd<T><<<grid, kBcWarps * 32, smem, ctx->stream>>>(d, static_cast<const T*>(raw), bias, s->norm_weight,
+                                                                 static_cast<const T*>(go), static_cast<T*>(draw), part);
+    } else {
+      if (smem > 48 * 1024) e = cudaFuncSetAttribute(k_bc_bwd<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e == cudaSuccess)
+        k_bc_bwd<float><<<grid, kBcWarps * 32, smem, ctx->stream>>>(d, static_cast<const float*>(raw), bias, s->norm_weight,
+                                                                     static_cast<const float*>(go), static_cast<float*>(draw), part);
+    }
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e == cudaSuccess) {
+      // the gain is shared by B and C (one bc_norm module): the second pass adds to the first
+      float* dgain = (d.has_norm && s->norm_weight) ? dnorm_weight : nullptr;
+      k_bc_reduce<<<64, 256, 0, ctx->stream>>>(d, nblk_tok, part, dbias, dgain, which);
+      e = cudaGetLastError();
+    }
+    ctx->launches += 2;
+  }
+  cudaError_t e2 = cudaFreeAsync(part, ctx->stream);
+  if (e != cudaSuccess) return m3::cuda_fail(ctx, e, "B/C prologue backward");
+  if (e2 != cudaSuccess) return m3::cuda_fail(ctx, e2, "cudaFreeAsync");
+  return M3_OK;
+}
+
+int m3_dt_lambda_forward(m3_ctx* ctx, const m3_act_desc* s, void* dt, void* lambda) {
+  if (!ctx || !s) return M3_ERR_NULL;
+  if (s->batch <= 0 || s->seq < 0 || s->heads <= 0) return m3::fail(ctx, M3_ERR_SHAPE, "dt / lambda: extents must be positive");
+  if (s->dtype != M3_F32 && s->dtype != M3_BF16) return m3::fail(ctx, M3_ERR_UNSUPPORTED, "dtype %d", s->dtype);
+  if (!s->dt_raw || !dt) return m3::fail(ctx, M3_ERR_NULL, "dt_raw and dt are required");
+  if (s->seq == 0) return M3_OK;
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  const int ntok = s->batch * s->seq;
+  const long long st = s->stride ? s->stride : s->heads;
+  const size_t n = (size_t)ntok * s->heads;
+  const unsigned grid = (unsigned)((n + 255) / 256 < 2048 ? (n + 255) / 256 : 2048);
+  if (s->dtype == M3_BF16) {
+    using T = __nv_bfloat16;
+    k_act_fwd<T><<<grid, 256, 0, ctx->stream>>>(ntok, s->heads, st, static_cast<const T*>(s->dt_raw),
+                                                 static_cast<const T*>(s->lambda_raw), s->dt_bias, static_cast<T*>(dt), static_cast<T*>(lambda));
+  } else {
+    k_act_fwd<float><<<grid, 256, 0, ctx->stream>>>(ntok, s->heads, st, static_cast<const float*>(s->dt_raw),
+                                                     static_cast<const float*>(s->lambda_raw), s->dt_bias, static_cast<float*>(dt), static_cast<float*>(lambda));
+  }
+  M3_CUDA(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return M3_OK;
+}
+
+int m3_dt_lambda_backward(m3_ctx* ctx, const m3_act_desc* s, const void* ddt, const void* dlambda, void* ddt_raw,
+                          void* dlambda_raw, float* ddt_bias) {
+  if (!ctx || !s) return M3_ERR_NULL;
+  if (s->batch <= 0 || s->seq < 0 || s->heads <= 0) return m3::fail(ctx, M3_ERR_SHAPE, "dt / lambda: extents must be positive");
+  if (s->dtype != M3_F32 && s->dtype != M3_BF16) return m3::fail(ctx, M3_ERR_UNSUPPORTED, "dtype %d", s->dtype);
+  if (!s->dt_raw || !ddt) return m3::fail(ctx, M3_ERR_NULL, "dt_raw and ddt are required");
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (s->seq == 0) {
+    if (ddt_bias) M3_CUDA(ctx, cudaMemsetAsync(ddt_bias, 0, s->heads * sizeof(float), ctx->stream));
+    return M3_OK;
+  }
+  const int ntok = s->batch * s->seq;
+  const long long st = s->stride ? s->stride : s->heads;
+  const int nblk = ntok < kActBlocks * 4 ? 1 + ntok / 64 : kActBlocks * 4;
+  float* part = nullptr;
+  const bool want_bias = ddt_bias && s->dt_bias;
+  if (want_bias) M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&part), (size_t)nblk * s->heads * sizeof(float), ctx->stream));
+  const int threads = s->heads < 32 ? 32 : (s->heads > 256 ? 256 : ((s->heads + 31) / 32) * 32);
+  if (s->dtype == M3_BF16) {
+    using T = __nv_bfloat16;
+    k_act_bwd<T><<<nblk, threads, 0, ctx->stream>>>(ntok, s->heads, st, static_cast<const T*>(s->dt_raw), static_cast<const T*>(s->lambda_raw),
+                                                     s->dt_bias, static_cast<const T*>(ddt), static_cast<const T*>(dlambda),
+                                                     static_cast<T*>(ddt_raw), static_cast<T*>(dlambda_raw), part);
+  } else {
+    k_act_bwd<float><<<nblk, threads, 0, ctx->stream>>>(ntok, s->heads, st, static_cast<const float*>(s->dt_raw),
+                                                         static_cast<const float*>(s->lambda_raw), s->dt_bias, static_cast<const float*>(ddt),
+                                                         static_cast<const float*>(dlambda), static_cast<float*>(ddt_raw),
+                                                         static_cast<float*>(dlambda_raw), part);
+  }
+  cudaError_t e = cudaGetLastError();
+  ctx->launches += 1;
+  if (e == cudaSuccess && want_bias) {
+    k_act_reduce<<<(s->heads + 255) / 256, 256, 0, ctx->stream>>>(nblk, s->heads, part, ddt_bias);
+    e = cudaGetLastError();
+    ctx->launches += 1;
+  }
+  cudaError_t e2 = part ? cudaFreeAsync(part, ctx->stream) : cudaSuccess;
+  if (e != cudaSuccess) return m3::cuda_fail(ctx, e, "dt / lambda backward");
+  if (e2 != cudaSuccess) return m3::cuda_fail(ctx, e2, "cudaFreeAsync");
+  return M3_OK;
+}
+
+static bool gate_vec(const m3_gate_desc* s, int es, long long zs, std::initializer_list<const void*> ptrs) {
+  const int V = 16 / es;
+  if (s->channels % V || zs % V) return false;
+  for (const void* p : ptrs)
+    if (p && (reinterpret_cast<uintptr_t>(p) % 16)) return false;
+  return true;
+}
+
+static int gate_check(m3_ctx* ctx, const m3_gate_desc* s) {
+  if (!ctx || !s) return M3_ERR_NULL;
+  if (s->batch <= 0 || s->seq < 0 || s->channels <= 0) return m3::fail(ctx, M3_ERR_SHAPE, "gate: extents must be positive");
+  if (s->dtype != M3_F32 && s->dtype != M3_BF16) return m3::fail(ctx, M3_ERR_UNSUPPORTED, "dtype %d", s->dtype);
+  if (!s->y || !s->z) return m3::fail(ctx, M3_ERR_NULL, "y and z are required");
+  if (s->z_stride && s->z_stride < s->channels) return m3::fail(ctx, M3_ERR_SHAPE, "z_stride below the channel count");
+  return M3_OK;
+}
+
+int m3_gate_forward(m3_ctx* ctx, const m3_gate_desc* s, void* out) {
+  const int rc = gate_check(ctx, s);
+  if (rc != M3_OK) return rc;
+  if (!out) return m3::fail(ctx, M3_ERR_NULL, "out is required");
+  if (s->seq == 0) return M3_OK;
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  const size_t ntok = (size_t)s->batch * s->seq;
+  const long long zs = s->z_stride ? s->z_stride : s->channels;
+  const int es = s->dtype == M3_BF16 ? 2 : 4;
+  const bool vec = gate_vec(s, es, zs, {s->y, s->z, out});
+  const size_t items = ntok * (s->channels / (vec ? 16 / es : 1));
+  const unsigned grid = (unsigned)((items + 255) / 256 < 148 * 16 ? (items + 255) / 256 : 148 * 16);
+  if (s->dtype == M3_BF16) {
+    using T = __nv_bfloat16;
+    if (vec) k_gate_fwd<T, true><<<grid, 256, 0, ctx->stream>>>(ntok, s->channels, zs, static_cast<const T*>(s->y), static_cast<const T*>(s->z), static_cast<T*>(out));
+    else k_gate_fwd<T, false><<<grid, 256, 0, ctx->stream>>>(ntok, s->channels, zs, static_cast<const T*>(s->y), static_cast<const T*>(s->z), static_cast<T*>(out));
+  } else {
+    if (vec) k_gate_fwd<float, true><<<grid, 256, 0, ctx->stream>>>(ntok, s->channels, zs, static_cast<const float*>(s->y), static_cast<const float*>(s->z), static_cast<float*>(out));
+    else k_gate_fwd<float, false><<<grid, 256, 0, ctx->stream>>>(ntok, s->channels, zs, static_cast<const float*>(s->y), static_cast<const float*>(s->z), static_cast<float*>(out));
+  }
+  M3_CUDA(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return M3_OK;
+}
+
+int m3_gate_backward(m3_ctx* ctx, const m3_gate_desc* s, const void* dout, void* dy, void* dz) {
+  const int rc = gate_check(ctx, s);
+  if (rc != M3_OK) return rc;
+  if (!dout) return m3::fail(ctx, M3_ERR_NULL, "dout is required");
+  if (s->seq == 0) return M3_OK;
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  const size_t ntok = (size_t)s->batch * s->seq;
+  const long long zs = s->z_stride ? s->z_stride : s->channels;
+  const int es = s->dtype == M3_BF16 ? 2 : 4;
+  const bool vec = gate_vec(s, es, zs, {s->y, s->z, dout, dy, dz});
+  const size_t items = ntok * (s->channels / (vec ? 16 / es : 1));
+  const unsigned grid = (unsigned)((items + 255) / 256 < 148 * 16 ? (items + 255) / 256 : 148 * 16);
+  if (s->dtype == M3_BF16) {
+    using T = __nv_bfloat16;
+    if (vec) k_gate_bwd<T, true><<<grid, 256, 0, ctx->stream>>>(ntok, s->channels, zs, static_cast<const T*>(s->y), static_cast<const T*>(s->z), static_cast<const T*>(dout), static_cast<T*>(dy), static_cast<T*>(dz));
+    else k_gate_bwd<T, false><<<grid, 256, 0, ctx->stream>>>(ntok, s->channels, zs, static_cast<const T*>(s->y), static_cast<const T*>(s->z), static_cast<const T*>(dout), static_cast<T*>(dy), static_cast<T*>(dz));
+  } else {
+    if (vec) k_gate_bwd<float, true><<<grid, 256, 0, ctx->stream>>>(ntok, s->channels, zs, static_cast<const float*>(s->y), static_cast<const float*>(s->z), static_cast<const float*>(dout), static_cast<float*>(dy), static_cast<float*>(dz));
+    else k_gate_bwd<float, false><<<grid, 256, 0, ctx->stream>>>(ntok, s->channels, zs, static_cast<const float*>(s->y), static_cast<const float*>(s->z), static_cast<const float*>(dout), static_cast<float*>(dy), static_cast<float*>(dz));
+  }
+  M3_CUDA(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return M3_OK;
+}
+
+}  // extern "C"

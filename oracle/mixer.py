@@ -34,3 +34,50 @@ def causal_conv1d(x, weight, bias=None, history=None, activation: bool = True):
         acc = acc + bias.reshape(1, 1, C)
     y = F.silu(acc) if activation else acc
     return y, full[:, full.shape[1] - (K - 1):]
+
+
+def rms_norm(v, weight=None, eps: float = 1e-5):
+    """Var::rms_norm as RmsNorm::apply uses it (src/nn/norm.rs:95-105): v * rsqrt(mean(v^2) + eps) * weight."""
+    out = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+    return out * weight if weight is not None else out
+
+
+def mixer_core(proj, p: dict, heads: int, head_dim: int, d_state: int, rank: int = 1, groups: Optional[int] = None,
+               chunk: int = 64, learned_lambda: bool = True, rotational: bool = True, eps: float = 1e-5,
+               conv_history=None, state=None, want_state: bool = False, fixed_lambda: float = 1.0):
+    """Everything Mamba3Mixer does between its input and output projections
+    (src/models/mamba3.rs:340-461, :475-484, :540-556, no post_gate_norm, one direction):
+    split the projection into z | x B C | dt | lambda | theta, convolve x|B|C and apply SiLU, expand
+    B / C groups to heads, add the per-head biases, RMS-normalise, move the rank axis last, softplus /
+    sigmoid, scan, gate with SiLU(z).
+
+    p: conv_w [K, d_inner + 2 bc], conv_b [same] or None, dt_bias [H], a_log [H], d_skip [H] or None,
+    b_bias / c_bias [H, N] or None, norm_w [N] or None ("norm" False in p disables the norm).
+    Returns (gated [B, T, d_inner], new conv history, OracleState or None)."""
+    B, T, W = proj.shape
+    H, P, N, R = heads, head_dim, d_state, rank
+    G = groups or H
+    d_inner, bc = H * P * R, G * N * R
+    n_lam = H if learned_lambda else 0
+    n_th = H * N // 2 if rotational else 0
+    assert W == 2 * d_inner + 2 * bc + H + n_lam + n_th, "projection width"
+    z, xbc, dt_raw, lam_raw, th_raw = torch.split(proj, [d_inner, d_inner + 2 * bc, H, n_lam, n_th], dim=-1)
+    xbc, hist = causal_conv1d(xbc, p["conv_w"], p.get("conv_b"), conv_history, True)
+    x, b_flat, c_flat = torch.split(xbc, [d_inner, bc, bc], dim=-1)
+
+    def to_heads(v, bias):                                          # :409-436
+        v = v.reshape(B, T, G, 1, R, N).expand(B, T, G, H // G, R, N).reshape(B, T, H, R, N)
+        if bias is not None:
+            v = v + bias.reshape(1, 1, H, 1, N)
+        if p.get("norm", True):
+            v = rms_norm(v, p.get("norm_w"), eps)
+        return v.permute(0, 1, 2, 4, 3)
+
+    b, c = to_heads(b_flat, p.get("b_bias")), to_heads(c_flat, p.get("c_bias"))
+    x5 = x.reshape(B, T, H, P, R)
+    dt = F.softplus(dt_raw + p["dt_bias"].reshape(1, 1, H))         # :440-442
+    lam = torch.sigmoid(lam_raw) if learned_lambda else torch.full_like(dt, fixed_lambda)
+    theta = th_raw.reshape(B, T, H, N // 2) if rotational else None
+    y, st = O.mamba3_scan(x5, b, c, dt, p["a_log"], lam, theta, p.get("d_skip"), state, chunk, want_state)
+    gated = y.reshape(B, T, d_inner) * F.silu(z)                    # :475-484
+    return gated, hist, st

@@ -42,3 +42,29 @@ def test_conv_windows_with_history_equal_one_pass():
     y2, h2 = M.causal_conv1d(x[:, 2:7], wt, b, h1)
     y3, _ = M.causal_conv1d(x[:, 7:], wt, b, h2)
     assert rel_err(torch.cat([y1, y2, y3], 1), full) < 1e-14
+
+
+def core_golden():
+    z = np.load(GOLD / "mixer_core.npz")
+    p = {"conv_w": np.ascontiguousarray(z["conv_w"][:, 0, :].T), "conv_b": z["conv_b"], "dt_bias": z["dt_bias"],
+         "a_log": z["a_log"], "d_skip": z["d_skip"], "b_bias": z["b_bias"], "c_bias": z["c_bias"], "norm_w": z["norm_w"]}
+    return z, p
+
+
+def test_mixer_core_matches_reference_port():
+    """The whole stretch between the port's two projections: values and the gradient of every
+    parameter and of the projection itself."""
+    z, p = core_golden()
+    B, T, H, P, N = (int(v) for v in z["dims"])
+    proj = T64(z["proj"], True)
+    pt = {k: T64(v, True) for k, v in p.items()}
+    gated, _, _ = M.mixer_core(proj, pt, H, P, N, chunk=int(z["chunk"]), eps=float(z["eps"]))
+    assert rel_err(gated.detach(), z["gated"]) < 1e-12
+    names = list(pt)
+    grads = torch.autograd.grad((gated * T64(z["dgated"])).sum(), [proj] + [pt[n] for n in names])
+    assert rel_err(grads[0], z["dproj"]) < 1e-11
+    for n, g in zip(names, grads[1:]):
+        want = z["d_" + n]
+        if n == "conv_w":
+            want = want[:, 0, :].T
+        assert rel_err(g, want) < 1e-11, n

@@ -586,3 +586,80 @@ def test_conv_silu_replays_the_reference_ports_vectors():
     check_f32("dx", dx, torch.tensor(z["dx"]))
     check_f32("dw", dw, torch.tensor(np.ascontiguousarray(z["dw"][:, 0, :].T)))
     check_f32("db", db, torch.tensor(z["db"]))
+
+
+# ---- the mixer between its two projections (src/models/mamba3.rs:340-461, :475-484) --------------------------
+
+def _core_params(core, p):
+    with torch.no_grad():
+        for name, val in p.items():
+            par = getattr(core, name)
+            if par is not None and val is not None:
+                par.copy_(torch.as_tensor(val, dtype=torch.float32))
+
+
+def test_mixer_core_replays_the_reference_ports_vectors():
+    """tests/golden/mixer_core.npz: the reference port's whole mixer interior, values and the gradient
+    of the projection and of every parameter, through the CUDA path in float32."""
+    from pathlib import Path
+    from mamba_trainer_b200.nn import MixerCore, MixerShape
+    z = np.load(Path(__file__).resolve().parent / "golden" / "mixer_core.npz")
+    B, T, H, P, N = (int(v) for v in z["dims"])
+    core = MixerCore(MixerShape(H, P, N), conv_kernel=int(z["kernel"]), chunk=int(z["chunk"]), eps=float(z["eps"]),
+                     device="cuda")
+    p = {"conv_w": np.ascontiguousarray(z["conv_w"][:, 0, :].T), "conv_b": z["conv_b"], "dt_bias": z["dt_bias"],
+         "a_log": z["a_log"], "d_skip": z["d_skip"], "b_bias": z["b_bias"], "c_bias": z["c_bias"], "norm_w": z["norm_w"]}
+    _core_params(core, p)
+    proj = torch.tensor(z["proj"], dtype=torch.float32, device="cuda", requires_grad=True)
+    out = core(proj)
+    check_f32("gated", out, torch.tensor(z["gated"]))
+    names = list(p)
+    grads = torch.autograd.grad(out, [proj] + [getattr(core, n) for n in names],
+                                grad_outputs=torch.tensor(z["dgated"], dtype=torch.float32, device="cuda"))
+    check_f32("dproj", grads[0], torch.tensor(z["dproj"]))
+    for n, g in zip(names, grads[1:]):
+        want = z["d_" + n]
+        check_f32("d" + n, g, torch.tensor(np.ascontiguousarray(want[:, 0, :].T) if n == "conv_w" else want))
+
+
+@pytest.mark.parametrize("rank,groups,rot,learned,norm_gain", [
+    (1, None, True, True, True),        # the reference port's configuration at tensor-core sizes
+    (2, 1, True, True, True),           # MIMO, two heads sharing one group
+    (1, None, False, False, False),     # real dynamics, Euler, norm without gain
+])
+def test_mixer_core_bf16_matches_the_oracle(rank, groups, rot, learned, norm_gain):
+    from mamba_trainer_b200.nn import MixerCore, MixerShape
+    from oracle.mixer import mixer_core as oracle_core
+    H, P, N, B, T = 2, 64, 128, 2, 200
+    shape = MixerShape(H, P, N, rank, groups, learned, rot)
+    torch.manual_seed(rank * 7 + (groups or 0))
+    core = MixerCore(shape, chunk=64, norm_gain=norm_gain, device="cuda")
+    g = torch.Generator().manual_seed(5)
+    r = lambda *s: torch.randn(*s, generator=g)
+    p = {"conv_w": r(4, shape.conv_channels) * 0.4, "conv_b": r(shape.conv_channels) * 0.2, "dt_bias": r(H) * 0.3 - 3.0,
+         "a_log": torch.rand(H, generator=g) * 2, "d_skip": r(H), "b_bias": r(H, N) * 0.3, "c_bias": r(H, N) * 0.3,
+         "norm_w": (1.0 + r(N) * 0.2) if norm_gain else None}
+    _core_params(core, p)
+    proj = r(B, T, shape.in_proj_width).bfloat16()
+    dgated = r(B, T, shape.d_inner).bfloat16()
+    pd = proj.cuda().requires_grad_(True)
+    out = core(pd)
+    names = [n for n in p if p[n] is not None]
+    grads = torch.autograd.grad(out, [pd] + [getattr(core, n) for n in names], grad_outputs=dgated.cuda())
+    pc = proj.double().requires_grad_(True)
+    pt = {n: v.double().requires_grad_(True) for n, v in p.items() if v is not None}
+    eo, _, _ = oracle_core(pc, pt, H, P, N, rank, groups, 64, learned, rot)
+    eg = torch.autograd.grad(eo, [pc] + [pt[n] for n in names], grad_outputs=dgated.double())
+    check_bf16("gated", out, eo.detach())
+    # the projection's gradient band by band: the bands differ in scale by orders of magnitude
+    di, bc = shape.d_inner, shape.bc_width
+    cuts = {"z": (0, di), "x": (di, 2 * di), "B": (2 * di, 2 * di + bc), "C": (2 * di + bc, 2 * di + 2 * bc),
+            "dt": (2 * di + 2 * bc, 2 * di + 2 * bc + H)}
+    for name, (lo, hi) in cuts.items():
+        check_bf16("dproj." + name, grads[0][..., lo:hi], eg[0][..., lo:hi])
+    for n, a_, e_ in zip(names, grads[1:], eg[1:]):
+        if n in ("a_log", "dt_bias"):     # sums over every token with heavy cancellation: bf16 operands show
+            assert ref_metric(a_.float(), e_) <= 2e-2 * max(1.0, float(e_.abs().max())), n
+            assert norm_rel(a_.float(), e_) <= 5e-2, f"d{n}: {norm_rel(a_.float(), e_):.3e}"
+        else:
+            check_bf16("d" + n, a_, e_)
