@@ -312,22 +312,6 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
   }
 }
 
-// dw[k, c] / dbias[c] = sum over the blocks' partials, in block order.
-__global__ void k_conv_reduce(int nblk, int K, int C, const float* __restrict__ part, float* __restrict__ dw,
-                              float* __restrict__ dbias) {
-  const size_t n = (size_t)(K + 1) * C;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    float s = 0.0f;
-    for (int j = 0; j < nblk; ++j) s += part[(size_t)j * n + i];
-    const int k = i / C;
-    if (k < K) {
-      if (dw) dw[i] = s;
-    } else if (dbias) {
-      dbias[i - (size_t)K * C] = s;
-    }
-  }
-}
-
 int check(m3_ctx* ctx, const m3_conv_desc* c, ConvDims* d) {
   if (!ctx || !c) return M3_ERR_NULL;
   if (c->batch <= 0 || c->seq < 0 || c->channels <= 0)
@@ -465,10 +449,10 @@ int m3_conv_backward(m3_ctx* ctx, const m3_conv_desc* c, const void* dy, void* d
   }
   ctx->launches += 1;
   if (e == cudaSuccess && want_par) {
-    const size_t n = (size_t)(d.K + 1) * d.C;
-    k_conv_reduce<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(nblk, d.K, d.C, part, dweight, c->bias ? dbias : nullptr);
-    e = cudaGetLastError();
-    ctx->launches += 1;
+    const size_t n = (size_t)(d.K + 1) * d.C;  // a block's partial: K taps of C channels, then the bias
+    if (dweight) e = m3::column_sums(ctx->stream, part, nblk, n, d.K * d.C, dweight);
+    if (e == cudaSuccess && dbias && c->bias) e = m3::column_sums(ctx->stream, part + (size_t)d.K * d.C, nblk, n, d.C, dbias);
+    ctx->launches += (dweight ? 1 : 0) + ((dbias && c->bias) ? 1 : 0);
   }
   cudaError_t e2 = part ? cudaFreeAsync(part, ctx->stream) : cudaSuccess;
   if (e != cudaSuccess) return m3::cuda_fail(ctx, e, "conv backward");

@@ -74,4 +74,10 @@ cudaError_t generic_backward(cudaStream_t st, const Dims& d, const m3_scan_desc&
 cudaError_t finalize_scalars(cudaStream_t st, const Dims& d, const m3_scan_desc& desc, const GenericBwdWs& bw,
                              void* ddt, void* dlam, float* dalog, float* ddsk, uint64_t* launches);
 
+// out[g][c] (+)= sum_{t < nterms} part[g * part_group_stride + t * stride + c] for c < ncols, g < groups;
+// fixed summation order (see m3_reduce.cu).
+cudaError_t column_sums(cudaStream_t st, const float* part, int nterms, size_t stride, int ncols, float* out,
+                        bool accumulate = false, int groups = 1, size_t part_group_stride = 0,
+                        size_t out_group_stride = 0);
+
 }  // namespace m3

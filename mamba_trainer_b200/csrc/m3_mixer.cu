@@ -24,7 +24,7 @@ using m3::ldf;
 using m3::stf;
 
 constexpr int kBcWarps = 8;      // warps per block
-constexpr int kBcTokens = 64;    // tokens per block (8 per warp)
+constexpr int kBcTokens = 256;   // tokens per block (32 per warp)
 constexpr int kMaxPerLane = 8;   // d_state <= 32 * kMaxPerLane = 256 on the fast path
 
 struct BcDims {
@@ -72,6 +72,75 @@ __global__ void __launch_bounds__(kBcWarps * 32)
       const int n = lane + 32 * j;
       if (n < d.N) stf(dst, (size_t)n * d.R + r, v[j] * scale * ((d.has_norm && gain) ? gain[n] : 1.0f));
     }
+  }
+}
+
+// ---- the same for bf16 with d_state a multiple of 128 (at most 256): a lane owns runs of four
+// consecutive state columns, reads them with 8-byte loads and writes its 4 x R outputs contiguously.
+__device__ __forceinline__ void unpack4(const uint2& q, float (&v)[4]) {
+  v[0] = __uint_as_float(q.x << 16); v[1] = __uint_as_float(q.x & 0xffff0000u);
+  v[2] = __uint_as_float(q.y << 16); v[3] = __uint_as_float(q.y & 0xffff0000u);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int R, int NJ>
+__global__ void __launch_bounds__(kBcWarps * 32)
+    k_bc_fwd_vec(BcDims d, const __nv_bfloat16* __restrict__ raw, const float* __restrict__ bias,
+                 const float* __restrict__ gain, __nv_bfloat16* __restrict__ out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t row = (size_t)blockIdx.x * kBcWarps + warp;
+  if (row >= (size_t)d.B * d.T * d.H) return;
+  const int h = row % d.H;
+  const size_t bt = row / d.H;
+  const int g = h / d.PG;
+  const __nv_bfloat16* src = raw + bt * d.rs + (size_t)g * R * d.N;
+  __nv_bfloat16* dst = out + row * d.N * R;
+  uint2 q[R][NJ];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) q[r][j] = __ldg(reinterpret_cast<const uint2*>(src + (size_t)r * d.N + 4 * lane + 128 * j));
+  float bs[NJ][4], gn[NJ][4];
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    const int n0 = 4 * lane + 128 * j;
+    const float4 b4 = bias ? __ldg(reinterpret_cast<const float4*>(bias + (size_t)h * d.N + n0)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 g4 = (d.has_norm && gain) ? __ldg(reinterpret_cast<const float4*>(gain + n0)) : make_float4(1.f, 1.f, 1.f, 1.f);
+    bs[j][0] = b4.x; bs[j][1] = b4.y; bs[j][2] = b4.z; bs[j][3] = b4.w;
+    gn[j][0] = g4.x; gn[j][1] = g4.y; gn[j][2] = g4.z; gn[j][3] = g4.w;
+  }
+  float o[NJ][4][R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float v[NJ][4];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      unpack4(q[r][j], v[j]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[j][i] += bs[j][i];
+        ss += v[j][i] * v[j][i];
+      }
+    }
+    const float scale = d.has_norm ? rsqrtf(warp_sum(ss) / (float)d.N + d.eps) : 1.0f;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[j][i][r] = v[j][i] * scale * gn[j][i];
+  }
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {  // 4 x R consecutive outputs: (n0, r = 0..R-1), (n0 + 1, ...), ...
+    const float* flat = &o[j][0][0];
+    uint32_t w[2 * R];
+#pragma unroll
+    for (int k = 0; k < 2 * R; ++k) w[k] = pack2(flat[2 * k], flat[2 * k + 1]);
+    uint2* dp = reinterpret_cast<uint2*>(dst + (size_t)(4 * lane + 128 * j) * R);
+#pragma unroll
+    for (int k = 0; k < R; ++k) dp[k] = make_uint2(w[2 * k], w[2 * k + 1]);
   }
 }
 
@@ -155,26 +224,136 @@ __global__ void __launch_bounds__(kBcWarps * 32)
   }
 }
 
-// d bias[h, n] = sum over token blocks of the partial of (group(h), h % PG); d gain[n] = sum over
-// token blocks and groups; block order.
-__global__ void k_bc_reduce(BcDims d, int nblk_tok, const float* __restrict__ part, float* __restrict__ dbias,
-                            float* __restrict__ dgain, int accumulate_gain) {
+// The same for bf16 with d_state 128 or 256 and rank 1, 2 or 4: 8-byte loads and stores, the
+// partial sums as float4 in the warp's private shared-memory slice.
+template <int R, int NJ>
+__global__ void __launch_bounds__(kBcWarps * 32)
+    k_bc_bwd_vec(BcDims d, const __nv_bfloat16* __restrict__ raw, const float* __restrict__ bias,
+                 const float* __restrict__ gain, const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ draw,
+                 float* __restrict__ part) {
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = blockIdx.y;
+  const size_t ntok = (size_t)d.B * d.T;
+  const size_t tok0 = (size_t)blockIdx.x * kBcTokens;
   const int width = (d.PG + 1) * d.N;
-  const size_t n_bias = (size_t)d.H * d.N;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_bias + d.N; i += (size_t)gridDim.x * blockDim.x) {
-    if (i < n_bias) {
-      if (!dbias) continue;
-      const int h = i / d.N, n = i % d.N, g = h / d.PG, hg = h % d.PG;
-      float s = 0.0f;
-      for (int bk = 0; bk < nblk_tok; ++bk) s += part[((size_t)bk * d.G + g) * width + (size_t)hg * d.N + n];
-      dbias[i] = s;
-    } else if (dgain) {
-      const int n = i - n_bias;
-      float s = accumulate_gain ? dgain[n] : 0.0f;
-      for (int bk = 0; bk < nblk_tok; ++bk)
-        for (int g = 0; g < d.G; ++g) s += part[((size_t)bk * d.G + g) * width + (size_t)d.PG * d.N + n];
-      dgain[n] = s;
+  float* mine = sm + (size_t)warp * width;
+  for (int i = lane; i < width; i += 32) mine[i] = 0.0f;
+  __syncwarp();
+  float gn[NJ][4];
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    const float4 g4 = (d.has_norm && gain) ? __ldg(reinterpret_cast<const float4*>(gain + 4 * lane + 128 * j)) : make_float4(1.f, 1.f, 1.f, 1.f);
+    gn[j][0] = g4.x; gn[j][1] = g4.y; gn[j][2] = g4.z; gn[j][3] = g4.w;
+  }
+  for (int it = warp; it < kBcTokens; it += kBcWarps) {
+    const size_t bt = tok0 + it;
+    if (bt >= ntok) break;
+    const __nv_bfloat16* src = raw + bt * d.rs + (size_t)g * R * d.N;
+    uint2 q[R][NJ];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) q[r][j] = __ldg(reinterpret_cast<const uint2*>(src + (size_t)r * d.N + 4 * lane + 128 * j));
+    float acc[R][NJ][4];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int j = 0; j < NJ; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[r][j][i] = 0.0f;
+    for (int hg = 0; hg < d.PG; ++hg) {
+      const int h = g * d.PG + hg;
+      const __nv_bfloat16* go = dout + (bt * d.H + h) * d.N * R;
+      float gy[NJ][4][R];  // (n0 + i, r), as stored
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        const uint2* gp = reinterpret_cast<const uint2*>(go + (size_t)(4 * lane + 128 * j) * R);
+        float* flat = &gy[j][0][0];
+#pragma unroll
+        for (int k = 0; k < R; ++k) {
+          float t4[4];
+          unpack4(__ldg(gp + k), t4);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) flat[4 * k + i] = t4[i];
+        }
+      }
+      float bs[NJ][4];
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        const float4 b4 = bias ? __ldg(reinterpret_cast<const float4*>(bias + (size_t)h * d.N + 4 * lane + 128 * j)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        bs[j][0] = b4.x; bs[j][1] = b4.y; bs[j][2] = b4.z; bs[j][3] = b4.w;
+      }
+      float dbias[NJ][4], dgain[NJ][4];
+#pragma unroll
+      for (int j = 0; j < NJ; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dbias[j][i] = dgain[j][i] = 0.0f;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float v[NJ][4], dxh[NJ][4];
+        float ss = 0.0f, dot = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+          unpack4(q[r][j], v[j]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            v[j][i] += bs[j][i];
+            ss += v[j][i] * v[j][i];
+            dxh[j][i] = gy[j][i][r] * gn[j][i];
+          }
+        }
+        float rstd = 1.0f, mean_dot = 0.0f;
+        if (d.has_norm) {
+          rstd = rsqrtf(warp_sum(ss) / (float)d.N + d.eps);
+#pragma unroll
+          for (int j = 0; j < NJ; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dot += dxh[j][i] * v[j][i] * rstd;
+          mean_dot = warp_sum(dot) / (float)d.N;
+        }
+#pragma unroll
+        for (int j = 0; j < NJ; ++j)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float xh = v[j][i] * rstd;
+            const float dv = d.has_norm ? rstd * (dxh[j][i] - xh * mean_dot) : dxh[j][i];
+            acc[r][j][i] += dv;
+            dbias[j][i] += dv;
+            dgain[j][i] += gy[j][i][r] * xh;
+          }
+      }
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        float4* pb = reinterpret_cast<float4*>(mine + (size_t)hg * d.N + 4 * lane + 128 * j);
+        float4 t = *pb;
+        t.x += dbias[j][0]; t.y += dbias[j][1]; t.z += dbias[j][2]; t.w += dbias[j][3];
+        *pb = t;
+        if (d.has_norm && gain) {
+          float4* pg = reinterpret_cast<float4*>(mine + (size_t)d.PG * d.N + 4 * lane + 128 * j);
+          float4 u = *pg;
+          u.x += dgain[j][0]; u.y += dgain[j][1]; u.z += dgain[j][2]; u.w += dgain[j][3];
+          *pg = u;
+        }
+      }
     }
+    if (draw) {
+      __nv_bfloat16* dr = draw + bt * d.rs + (size_t)g * R * d.N;
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int j = 0; j < NJ; ++j)
+          *reinterpret_cast<uint2*>(dr + (size_t)r * d.N + 4 * lane + 128 * j) =
+              make_uint2(pack2(acc[r][j][0], acc[r][j][1]), pack2(acc[r][j][2], acc[r][j][3]));
+    }
+  }
+  __syncthreads();
+  if (!part) return;
+  const size_t blk = (size_t)blockIdx.x * gridDim.y + g;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float s = 0.0f;
+    for (int w = 0; w < kBcWarps; ++w) s += sm[(size_t)w * width + i];
+    part[blk * width + i] = s;
   }
 }
 
@@ -194,37 +373,31 @@ __global__ void k_act_fwd(int ntok, int H, long long stride, const T* __restrict
   }
 }
 
-constexpr int kActBlocks = 64;
-// One block per slice of tokens; thread h' strides over heads, so each head's partial sum of the
-// bias gradient has a fixed order.
+constexpr int kActRun = 32;  // tokens per thread of the backward pass
+// Thread (run, head): walks kActRun tokens of one head and leaves that run's partial sum of the bias
+// gradient; the runs are added by column_sums.
 template <class T>
 __global__ void k_act_bwd(int ntok, int H, long long stride, const T* __restrict__ dt_raw, const T* __restrict__ lam_raw,
                           const float* __restrict__ dt_bias, const T* __restrict__ ddt, const T* __restrict__ dlam,
                           T* __restrict__ ddt_raw, T* __restrict__ dlam_raw, float* __restrict__ part) {
-  const int per = (ntok + gridDim.x - 1) / gridDim.x;
-  const int lo = blockIdx.x * per, hi = min(ntok, lo + per);
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
-    float s = 0.0f;
-    for (int bt = lo; bt < hi; ++bt) {
-      const size_t i = (size_t)bt * H + h, j = (size_t)bt * stride + h;
-      const float g = ldf(ddt, i) * sigmoid(ldf(dt_raw, j) + (dt_bias ? dt_bias[h] : 0.0f));
-      if (ddt_raw) stf(ddt_raw, j, g);
-      s += g;
-      if (lam_raw && dlam && dlam_raw) {
-        const float l = sigmoid(ldf(lam_raw, j));
-        stf(dlam_raw, j, ldf(dlam, i) * l * (1.0f - l));
-      }
+  const int nruns = (ntok + kActRun - 1) / kActRun;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)nruns * H) return;
+  const int h = i % H, run = i / H;
+  const int lo = run * kActRun, hi = min(ntok, lo + kActRun);
+  const float bias = dt_bias ? dt_bias[h] : 0.0f;
+  float s = 0.0f;
+  for (int bt = lo; bt < hi; ++bt) {
+    const size_t a = (size_t)bt * H + h, j = (size_t)bt * stride + h;
+    const float g = ldf(ddt, a) * sigmoid(ldf(dt_raw, j) + bias);
+    if (ddt_raw) stf(ddt_raw, j, g);
+    s += g;
+    if (lam_raw && dlam && dlam_raw) {
+      const float l = sigmoid(ldf(lam_raw, j));
+      stf(dlam_raw, j, ldf(dlam, a) * l * (1.0f - l));
     }
-    if (part) part[(size_t)blockIdx.x * H + h] = s;
   }
-}
-
-__global__ void k_act_reduce(int nblk, int H, const float* __restrict__ part, float* __restrict__ dbias) {
-  for (int h = blockIdx.x * blockDim.x + threadIdx.x; h < H; h += gridDim.x * blockDim.x) {
-    float s = 0.0f;
-    for (int b = 0; b < nblk; ++b) s += part[(size_t)b * H + h];
-    dbias[h] = s;
-  }
+  if (part) part[i] = s;
 }
 
 // ---- gate -----------------------------------------------------------------------------------------------
@@ -326,7 +499,25 @@ int m3_bc_forward(m3_ctx* ctx, const m3_bc_desc* s, void* b, void* c) {
   M3_CUDA(ctx, cudaSetDevice(ctx->device));
   const size_t rows = (size_t)d.B * d.T * d.H;
   const unsigned grid = (unsigned)((rows + kBcWarps - 1) / kBcWarps);
-  if (s->dtype == M3_BF16) {
+  const bool aligned = !(d.rs % 4) && !(reinterpret_cast<uintptr_t>(s->b_raw) % 8) && !(reinterpret_cast<uintptr_t>(s->c_raw) % 8) &&
+                       !(reinterpret_cast<uintptr_t>(b) % 8) && !(reinterpret_cast<uintptr_t>(c) % 8) &&
+                       !(reinterpret_cast<uintptr_t>(s->b_bias) % 16) && !(reinterpret_cast<uintptr_t>(s->c_bias) % 16) &&
+                       !(reinterpret_cast<uintptr_t>(s->norm_weight) % 16);
+  if (s->dtype == M3_BF16 && aligned && (d.N == 128 || d.N == 256) && (d.R == 1 || d.R == 2 || d.R == 4)) {
+    using T = __nv_bfloat16;
+    for (int which = 0; which < 2; ++which) {
+      const T* raw = static_cast<const T*>(which ? s->c_raw : s->b_raw);
+      const float* bias = which ? s->c_bias : s->b_bias;
+      T* out = static_cast<T*>(which ? c : b);
+#define M3_BC_FWD(RR, NJ) k_bc_fwd_vec<RR, NJ><<<grid, kBcWarps * 32, 0, ctx->stream>>>(d, raw, bias, s->norm_weight, out)
+      if (d.N == 128) {
+        if (d.R == 1) M3_BC_FWD(1, 1); else if (d.R == 2) M3_BC_FWD(2, 1); else M3_BC_FWD(4, 1);
+      } else {
+        if (d.R == 1) M3_BC_FWD(1, 2); else if (d.R == 2) M3_BC_FWD(2, 2); else M3_BC_FWD(4, 2);
+      }
+#undef M3_BC_FWD
+    }
+  } else if (s->dtype == M3_BF16) {
     using T = __nv_bfloat16;
     k_bc_fwd<T><<<grid, kBcWarps * 32, 0, ctx->stream>>>(d, static_cast<const T*>(s->b_raw), s->b_bias, s->norm_weight, static_cast<T*>(b));
     k_bc_fwd<T><<<grid, kBcWarps * 32, 0, ctx->stream>>>(d, static_cast<const T*>(s->c_raw), s->c_bias, s->norm_weight, static_cast<T*>(c));
@@ -367,7 +558,21 @@ int m3_bc_backward(m3_ctx* ctx, const m3_bc_desc* s, const void* db, const void*
     const void* go = which ? dc : db;
     void* draw = which ? dc_raw : db_raw;
     float* dbias = bias ? (which ? dc_bias : db_bias) : nullptr;
-    if (s->dtype == M3_BF16) {
+    const bool aligned = !(d.rs % 4) && !(reinterpret_cast<uintptr_t>(raw) % 8) && !(reinterpret_cast<uintptr_t>(go) % 8) &&
+                         !(reinterpret_cast<uintptr_t>(draw) % 8) && !(reinterpret_cast<uintptr_t>(bias) % 16) &&
+                         !(reinterpret_cast<uintptr_t>(s->norm_weight) % 16);
+    if (s->dtype == M3_BF16 && aligned && smem <= 48 * 1024 && (d.N == 128 || d.N == 256) && (d.R == 1 || d.R == 2 || d.R == 4)) {
+      using T = __nv_bfloat16;
+#define M3_BC_BWD(RR, NJ)                                                                                            \
+  k_bc_bwd_vec<RR, NJ><<<grid, kBcWarps * 32, smem, ctx->stream>>>(d, static_cast<const T*>(raw), bias, s->norm_weight, \
+                                                                   static_cast<const T*>(go), static_cast<T*>(draw), part)
+      if (d.N == 128) {
+        if (d.R == 1) M3_BC_BWD(1, 1); else if (d.R == 2) M3_BC_BWD(2, 1); else M3_BC_BWD(4, 1);
+      } else {
+        if (d.R == 1) M3_BC_BWD(1, 2); else if (d.R == 2) M3_BC_BWD(2, 2); else M3_BC_BWD(4, 2);
+      }
+#undef M3_BC_BWD
+    } else if (s->dtype == M3_BF16) {
       using T = __nv_bfloat16;
       if (smem > 48 * 1024) e = cudaFuncSetAttribute(k_bc_bwd<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e == cudaSuccess)
@@ -380,13 +585,13 @@ int m3_bc_backward(m3_ctx* ctx, const m3_bc_desc* s, const void* db, const void*
                                                                      static_cast<const float*>(go), static_cast<float*>(draw), part);
     }
     if (e == cudaSuccess) e = cudaGetLastError();
-    if (e == cudaSuccess) {
-      // the gain is shared by B and C (one bc_norm module): the second pass adds to the first
-      float* dgain = (d.has_norm && s->norm_weight) ? dnorm_weight : nullptr;
-      k_bc_reduce<<<64, 256, 0, ctx->stream>>>(d, nblk_tok, part, dbias, dgain, which);
-      e = cudaGetLastError();
-    }
-    ctx->launches += 2;
+    if (e == cudaSuccess && dbias)  // d bias[g * PG + hg, n]: the first PG * N columns of group g's partials
+      e = m3::column_sums(ctx->stream, part, nblk_tok, (size_t)d.G * width, d.PG * d.N, dbias, false, d.G, width,
+                          (size_t)d.PG * d.N);
+    // the gain is shared by B and C (one bc_norm module): the second pass adds to the first
+    if (e == cudaSuccess && d.has_norm && s->norm_weight && dnorm_weight)
+      e = m3::column_sums(ctx->stream, part + (size_t)d.PG * d.N, nblk_tok * d.G, width, d.N, dnorm_weight, which == 1);
+    ctx->launches += 3;
   }
   cudaError_t e2 = cudaFreeAsync(part, ctx->stream);
   if (e != cudaSuccess) return m3::cuda_fail(ctx, e, "B/C prologue backward");
@@ -431,27 +636,27 @@ int m3_dt_lambda_backward(m3_ctx* ctx, const m3_act_desc* s, const void* ddt, co
   }
   const int ntok = s->batch * s->seq;
   const long long st = s->stride ? s->stride : s->heads;
-  const int nblk = ntok < kActBlocks * 4 ? 1 + ntok / 64 : kActBlocks * 4;
+  const int nruns = (ntok + kActRun - 1) / kActRun;
   float* part = nullptr;
   const bool want_bias = ddt_bias && s->dt_bias;
-  if (want_bias) M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&part), (size_t)nblk * s->heads * sizeof(float), ctx->stream));
-  const int threads = s->heads < 32 ? 32 : (s->heads > 256 ? 256 : ((s->heads + 31) / 32) * 32);
+  if (want_bias) M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&part), (size_t)nruns * s->heads * sizeof(float), ctx->stream));
+  const size_t nthreads = (size_t)nruns * s->heads;
+  const unsigned grid = (unsigned)((nthreads + 127) / 128);
   if (s->dtype == M3_BF16) {
     using T = __nv_bfloat16;
-    k_act_bwd<T><<<nblk, threads, 0, ctx->stream>>>(ntok, s->heads, st, static_cast<const T*>(s->dt_raw), static_cast<const T*>(s->lambda_raw),
-                                                     s->dt_bias, static_cast<const T*>(ddt), static_cast<const T*>(dlambda),
-                                                     static_cast<T*>(ddt_raw), static_cast<T*>(dlambda_raw), part);
+    k_act_bwd<T><<<grid, 128, 0, ctx->stream>>>(ntok, s->heads, st, static_cast<const T*>(s->dt_raw), static_cast<const T*>(s->lambda_raw),
+                                                 s->dt_bias, static_cast<const T*>(ddt), static_cast<const T*>(dlambda),
+                                                 static_cast<T*>(ddt_raw), static_cast<T*>(dlambda_raw), part);
   } else {
-    k_act_bwd<float><<<nblk, threads, 0, ctx->stream>>>(ntok, s->heads, st, static_cast<const float*>(s->dt_raw),
-                                                         static_cast<const float*>(s->lambda_raw), s->dt_bias, static_cast<const float*>(ddt),
-                                                         static_cast<const float*>(dlambda), static_cast<float*>(ddt_raw),
-                                                         static_cast<float*>(dlambda_raw), part);
+    k_act_bwd<float><<<grid, 128, 0, ctx->stream>>>(ntok, s->heads, st, static_cast<const float*>(s->dt_raw),
+                                                     static_cast<const float*>(s->lambda_raw), s->dt_bias, static_cast<const float*>(ddt),
+                                                     static_cast<const float*>(dlambda), static_cast<float*>(ddt_raw),
+                                                     static_cast<float*>(dlambda_raw), part);
   }
   cudaError_t e = cudaGetLastError();
   ctx->launches += 1;
   if (e == cudaSuccess && want_bias) {
-    k_act_reduce<<<(s->heads + 255) / 256, 256, 0, ctx->stream>>>(nblk, s->heads, part, ddt_bias);
-    e = cudaGetLastError();
+    e = m3::column_sums(ctx->stream, part, nruns, s->heads, s->heads, ddt_bias);
     ctx->launches += 1;
   }
   cudaError_t e2 = part ? cudaFreeAsync(part, ctx->stream) : cudaSuccess;
