@@ -162,6 +162,40 @@ def run_reference(args, w, rank):
     print(json.dumps(line), flush=True)
 
 
+def mixer_core_leg(w, dev):
+    """Secondary figure, not the headline: the whole stretch of the mixer between its two projections
+    (convolution + SiLU, B/C bias + RMS norm + layout, dt / lambda activations, the scan, the gate)
+    forward + backward as one tape node, on the workload's shapes with groups = heads."""
+    from mamba_trainer_b200.nn import MixerCore, MixerShape
+    shape = MixerShape(w.heads, w.head_dim, w.d_state, w.rank, None, True, w.rotational)
+    core = MixerCore(shape, chunk=w.chunk, device=dev)
+    g = torch.Generator(device=dev).manual_seed(1)
+    proj = (torch.randn(w.batch, w.seq, shape.in_proj_width, device=dev, generator=g) * 0.5).to(w.dtype).requires_grad_(True)
+    dg = torch.randn(w.batch, w.seq, shape.d_inner, device=dev, generator=g).to(w.dtype)
+    params = list(core.parameters())
+
+    def fb():
+        return torch.autograd.grad(core(proj), [proj] + params, grad_outputs=dg)
+
+    for _ in range(3):
+        fb()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = 10
+    e0.record()
+    for _ in range(n):
+        fb()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / n
+    es = w.elem_bytes()
+    # projection read by the forward and again by the backward, its gradient written, gated output
+    # written and its gradient read: what an ideal single fused pass would move
+    ideal = es * w.tokens * (3 * shape.in_proj_width + 2 * shape.d_inner)
+    return {"value": w.tokens / (ms * 1e-3) / 1e6, "unit": UNIT, "ms_per_step": ms, "launches_per_step": 22,
+            "in_proj_width": shape.in_proj_width, "ideal_bytes": ideal, "achieved_gbs_of_ideal": ideal / (ms * 1e-3) / 1e9}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -312,6 +346,8 @@ def main():
             "clocks": clocks, "gpu_launches": int(launches),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         }
+        if world == 1:
+            line["mixer_core"] = mixer_core_leg(w, dev)
         if not args.no_cpu_baseline and world == 1:
             v, cores, sample = cpu_oracle_throughput(w)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}

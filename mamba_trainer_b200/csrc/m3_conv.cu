@@ -116,9 +116,11 @@ __device__ __forceinline__ T* out_band(const ConvDims& d, T* y, T* y2, int c0, l
   return y + c0;
 }
 
-__device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
+// Fast-math division (2 ulp): the kernels are bound by instruction issue, and an IEEE division
+// costs about as much as the rest of a tap loop.
+__device__ __forceinline__ float silu(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 __device__ __forceinline__ float silu_grad(float v) {
-  const float s = 1.0f / (1.0f + __expf(-v));
+  const float s = __fdividef(1.0f, 1.0f + __expf(-v));
   return s * (1.0f + v * (1.0f - s));
 }
 
@@ -203,7 +205,7 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
     k_conv_bwd(ConvDims d, const T* __restrict__ x, const T* __restrict__ hist, const float* __restrict__ w,
                const float* __restrict__ bias, const T* __restrict__ dy, const T* __restrict__ dy2, T* __restrict__ dx,
                T* __restrict__ dhist, float* __restrict__ part) {
-  __shared__ float red[kLanesT][kLanesC * V + 1];
+  __shared__ float red[kLanesT][V][kLanesC + 1];  // [time lane][element of the vector][channel lane]: conflict-free
   const int c0 = (blockIdx.x * kLanesC + threadIdx.x) * V;
   const int b = blockIdx.z;
   const int t0 = (blockIdx.y * kLanesT + threadIdx.y) * kRun;
@@ -298,14 +300,14 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
     if (k < pad) continue;  // a padding tap has no gradient
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < V; ++i) red[threadIdx.y][threadIdx.x * V + i] = (k == KT) ? pb[i] : pw[k < KT ? k : 0][i];
+    for (int i = 0; i < V; ++i) red[threadIdx.y][i][threadIdx.x] = (k == KT) ? pb[i] : pw[k < KT ? k : 0][i];
     __syncthreads();
     if (threadIdx.y == 0 && c0 < d.C) {
 #pragma unroll
       for (int i = 0; i < V; ++i) {
         float s = 0.0f;
 #pragma unroll
-        for (int ty = 0; ty < kLanesT; ++ty) s += red[ty][threadIdx.x * V + i];
+        for (int ty = 0; ty < kLanesT; ++ty) s += red[ty][i][threadIdx.x];
         part[(blk * (d.K + 1) + (k - pad)) * d.C + c0 + i] = s;
       }
     }

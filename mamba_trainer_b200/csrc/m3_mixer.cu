@@ -75,73 +75,83 @@ __global__ void __launch_bounds__(kBcWarps * 32)
   }
 }
 
-// ---- the same for bf16 with d_state a multiple of 128 (at most 256): a lane owns runs of four
-// consecutive state columns, reads them with 8-byte loads and writes its 4 x R outputs contiguously.
-__device__ __forceinline__ void unpack4(const uint2& q, float (&v)[4]) {
+// ---- the same for bf16 with d_state 128 or 256: a lane owns 16 consecutive state columns (two
+// 16-byte loads per rank), so a row takes d_state / 16 lanes and a warp works on 2 or 4 rows at once;
+// the row's sum of squares is a 3- or 4-step shuffle.  These kernels are bound by instruction
+// issue, not by memory, so work per instruction is what counts.
+__device__ __forceinline__ void unpack8(const uint4& q, float* v) {
   v[0] = __uint_as_float(q.x << 16); v[1] = __uint_as_float(q.x & 0xffff0000u);
   v[2] = __uint_as_float(q.y << 16); v[3] = __uint_as_float(q.y & 0xffff0000u);
+  v[4] = __uint_as_float(q.z << 16); v[5] = __uint_as_float(q.z & 0xffff0000u);
+  v[6] = __uint_as_float(q.w << 16); v[7] = __uint_as_float(q.w & 0xffff0000u);
 }
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+__device__ __forceinline__ void load16f(const float* p, float (&v)[16]) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float4 t = __ldg(reinterpret_cast<const float4*>(p) + k);
+    v[4 * k] = t.x; v[4 * k + 1] = t.y; v[4 * k + 2] = t.z; v[4 * k + 3] = t.w;
+  }
+}
+template <int LPR>
+__device__ __forceinline__ float row_sum(float v) {  // over the LPR adjacent lanes of one row
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
 
-template <int R, int NJ>
+template <int R, int N>
 __global__ void __launch_bounds__(kBcWarps * 32)
     k_bc_fwd_vec(BcDims d, const __nv_bfloat16* __restrict__ raw, const float* __restrict__ bias,
                  const float* __restrict__ gain, __nv_bfloat16* __restrict__ out) {
+  constexpr int LPR = N / 16, RPW = 32 / LPR;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const size_t row = (size_t)blockIdx.x * kBcWarps + warp;
-  if (row >= (size_t)d.B * d.T * d.H) return;
+  const int sub = lane % LPR, n0 = 16 * sub;
+  const size_t rows = (size_t)d.B * d.T * d.H;
+  const size_t row_raw = ((size_t)blockIdx.x * kBcWarps + warp) * RPW + lane / LPR;
+  const bool valid = row_raw < rows;
+  const size_t row = valid ? row_raw : rows - 1;  // every lane takes part in the shuffles
   const int h = row % d.H;
   const size_t bt = row / d.H;
   const int g = h / d.PG;
-  const __nv_bfloat16* src = raw + bt * d.rs + (size_t)g * R * d.N;
-  __nv_bfloat16* dst = out + row * d.N * R;
-  uint2 q[R][NJ];
-#pragma unroll
-  for (int r = 0; r < R; ++r)
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) q[r][j] = __ldg(reinterpret_cast<const uint2*>(src + (size_t)r * d.N + 4 * lane + 128 * j));
-  float bs[NJ][4], gn[NJ][4];
-#pragma unroll
-  for (int j = 0; j < NJ; ++j) {
-    const int n0 = 4 * lane + 128 * j;
-    const float4 b4 = bias ? __ldg(reinterpret_cast<const float4*>(bias + (size_t)h * d.N + n0)) : make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4 g4 = (d.has_norm && gain) ? __ldg(reinterpret_cast<const float4*>(gain + n0)) : make_float4(1.f, 1.f, 1.f, 1.f);
-    bs[j][0] = b4.x; bs[j][1] = b4.y; bs[j][2] = b4.z; bs[j][3] = b4.w;
-    gn[j][0] = g4.x; gn[j][1] = g4.y; gn[j][2] = g4.z; gn[j][3] = g4.w;
-  }
-  float o[NJ][4][R];
+  const __nv_bfloat16* src = raw + bt * d.rs + (size_t)g * R * N + n0;
+  uint4 q[R][2];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    float v[NJ][4];
+    q[r][0] = __ldg(reinterpret_cast<const uint4*>(src + (size_t)r * N));
+    q[r][1] = __ldg(reinterpret_cast<const uint4*>(src + (size_t)r * N + 8));
+  }
+  float bs[16], gn[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { bs[i] = 0.0f; gn[i] = 1.0f; }
+  if (bias) load16f(bias + (size_t)h * N + n0, bs);
+  if (d.has_norm && gain) load16f(gain + n0, gn);
+  float o[16][R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float v[16];
+    unpack8(q[r][0], v);
+    unpack8(q[r][1], v + 8);
     float ss = 0.0f;
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      unpack4(q[r][j], v[j]);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        v[j][i] += bs[j][i];
-        ss += v[j][i] * v[j][i];
-      }
+    for (int i = 0; i < 16; ++i) {
+      v[i] += bs[i];
+      ss = fmaf(v[i], v[i], ss);
     }
-    const float scale = d.has_norm ? rsqrtf(warp_sum(ss) / (float)d.N + d.eps) : 1.0f;
+    const float scale = d.has_norm ? rsqrtf(row_sum<LPR>(ss) * (1.0f / N) + d.eps) : 1.0f;
 #pragma unroll
-    for (int j = 0; j < NJ; ++j)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) o[j][i][r] = v[j][i] * scale * gn[j][i];
+    for (int i = 0; i < 16; ++i) o[i][r] = v[i] * scale * gn[i];
   }
+  if (!valid) return;
+  const float* flat = &o[0][0];  // (n0 + i, r) in storage order: 16 * R consecutive outputs
+  uint4* dp = reinterpret_cast<uint4*>(out + row * N * R + (size_t)n0 * R);
 #pragma unroll
-  for (int j = 0; j < NJ; ++j) {  // 4 x R consecutive outputs: (n0, r = 0..R-1), (n0 + 1, ...), ...
-    const float* flat = &o[j][0][0];
-    uint32_t w[2 * R];
-#pragma unroll
-    for (int k = 0; k < 2 * R; ++k) w[k] = pack2(flat[2 * k], flat[2 * k + 1]);
-    uint2* dp = reinterpret_cast<uint2*>(dst + (size_t)(4 * lane + 128 * j) * R);
-#pragma unroll
-    for (int k = 0; k < R; ++k) dp[k] = make_uint2(w[2 * k], w[2 * k + 1]);
-  }
+  for (int k = 0; k < 2 * R; ++k)
+    dp[k] = make_uint4(pack2(flat[8 * k], flat[8 * k + 1]), pack2(flat[8 * k + 2], flat[8 * k + 3]),
+                       pack2(flat[8 * k + 4], flat[8 * k + 5]), pack2(flat[8 * k + 6], flat[8 * k + 7]));
 }
 
 // ---- B / C backward: a block owns one group and kBcTokens tokens; a warp walks tokens, sums the
@@ -224,142 +234,113 @@ __global__ void __launch_bounds__(kBcWarps * 32)
   }
 }
 
-// The same for bf16 with d_state 128 or 256 and rank 1, 2 or 4: 8-byte loads and stores, the
-// partial sums as float4 in the warp's private shared-memory slice.
-template <int R, int NJ>
+// The same for bf16, d_state 128 or 256, one head per group: 16 columns per lane as in the forward
+// kernel, the bias / gain partial sums in registers across the warp's tokens, then added over the
+// warp's rows by shuffles (a fixed tree) and over the block's warps through shared memory.
+template <int R, int N>
 __global__ void __launch_bounds__(kBcWarps * 32)
     k_bc_bwd_vec(BcDims d, const __nv_bfloat16* __restrict__ raw, const float* __restrict__ bias,
                  const float* __restrict__ gain, const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ draw,
                  float* __restrict__ part) {
-  extern __shared__ float sm[];
+  constexpr int LPR = N / 16, RPW = 32 / LPR;
+  __shared__ float sm[kBcWarps][2][N];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int g = blockIdx.y;
+  const int sub = lane % LPR, rw = lane / LPR, n0 = 16 * sub;
+  const int g = blockIdx.y, h = g;  // PG == 1
   const size_t ntok = (size_t)d.B * d.T;
   const size_t tok0 = (size_t)blockIdx.x * kBcTokens;
-  const int width = (d.PG + 1) * d.N;
-  float* mine = sm + (size_t)warp * width;
-  for (int i = lane; i < width; i += 32) mine[i] = 0.0f;
-  __syncwarp();
-  float gn[NJ][4];
+  float bs[16], gn[16], pbias[16], pgain[16];
 #pragma unroll
-  for (int j = 0; j < NJ; ++j) {
-    const float4 g4 = (d.has_norm && gain) ? __ldg(reinterpret_cast<const float4*>(gain + 4 * lane + 128 * j)) : make_float4(1.f, 1.f, 1.f, 1.f);
-    gn[j][0] = g4.x; gn[j][1] = g4.y; gn[j][2] = g4.z; gn[j][3] = g4.w;
-  }
-  for (int it = warp; it < kBcTokens; it += kBcWarps) {
-    const size_t bt = tok0 + it;
-    if (bt >= ntok) break;
-    const __nv_bfloat16* src = raw + bt * d.rs + (size_t)g * R * d.N;
-    uint2 q[R][NJ];
+  for (int i = 0; i < 16; ++i) { bs[i] = 0.0f; gn[i] = 1.0f; pbias[i] = 0.0f; pgain[i] = 0.0f; }
+  if (bias) load16f(bias + (size_t)h * N + n0, bs);
+  const bool use_gain = d.has_norm && gain;
+  if (use_gain) load16f(gain + n0, gn);
+  for (int it = warp * RPW + rw; it < kBcTokens; it += kBcWarps * RPW) {
+    const size_t bt_raw = tok0 + it;
+    const bool valid = bt_raw < ntok;
+    const size_t bt = valid ? bt_raw : ntok - 1;
+    const __nv_bfloat16* src = raw + bt * d.rs + (size_t)g * R * N + n0;
+    const __nv_bfloat16* go = dout + (bt * d.H + h) * N * R + (size_t)n0 * R;
+    uint4 q[R][2], gq[2 * R];
 #pragma unroll
-    for (int r = 0; r < R; ++r)
+    for (int r = 0; r < R; ++r) {
+      q[r][0] = __ldg(reinterpret_cast<const uint4*>(src + (size_t)r * N));
+      q[r][1] = __ldg(reinterpret_cast<const uint4*>(src + (size_t)r * N + 8));
+    }
 #pragma unroll
-      for (int j = 0; j < NJ; ++j) q[r][j] = __ldg(reinterpret_cast<const uint2*>(src + (size_t)r * d.N + 4 * lane + 128 * j));
-    float acc[R][NJ][4];
+    for (int k = 0; k < 2 * R; ++k) gq[k] = __ldg(reinterpret_cast<const uint4*>(go) + k);
+    float gy[16][R];  // (n0 + i, r), as stored
+    {
+      float* flat = &gy[0][0];
 #pragma unroll
-    for (int r = 0; r < R; ++r)
+      for (int k = 0; k < 2 * R; ++k) unpack8(gq[k], flat + 8 * k);
+    }
+    const float live = valid ? 1.0f : 0.0f;
 #pragma unroll
-      for (int j = 0; j < NJ; ++j)
+    for (int r = 0; r < R; ++r) {
+      float v[16], dxh[16];
+      unpack8(q[r][0], v);
+      unpack8(q[r][1], v + 8);
+      float ss = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[r][j][i] = 0.0f;
-    for (int hg = 0; hg < d.PG; ++hg) {
-      const int h = g * d.PG + hg;
-      const __nv_bfloat16* go = dout + (bt * d.H + h) * d.N * R;
-      float gy[NJ][4][R];  // (n0 + i, r), as stored
-#pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        const uint2* gp = reinterpret_cast<const uint2*>(go + (size_t)(4 * lane + 128 * j) * R);
-        float* flat = &gy[j][0][0];
-#pragma unroll
-        for (int k = 0; k < R; ++k) {
-          float t4[4];
-          unpack4(__ldg(gp + k), t4);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) flat[4 * k + i] = t4[i];
-        }
+      for (int i = 0; i < 16; ++i) {
+        v[i] += bs[i];
+        ss = fmaf(v[i], v[i], ss);
+        dxh[i] = gy[i][r] * gn[i];
       }
-      float bs[NJ][4];
+      float rstd = 1.0f, mean_dot = 0.0f;
+      if (d.has_norm) {
+        rstd = rsqrtf(row_sum<LPR>(ss) * (1.0f / N) + d.eps);
+        float dot = 0.0f;
 #pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        const float4 b4 = bias ? __ldg(reinterpret_cast<const float4*>(bias + (size_t)h * d.N + 4 * lane + 128 * j)) : make_float4(0.f, 0.f, 0.f, 0.f);
-        bs[j][0] = b4.x; bs[j][1] = b4.y; bs[j][2] = b4.z; bs[j][3] = b4.w;
+        for (int i = 0; i < 16; ++i) dot = fmaf(dxh[i], v[i], dot);
+        mean_dot = row_sum<LPR>(dot) * rstd * (1.0f / N);
       }
-      float dbias[NJ][4], dgain[NJ][4];
+      float dv[16];
 #pragma unroll
-      for (int j = 0; j < NJ; ++j)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) dbias[j][i] = dgain[j][i] = 0.0f;
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        float v[NJ][4], dxh[NJ][4];
-        float ss = 0.0f, dot = 0.0f;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-          unpack4(q[r][j], v[j]);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            v[j][i] += bs[j][i];
-            ss += v[j][i] * v[j][i];
-            dxh[j][i] = gy[j][i][r] * gn[j][i];
-          }
-        }
-        float rstd = 1.0f, mean_dot = 0.0f;
-        if (d.has_norm) {
-          rstd = rsqrtf(warp_sum(ss) / (float)d.N + d.eps);
-#pragma unroll
-          for (int j = 0; j < NJ; ++j)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) dot += dxh[j][i] * v[j][i] * rstd;
-          mean_dot = warp_sum(dot) / (float)d.N;
-        }
-#pragma unroll
-        for (int j = 0; j < NJ; ++j)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float xh = v[j][i] * rstd;
-            const float dv = d.has_norm ? rstd * (dxh[j][i] - xh * mean_dot) : dxh[j][i];
-            acc[r][j][i] += dv;
-            dbias[j][i] += dv;
-            dgain[j][i] += gy[j][i][r] * xh;
-          }
+      for (int i = 0; i < 16; ++i) {
+        const float xh = v[i] * rstd;
+        dv[i] = d.has_norm ? rstd * (dxh[i] - xh * mean_dot) : dxh[i];
+        pbias[i] = fmaf(live, dv[i], pbias[i]);
+        pgain[i] = fmaf(live * gy[i][r], xh, pgain[i]);
       }
-#pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        float4* pb = reinterpret_cast<float4*>(mine + (size_t)hg * d.N + 4 * lane + 128 * j);
-        float4 t = *pb;
-        t.x += dbias[j][0]; t.y += dbias[j][1]; t.z += dbias[j][2]; t.w += dbias[j][3];
-        *pb = t;
-        if (d.has_norm && gain) {
-          float4* pg = reinterpret_cast<float4*>(mine + (size_t)d.PG * d.N + 4 * lane + 128 * j);
-          float4 u = *pg;
-          u.x += dgain[j][0]; u.y += dgain[j][1]; u.z += dgain[j][2]; u.w += dgain[j][3];
-          *pg = u;
-        }
+      if (draw && valid) {
+        uint4* dr = reinterpret_cast<uint4*>(draw + bt * d.rs + (size_t)g * R * N + (size_t)r * N + n0);
+        dr[0] = make_uint4(pack2(dv[0], dv[1]), pack2(dv[2], dv[3]), pack2(dv[4], dv[5]), pack2(dv[6], dv[7]));
+        dr[1] = make_uint4(pack2(dv[8], dv[9]), pack2(dv[10], dv[11]), pack2(dv[12], dv[13]), pack2(dv[14], dv[15]));
       }
     }
-    if (draw) {
-      __nv_bfloat16* dr = draw + bt * d.rs + (size_t)g * R * d.N;
+  }
+  // rows of the warp (lanes LPR apart), then warps of the block
 #pragma unroll
-      for (int r = 0; r < R; ++r)
+  for (int i = 0; i < 16; ++i) {
 #pragma unroll
-        for (int j = 0; j < NJ; ++j)
-          *reinterpret_cast<uint2*>(dr + (size_t)r * d.N + 4 * lane + 128 * j) =
-              make_uint2(pack2(acc[r][j][0], acc[r][j][1]), pack2(acc[r][j][2], acc[r][j][3]));
+    for (int o = LPR; o < 32; o <<= 1) {
+      pbias[i] += __shfl_xor_sync(0xffffffffu, pbias[i], o);
+      pgain[i] += __shfl_xor_sync(0xffffffffu, pgain[i], o);
+    }
+  }
+  if (rw == 0) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      sm[warp][0][n0 + i] = pbias[i];
+      sm[warp][1][n0 + i] = pgain[i];
     }
   }
   __syncthreads();
   if (!part) return;
   const size_t blk = (size_t)blockIdx.x * gridDim.y + g;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+  for (int i = threadIdx.x; i < 2 * N; i += blockDim.x) {
     float s = 0.0f;
-    for (int w = 0; w < kBcWarps; ++w) s += sm[(size_t)w * width + i];
-    part[blk * width + i] = s;
+#pragma unroll
+    for (int w = 0; w < kBcWarps; ++w) s += sm[w][i / N][i % N];
+    part[blk * 2 * N + i] = s;   // width = (PG + 1) * N with PG == 1
   }
 }
 
 // ---- dt / lambda ---------------------------------------------------------------------------------------
 __device__ __forceinline__ float softplus(float v) { return v > 20.0f ? v : log1pf(__expf(v)); }
-__device__ __forceinline__ float sigmoid(float v) { return 1.0f / (1.0f + __expf(-v)); }
+__device__ __forceinline__ float sigmoid(float v) { return __fdividef(1.0f, 1.0f + __expf(-v)); }
 
 template <class T>
 __global__ void k_act_fwd(int ntok, int H, long long stride, const T* __restrict__ dt_raw, const T* __restrict__ lam_raw,
@@ -373,7 +354,7 @@ __global__ void k_act_fwd(int ntok, int H, long long stride, const T* __restrict
   }
 }
 
-constexpr int kActRun = 32;  // tokens per thread of the backward pass
+constexpr int kActRun = 8;  // tokens per thread of the backward pass
 // Thread (run, head): walks kActRun tokens of one head and leaves that run's partial sum of the bias
 // gradient; the runs are added by column_sums.
 template <class T>
@@ -499,8 +480,8 @@ int m3_bc_forward(m3_ctx* ctx, const m3_bc_desc* s, void* b, void* c) {
   M3_CUDA(ctx, cudaSetDevice(ctx->device));
   const size_t rows = (size_t)d.B * d.T * d.H;
   const unsigned grid = (unsigned)((rows + kBcWarps - 1) / kBcWarps);
-  const bool aligned = !(d.rs % 4) && !(reinterpret_cast<uintptr_t>(s->b_raw) % 8) && !(reinterpret_cast<uintptr_t>(s->c_raw) % 8) &&
-                       !(reinterpret_cast<uintptr_t>(b) % 8) && !(reinterpret_cast<uintptr_t>(c) % 8) &&
+  const bool aligned = !(d.rs % 8) && !(reinterpret_cast<uintptr_t>(s->b_raw) % 16) && !(reinterpret_cast<uintptr_t>(s->c_raw) % 16) &&
+                       !(reinterpret_cast<uintptr_t>(b) % 16) && !(reinterpret_cast<uintptr_t>(c) % 16) &&
                        !(reinterpret_cast<uintptr_t>(s->b_bias) % 16) && !(reinterpret_cast<uintptr_t>(s->c_bias) % 16) &&
                        !(reinterpret_cast<uintptr_t>(s->norm_weight) % 16);
   if (s->dtype == M3_BF16 && aligned && (d.N == 128 || d.N == 256) && (d.R == 1 || d.R == 2 || d.R == 4)) {
@@ -509,11 +490,13 @@ int m3_bc_forward(m3_ctx* ctx, const m3_bc_desc* s, void* b, void* c) {
       const T* raw = static_cast<const T*>(which ? s->c_raw : s->b_raw);
       const float* bias = which ? s->c_bias : s->b_bias;
       T* out = static_cast<T*>(which ? c : b);
-#define M3_BC_FWD(RR, NJ) k_bc_fwd_vec<RR, NJ><<<grid, kBcWarps * 32, 0, ctx->stream>>>(d, raw, bias, s->norm_weight, out)
+#define M3_BC_FWD(RR, NN)                                                                       \
+  k_bc_fwd_vec<RR, NN><<<(unsigned)((rows + kBcWarps * (512 / NN) - 1) / (kBcWarps * (512 / NN))), \
+                         kBcWarps * 32, 0, ctx->stream>>>(d, raw, bias, s->norm_weight, out)
       if (d.N == 128) {
-        if (d.R == 1) M3_BC_FWD(1, 1); else if (d.R == 2) M3_BC_FWD(2, 1); else M3_BC_FWD(4, 1);
+        if (d.R == 1) M3_BC_FWD(1, 128); else if (d.R == 2) M3_BC_FWD(2, 128); else M3_BC_FWD(4, 128);
       } else {
-        if (d.R == 1) M3_BC_FWD(1, 2); else if (d.R == 2) M3_BC_FWD(2, 2); else M3_BC_FWD(4, 2);
+        if (d.R == 1) M3_BC_FWD(1, 256); else if (d.R == 2) M3_BC_FWD(2, 256); else M3_BC_FWD(4, 256);
       }
 #undef M3_BC_FWD
     }
@@ -558,18 +541,18 @@ int m3_bc_backward(m3_ctx* ctx, const m3_bc_desc* s, const void* db, const void*
     const void* go = which ? dc : db;
     void* draw = which ? dc_raw : db_raw;
     float* dbias = bias ? (which ? dc_bias : db_bias) : nullptr;
-    const bool aligned = !(d.rs % 4) && !(reinterpret_cast<uintptr_t>(raw) % 8) && !(reinterpret_cast<uintptr_t>(go) % 8) &&
-                         !(reinterpret_cast<uintptr_t>(draw) % 8) && !(reinterpret_cast<uintptr_t>(bias) % 16) &&
+    const bool aligned = !(d.rs % 8) && !(reinterpret_cast<uintptr_t>(raw) % 16) && !(reinterpret_cast<uintptr_t>(go) % 16) &&
+                         !(reinterpret_cast<uintptr_t>(draw) % 16) && !(reinterpret_cast<uintptr_t>(bias) % 16) &&
                          !(reinterpret_cast<uintptr_t>(s->norm_weight) % 16);
-    if (s->dtype == M3_BF16 && aligned && smem <= 48 * 1024 && (d.N == 128 || d.N == 256) && (d.R == 1 || d.R == 2 || d.R == 4)) {
+    if (s->dtype == M3_BF16 && aligned && d.PG == 1 && (d.N == 128 || d.N == 256) && (d.R == 1 || d.R == 2 || d.R == 4)) {
       using T = __nv_bfloat16;
-#define M3_BC_BWD(RR, NJ)                                                                                            \
-  k_bc_bwd_vec<RR, NJ><<<grid, kBcWarps * 32, smem, ctx->stream>>>(d, static_cast<const T*>(raw), bias, s->norm_weight, \
-                                                                   static_cast<const T*>(go), static_cast<T*>(draw), part)
+#define M3_BC_BWD(RR, NN)                                                                                       \
+  k_bc_bwd_vec<RR, NN><<<grid, kBcWarps * 32, 0, ctx->stream>>>(d, static_cast<const T*>(raw), bias, s->norm_weight, \
+                                                                static_cast<const T*>(go), static_cast<T*>(draw), part)
       if (d.N == 128) {
-        if (d.R == 1) M3_BC_BWD(1, 1); else if (d.R == 2) M3_BC_BWD(2, 1); else M3_BC_BWD(4, 1);
+        if (d.R == 1) M3_BC_BWD(1, 128); else if (d.R == 2) M3_BC_BWD(2, 128); else M3_BC_BWD(4, 128);
       } else {
-        if (d.R == 1) M3_BC_BWD(1, 2); else if (d.R == 2) M3_BC_BWD(2, 2); else M3_BC_BWD(4, 2);
+        if (d.R == 1) M3_BC_BWD(1, 256); else if (d.R == 2) M3_BC_BWD(2, 256); else M3_BC_BWD(4, 256);
       }
 #undef M3_BC_BWD
     } else if (s->dtype == M3_BF16) {
