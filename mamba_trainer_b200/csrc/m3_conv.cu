@@ -24,7 +24,8 @@
 namespace {
 
 constexpr int kMaxTaps = 8;
-constexpr int kRun = 8;      // time steps per thread
+constexpr int kRunFwd = 4;   // time steps per thread, forward
+constexpr int kRunBwd = 8;   // and backward (its look-ahead recomputes K-1 steps per run)
 constexpr int kLanesT = 8;   // threads of a block along time
 constexpr int kLanesC = 32;  // threads of a block along channel vectors
 
@@ -142,7 +143,7 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
                const float* __restrict__ bias, T* __restrict__ y, T* __restrict__ y2) {
   const int c0 = (blockIdx.x * kLanesC + threadIdx.x) * V;
   const int b = blockIdx.z;
-  const int t0 = (blockIdx.y * kLanesT + threadIdx.y) * kRun;
+  const int t0 = (blockIdx.y * kLanesT + threadIdx.y) * kRunFwd;
   if (c0 >= d.C || t0 >= d.T) return;
   long long ys;
   T* yb = out_band<T>(d, y, y2, c0, &ys);
@@ -155,14 +156,14 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
 #pragma unroll
   for (int i = 0; i < V; ++i) bs[i] = bias ? bias[c0 + i] : 0.0f;
   // Every row this thread needs is requested before the first one is used.
-  typename Vec<T, V>::raw_t raw[kRun + KT - 1];  // raw[j] = x[t0 - (KT-1) + j]
+  typename Vec<T, V>::raw_t raw[kRunFwd + KT - 1];  // raw[j] = x[t0 - (KT-1) + j]
 #pragma unroll
-  for (int j = 0; j < kRun + KT - 1; ++j) raw[j] = load_x<T, V>(d, x, hist, b, t0 - (KT - 1) + j, c0);
+  for (int j = 0; j < kRunFwd + KT - 1; ++j) raw[j] = load_x<T, V>(d, x, hist, b, t0 - (KT - 1) + j, c0);
 #pragma unroll
   for (int k = 0; k < KT - 1; ++k) Vec<T, V>::unpack(raw[k], win[k + 1]);
-  const int t1 = min(t0 + kRun, d.T);
+  const int t1 = min(t0 + kRunFwd, d.T);
 #pragma unroll
-  for (int it = 0; it < kRun; ++it) {
+  for (int it = 0; it < kRunFwd; ++it) {
     const int t = t0 + it;
 #pragma unroll
     for (int k = 0; k < KT - 1; ++k)
@@ -208,7 +209,7 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
   __shared__ float red[kLanesT][V][kLanesC + 1];  // [time lane][element of the vector][channel lane]: conflict-free
   const int c0 = (blockIdx.x * kLanesC + threadIdx.x) * V;
   const int b = blockIdx.z;
-  const int t0 = (blockIdx.y * kLanesT + threadIdx.y) * kRun;
+  const int t0 = (blockIdx.y * kLanesT + threadIdx.y) * kRunBwd;
   const bool active = c0 < d.C && t0 < d.T;
   const int pad = KT - d.K;
   float pw[KT][V], pb[V];
@@ -233,19 +234,19 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
     // look-ahead of dx) is requested before the first one is used.
     long long ys;
     const T* gb = out_band<const T>(d, dy, dy2, c0, &ys);
-    typename Vec<T, V>::raw_t rx[kRun + 2 * (KT - 1)], rg[kRun + KT - 1];  // rx[j] = x[t0-(KT-1)+j], rg[j] = dy[t0+j]
+    typename Vec<T, V>::raw_t rx[kRunBwd + 2 * (KT - 1)], rg[kRunBwd + KT - 1];  // rx[j] = x[t0-(KT-1)+j], rg[j] = dy[t0+j]
 #pragma unroll
-    for (int j = 0; j < kRun + 2 * (KT - 1); ++j) rx[j] = load_x<T, V>(d, x, hist, b, t0 - (KT - 1) + j, c0);
+    for (int j = 0; j < kRunBwd + 2 * (KT - 1); ++j) rx[j] = load_x<T, V>(d, x, hist, b, t0 - (KT - 1) + j, c0);
 #pragma unroll
-    for (int j = 0; j < kRun + KT - 1; ++j)
+    for (int j = 0; j < kRunBwd + KT - 1; ++j)
       rg[j] = (t0 + j < d.T) ? Vec<T, V>::load_raw(gb + ((size_t)b * d.T + t0 + j) * ys) : Vec<T, V>::zero_raw();
 #pragma unroll
     for (int k = 0; k < KT - 1; ++k) Vec<T, V>::unpack(rx[k], win[k + 1]);
-    const int t1 = min(t0 + kRun, d.T);
+    const int t1 = min(t0 + kRunBwd, d.T);
     // s walks the run plus KT-1 steps of look-ahead; dx[s-(KT-1)] is complete once g[s] is known.
     const int emit_from = (t0 == 0 && dhist) ? -(d.K - 1) : t0;
 #pragma unroll
-    for (int it = 0; it < kRun + KT - 1; ++it) {
+    for (int it = 0; it < kRunBwd + KT - 1; ++it) {
       const int s = t0 + it;
 #pragma unroll
       for (int k = 0; k < KT - 1; ++k)
@@ -349,7 +350,7 @@ template <class T, int V>
 cudaError_t fwd_launch(cudaStream_t st, const ConvDims& d, const m3_conv_desc& c, void* y) {
   T* y2 = static_cast<T*>(c.y2);
   const dim3 block(kLanesC, kLanesT);
-  const dim3 grid((d.C / V + kLanesC - 1) / kLanesC, (d.T + kLanesT * kRun - 1) / (kLanesT * kRun), d.B);
+  const dim3 grid((d.C / V + kLanesC - 1) / kLanesC, (d.T + kLanesT * kRunFwd - 1) / (kLanesT * kRunFwd), d.B);
   const T* x = static_cast<const T*>(c.x);
   const T* h = static_cast<const T*>(c.history);
   if (d.K <= 2) k_conv_fwd<T, V, 2><<<grid, block, 0, st>>>(d, x, h, c.weight, c.bias, static_cast<T*>(y), y2);
@@ -362,7 +363,7 @@ template <class T, int V>
 cudaError_t bwd_launch(cudaStream_t st, const ConvDims& d, const m3_conv_desc& c, const void* dy, void* dx, void* dhist,
                        float* part, dim3* grid_out) {
   const dim3 block(kLanesC, kLanesT);
-  const dim3 grid((d.C / V + kLanesC - 1) / kLanesC, (d.T + kLanesT * kRun - 1) / (kLanesT * kRun), d.B);
+  const dim3 grid((d.C / V + kLanesC - 1) / kLanesC, (d.T + kLanesT * kRunBwd - 1) / (kLanesT * kRunBwd), d.B);
   *grid_out = grid;
   const T* x = static_cast<const T*>(c.x);
   const T* h = static_cast<const T*>(c.history);
@@ -392,7 +393,7 @@ int m3_conv_forward(m3_ctx* ctx, const m3_conv_desc* c, void* y, void* new_histo
   cudaError_t e = cudaSuccess;
   if (d.T > 0) {
     if (c->dtype == M3_BF16) {
-      e = vector_ok(d, 8, 2, {c->x, c->history, y, c->y2}) ? fwd_launch<__nv_bfloat16, 8>(ctx->stream, d, *c, y)
+      e = vector_ok(d, 4, 2, {c->x, c->history, y, c->y2}) ? fwd_launch<__nv_bfloat16, 4>(ctx->stream, d, *c, y)
                                                      : fwd_launch<__nv_bfloat16, 1>(ctx->stream, d, *c, y);
     } else {
       e = vector_ok(d, 4, 4, {c->x, c->history, y, c->y2}) ? fwd_launch<float, 4>(ctx->stream, d, *c, y)
@@ -434,7 +435,7 @@ int m3_conv_backward(m3_ctx* ctx, const m3_conv_desc* c, const void* dy, void* d
     if (dhistory) M3_CUDA(ctx, cudaMemsetAsync(dhistory, 0, (size_t)d.B * (d.K - 1) * d.C * (c->dtype == M3_BF16 ? 2 : 4), ctx->stream));
     return M3_OK;
   }
-  const int nblk = d.B * ((d.T + kLanesT * kRun - 1) / (kLanesT * kRun));
+  const int nblk = d.B * ((d.T + kLanesT * kRunBwd - 1) / (kLanesT * kRunBwd));
   float* part = nullptr;
   if (want_par)
     M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&part), (size_t)nblk * (d.K + 1) * d.C * sizeof(float), ctx->stream));
