@@ -21,7 +21,7 @@ import torch
 from .. import _ffi
 from ..error import ConfigError, ShapeError, UnsupportedError
 from ..ssm.config import Discretization
-from ..ssm.scan import Context, _DTYPES, _Saved
+from ..ssm.scan import Context, ScanInputs, SsmState, _DTYPES, _Saved, mamba3_scan, mamba3_step
 
 
 def _p(t: Optional[torch.Tensor], offset: int = 0):
@@ -67,6 +67,14 @@ class MixerShape:
     @property
     def in_proj_width(self) -> int:
         return 2 * self.d_inner + 2 * self.bc_width + self.heads + self.lambda_width + self.theta_width
+
+
+@dataclass
+class MixerCache:
+    """What a layer carries from one window to the next (MixerCache, src/models/mamba3.rs:62-80): the
+    convolution's last K-1 inputs and the scan's state."""
+    conv: torch.Tensor      # [batch, K-1, conv_channels]
+    ssm: SsmState
 
 
 class _MixerCore(torch.autograd.Function):
@@ -213,6 +221,74 @@ class MixerCore(torch.nn.Module):
         self.b_bias = par(torch.zeros(H, N)) if bc_bias else None
         self.c_bias = par(torch.zeros(H, N)) if bc_bias else None
         self.norm_w = par(torch.ones(N)) if (bc_norm and norm_gain) else None
+
+    def empty_cache(self, batch: int, device, dtype=torch.float32) -> MixerCache:
+        s = self.shape
+        return MixerCache(torch.zeros((batch, self.conv_w.shape[0] - 1, s.conv_channels), device=device, dtype=dtype),
+                          SsmState.zeros(batch, s.heads, s.head_dim, s.d_state, s.rotational, device))
+
+    @torch.no_grad()
+    def forward_cached(self, proj: torch.Tensor, cache: Optional[MixerCache] = None):
+        """Inference with a carried state (Mamba3Mixer::apply_with_state, src/models/mamba3.rs:486-560):
+        a prefill window or a single decoding step.  Returns (gated output, new MixerCache).  A window
+        of one position runs the decode kernel (mamba3_step), longer ones the scan."""
+        s = self.shape
+        if proj.dim() != 3 or proj.shape[2] != s.in_proj_width:
+            raise ShapeError(f"expected [batch, seq, {s.in_proj_width}], got {tuple(proj.shape)}")
+        if self.bidirectional:
+            raise UnsupportedError("a bidirectional mixer has no causal state to carry")   # mamba3.rs:494-499
+        proj = proj.contiguous()
+        ctx = Context.for_device(proj.device)
+        lib, hd = ctx.lib, ctx.handle
+        B, T, W = proj.shape
+        el, code, dev = proj.dtype, _DTYPES[proj.dtype], proj.device
+        H, P, N, R, G = s.heads, s.head_dim, s.d_state, s.rank, s.n_groups
+        di, bc = s.d_inner, s.bc_width
+        off_dt = 2 * di + 2 * bc
+        off_lam, off_th = off_dt + H, off_dt + H + s.lambda_width
+        if cache is None:
+            cache = self.empty_cache(B, dev, el)
+        f = lambda t: None if t is None else t.detach().to(torch.float32).contiguous()
+        conv_w, conv_b, dt_bias = f(self.conv_w), f(self.conv_b), f(self.dt_bias)
+        b_bias, c_bias, norm_w = f(self.b_bias), f(self.c_bias), f(self.norm_w)
+        new = lambda *shape: torch.empty(shape, device=dev, dtype=el)
+        K = conv_w.shape[0]
+        hist = cache.conv.to(el).contiguous()
+        x, bcr, new_hist = new(B, T, H, P, R), new(B, T, 2 * bc), new(B, K - 1, di + 2 * bc)
+        cdesc = _ffi.ConvDesc(batch=B, seq=T, channels=di + 2 * bc, kernel_size=K, dtype=code, activation=1,
+                              x_stride=W, y_stride=di, x=_p(proj, di), history=_p(hist), weight=_p(conv_w),
+                              bias=_p(conv_b), split=di, y2_stride=2 * bc, y2=_p(bcr), dy2=None)
+        ctx.check(lib.m3_conv_forward(hd, C.byref(cdesc), _p(x), _p(new_hist)))
+        b, c = new(B, T, H, N, R), new(B, T, H, N, R)
+        bdesc = _ffi.BcDesc(batch=B, seq=T, heads=H, groups=G, d_state=N, rank=R, dtype=code,
+                            has_norm=1 if self.use_norm else 0, eps=float(self.eps), raw_stride=2 * bc,
+                            b_raw=_p(bcr), c_raw=_p(bcr, bc), b_bias=_p(b_bias), c_bias=_p(c_bias), norm_weight=_p(norm_w))
+        ctx.check(lib.m3_bc_forward(hd, C.byref(bdesc), _p(b), _p(c)))
+        dt = new(B, T, H)
+        lam = new(B, T, H) if s.learned_lambda else None
+        adesc = _ffi.ActDesc(batch=B, seq=T, heads=H, dtype=code, stride=W, dt_raw=_p(proj, off_dt),
+                             lambda_raw=_p(proj, off_lam) if s.learned_lambda else None, dt_bias=_p(dt_bias))
+        ctx.check(lib.m3_dt_lambda_forward(hd, C.byref(adesc), _p(dt), _p(lam)))
+        theta = proj[..., off_th:off_th + s.theta_width].reshape(B, T, H, N // 2).contiguous() if s.rotational else None
+        if T == 1:
+            y, ssm = mamba3_step(x[:, 0], b[:, 0], c[:, 0], dt[:, 0], lam[:, 0] if lam is not None else None,
+                                 self.a_log, theta[:, 0] if theta is not None else None, self.d_skip, cache.ssm,
+                                 self.disc)
+            y = y.unsqueeze(1)
+        else:
+            inp = ScanInputs.new(x, b, c, dt, self.a_log.detach(), lam).with_chunk_size(self.chunk)
+            inp = inp.with_discretization(self.disc).with_state(cache.ssm).with_state_output(True)
+            if theta is not None:
+                inp = inp.with_theta(theta)
+            if self.d_skip is not None:
+                inp = inp.with_skip(self.d_skip.detach())
+            res = mamba3_scan(inp)
+            y, ssm = res.y, res.state
+        y = y.contiguous()
+        out = new(B, T, di)
+        gdesc = _ffi.GateDesc(batch=B, seq=T, channels=di, dtype=code, z_stride=W, y=_p(y), z=_p(proj))
+        ctx.check(lib.m3_gate_forward(hd, C.byref(gdesc), _p(out)))
+        return out, MixerCache(new_hist, ssm)
 
     def forward(self, proj: torch.Tensor, path: int = _ffi.PATH_AUTO) -> torch.Tensor:
         """proj: the input projection's output [batch, seq, in_proj_width]; returns the gated scan

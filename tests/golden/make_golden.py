@@ -3,7 +3,7 @@
 Run in a container that has the reference checked out (it is not needed to run the
 tests):
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the mamba-trainer checkout>
 
 It imports the reference's PyTorch port of the scan path (bench/torch_mamba3.py:
 `ssd_chunked` :47-129, `rotate_halves` :132-137, `LOG_DECAY_FLOOR` :25) by file
@@ -151,7 +151,9 @@ def mixer_core_case(ref):
 
 
 def main():
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to the mamba-trainer checkout>")
+    root = Path(sys.argv[1])
     ref = load_reference(root)
     assert ref.LOG_DECAY_FLOOR == -60.0
     ssd_case(ref, "ssd_chunked_even", (2, 12, 3, 4, 6), 4)

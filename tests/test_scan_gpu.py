@@ -663,3 +663,33 @@ def test_mixer_core_bf16_matches_the_oracle(rank, groups, rot, learned, norm_gai
             assert norm_rel(a_.float(), e_) <= 5e-2, f"d{n}: {norm_rel(a_.float(), e_):.3e}"
         else:
             check_bf16("d" + n, a_, e_)
+
+
+@pytest.mark.parametrize("rank,dtype", [(1, torch.float32), (2, torch.float32), (1, torch.bfloat16)])
+def test_mixer_core_decode_matches_the_parallel_pass(rank, dtype):
+    """tests/model.rs:141-200 (decode == parallel, < 2e-3): one pass over the whole sequence against a
+    prefill window followed by single-position steps, each continuing from the carried cache."""
+    from mamba_trainer_b200.nn import MixerCore, MixerShape
+    small = dtype == torch.float32
+    H, P, N = (2, 4, 6) if small else (2, 64, 128)
+    B, T, split = 2, 19, 12
+    shape = MixerShape(H, P, N, rank)
+    torch.manual_seed(rank)
+    core = MixerCore(shape, chunk=8, device="cuda")
+    with torch.no_grad():
+        core.b_bias.normal_(0, 0.3); core.c_bias.normal_(0, 0.3); core.conv_b.normal_(0, 0.2); core.d_skip.normal_()
+    proj = torch.randn(B, T, shape.in_proj_width, device="cuda").to(dtype)
+    with torch.no_grad():
+        whole = core(proj)
+    out1, cache = core.forward_cached(proj[:, :split])
+    outs = [out1]
+    for t in range(split, T):
+        o, cache = core.forward_cached(proj[:, t:t + 1], cache)
+        outs.append(o)
+    got = torch.cat(outs, 1)
+    tol = 2e-3 if small else 3e-2
+    assert ref_metric(got.float(), whole.float()) <= tol, ref_metric(got.float(), whole.float())
+    # and two windows of several positions each
+    o1, ca = core.forward_cached(proj[:, :7])
+    o2, _ = core.forward_cached(proj[:, 7:], ca)
+    assert ref_metric(torch.cat([o1, o2], 1).float(), whole.float()) <= tol
