@@ -269,6 +269,13 @@ typedef struct {
   int64_t y2_stride;
   void *y2;
   const void *dy2;
+  /* Channel ranges [lo, hi) that are convolved right to left: the backward direction of a
+   * bidirectional mixer, whose x, B and C halves the reference reverses in time before the
+   * convolution (src/models/mamba3.rs:352-370).  Inputs, outputs and gradients stay in ordinary
+   * time; such channels take no history.  n_reversed = 0: none. */
+  int32_t n_reversed;
+  int32_t reversed_lo[4], reversed_hi[4];
+  int32_t reserved1;
 } m3_conv_desc;
 /* new_history (causal_conv1d_history): [batch, K-1, channels], the inputs the next window
  * continues from; NULL skips it. */

@@ -59,7 +59,8 @@ class StepOut(C.Structure):
 class ConvDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("batch", "seq", "channels", "kernel_size", "dtype", "activation")] + [
         ("x_stride", C.c_int64), ("y_stride", C.c_int64)] + [(n, C.c_void_p) for n in ("x", "history", "weight", "bias")] + [
-        ("split", C.c_int32), ("reserved0", C.c_int32), ("y2_stride", C.c_int64), ("y2", C.c_void_p), ("dy2", C.c_void_p)]
+        ("split", C.c_int32), ("reserved0", C.c_int32), ("y2_stride", C.c_int64), ("y2", C.c_void_p), ("dy2", C.c_void_p),
+        ("n_reversed", C.c_int32), ("reversed_lo", C.c_int32 * 4), ("reversed_hi", C.c_int32 * 4), ("reserved1", C.c_int32)]
 
 
 class BcDesc(C.Structure):

@@ -103,7 +103,19 @@ struct ConvDims {
   int act;
   int split;         // channels >= split live in a second output tensor (0: none)
   long long y2s;     // its row stride
+  int nrev;          // channel ranges convolved right to left (the backward direction of a
+  int rev_lo[4];     // bidirectional mixer): position s of such a channel is time T-1-s
+  int rev_hi[4];
 };
+
+__device__ __forceinline__ bool walks_backwards(const ConvDims& d, int c0) {
+  bool r = false;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) r = r || (i < d.nrev && c0 >= d.rev_lo[i] && c0 < d.rev_hi[i]);
+  return r;
+}
+// Time of position s for a channel of the given direction.
+__device__ __forceinline__ int at_time(const ConvDims& d, bool rev, int s) { return rev ? d.T - 1 - s : s; }
 
 // Where channel vector c0 of the output (or of its gradient) lives: the first tensor, or the
 // second one for channels at and beyond the split.
@@ -128,8 +140,8 @@ __device__ __forceinline__ float silu_grad(float v) {
 // x of (b, t, channel vector c0): the sequence, the carried history for t < 0, or zero.
 template <class T, int V>
 __device__ __forceinline__ typename Vec<T, V>::raw_t load_x(const ConvDims& d, const T* x, const T* hist, int b, int t,
-                                                            int c0) {
-  if (t >= 0 && t < d.T) return Vec<T, V>::load_raw(x + ((size_t)b * d.T + t) * d.xs + c0);
+                                                            int c0, bool rev = false) {
+  if (t >= 0 && t < d.T) return Vec<T, V>::load_raw(x + ((size_t)b * d.T + at_time(d, rev, t)) * d.xs + c0);
   if (t < 0 && hist && t + (d.K - 1) >= 0)
     return Vec<T, V>::load_raw(hist + ((size_t)b * (d.K - 1) + (t + d.K - 1)) * d.C + c0);
   return Vec<T, V>::zero_raw();
@@ -147,6 +159,7 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
   if (c0 >= d.C || t0 >= d.T) return;
   long long ys;
   T* yb = out_band<T>(d, y, y2, c0, &ys);
+  const bool rev = walks_backwards(d, c0);
   const int pad = KT - d.K;
   float wt[KT][V], bs[V], win[KT][V];  // win[k] pairs with tap k: x[t - (KT-1-k)]
 #pragma unroll
@@ -158,7 +171,7 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
   // Every row this thread needs is requested before the first one is used.
   typename Vec<T, V>::raw_t raw[kRunFwd + KT - 1];  // raw[j] = x[t0 - (KT-1) + j]
 #pragma unroll
-  for (int j = 0; j < kRunFwd + KT - 1; ++j) raw[j] = load_x<T, V>(d, x, hist, b, t0 - (KT - 1) + j, c0);
+  for (int j = 0; j < kRunFwd + KT - 1; ++j) raw[j] = load_x<T, V>(d, x, hist, b, t0 - (KT - 1) + j, c0, rev);
 #pragma unroll
   for (int k = 0; k < KT - 1; ++k) Vec<T, V>::unpack(raw[k], win[k + 1]);
   const int t1 = min(t0 + kRunFwd, d.T);
@@ -181,7 +194,7 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
 #pragma unroll
       for (int i = 0; i < V; ++i) acc[i] = silu(acc[i]);
     }
-    if (t < t1) Vec<T, V>::store(yb + ((size_t)b * d.T + t) * ys, acc);
+    if (t < t1) Vec<T, V>::store(yb + ((size_t)b * d.T + at_time(d, rev, t)) * ys, acc);
   }
 }
 
@@ -234,12 +247,13 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
     // look-ahead of dx) is requested before the first one is used.
     long long ys;
     const T* gb = out_band<const T>(d, dy, dy2, c0, &ys);
+    const bool rev = walks_backwards(d, c0);
     typename Vec<T, V>::raw_t rx[kRunBwd + 2 * (KT - 1)], rg[kRunBwd + KT - 1];  // rx[j] = x[t0-(KT-1)+j], rg[j] = dy[t0+j]
 #pragma unroll
-    for (int j = 0; j < kRunBwd + 2 * (KT - 1); ++j) rx[j] = load_x<T, V>(d, x, hist, b, t0 - (KT - 1) + j, c0);
+    for (int j = 0; j < kRunBwd + 2 * (KT - 1); ++j) rx[j] = load_x<T, V>(d, x, hist, b, t0 - (KT - 1) + j, c0, rev);
 #pragma unroll
     for (int j = 0; j < kRunBwd + KT - 1; ++j)
-      rg[j] = (t0 + j < d.T) ? Vec<T, V>::load_raw(gb + ((size_t)b * d.T + t0 + j) * ys) : Vec<T, V>::zero_raw();
+      rg[j] = (t0 + j < d.T) ? Vec<T, V>::load_raw(gb + ((size_t)b * d.T + at_time(d, rev, t0 + j)) * ys) : Vec<T, V>::zero_raw();
 #pragma unroll
     for (int k = 0; k < KT - 1; ++k) Vec<T, V>::unpack(rx[k], win[k + 1]);
     const int t1 = min(t0 + kRunBwd, d.T);
@@ -286,7 +300,7 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
 #pragma unroll
           for (int i = 0; i < V; ++i) o[i] = fmaf(wt[KT - 1 - j][i], gw[j][i], o[i]);
         if (te >= 0) {
-          if (dx) Vec<T, V>::store(dx + ((size_t)b * d.T + te) * d.xs + c0, o);
+          if (dx) Vec<T, V>::store(dx + ((size_t)b * d.T + at_time(d, rev, te)) * d.xs + c0, o);
         } else {
           Vec<T, V>::store(dhist + ((size_t)b * (d.K - 1) + (te + d.K - 1)) * d.C + c0, o);
         }
@@ -329,6 +343,15 @@ int check(m3_ctx* ctx, const m3_conv_desc* c, ConvDims* d) {
   if (d->xs < c->channels || d->ys < (c->split > 0 ? c->split : c->channels))
     return m3::fail(ctx, M3_ERR_SHAPE, "row strides below the channel count");
   d->act = c->activation ? 1 : 0;
+  d->nrev = c->n_reversed;
+  if (c->n_reversed < 0 || c->n_reversed > 4) return m3::fail(ctx, M3_ERR_UNSUPPORTED, "at most 4 reversed channel ranges");
+  for (int i = 0; i < 4; ++i) {
+    d->rev_lo[i] = i < c->n_reversed ? c->reversed_lo[i] : 0;
+    d->rev_hi[i] = i < c->n_reversed ? c->reversed_hi[i] : 0;
+    if (i < c->n_reversed && (d->rev_lo[i] < 0 || d->rev_hi[i] > c->channels || d->rev_lo[i] > d->rev_hi[i]))
+      return m3::fail(ctx, M3_ERR_SHAPE, "reversed channel range %d outside [0, channels]", i);
+  }
+  if (c->n_reversed > 0 && c->history) return m3::fail(ctx, M3_ERR_CONFIG, "a right-to-left channel has no history to continue from");
   d->split = c->split;
   d->y2s = 0;
   if (c->split < 0 || c->split >= c->channels) return m3::fail(ctx, M3_ERR_SHAPE, "split %d outside [0, channels)", c->split);
@@ -341,6 +364,8 @@ int check(m3_ctx* ctx, const m3_conv_desc* c, ConvDims* d) {
 
 bool vector_ok(const ConvDims& d, int V, int es, std::initializer_list<const void*> ptrs) {
   if (d.C % V || d.xs % V || d.ys % V || d.split % V || d.y2s % V) return false;
+  for (int i = 0; i < d.nrev; ++i)
+    if (d.rev_lo[i] % V || d.rev_hi[i] % V) return false;  // a vector must not straddle a direction change
   for (const void* p : ptrs)
     if (p && (reinterpret_cast<uintptr_t>(p) % (size_t)(V * es))) return false;
   return true;
@@ -389,6 +414,7 @@ int m3_conv_forward(m3_ctx* ctx, const m3_conv_desc* c, void* y, void* new_histo
   if (rc != M3_OK) return rc;
   if (!y) return m3::fail(ctx, M3_ERR_NULL, "y is required");
   if (c->split > 0 && !c->y2) return m3::fail(ctx, M3_ERR_NULL, "split needs y2");
+  if (c->n_reversed > 0 && new_history) return m3::fail(ctx, M3_ERR_CONFIG, "a right-to-left channel carries no history");
   M3_CUDA(ctx, cudaSetDevice(ctx->device));
   cudaError_t e = cudaSuccess;
   if (d.T > 0) {

@@ -97,6 +97,12 @@ class _MixerCore(torch.autograd.Function):
         cdesc = _ffi.ConvDesc(batch=B, seq=T, channels=di + 2 * bc, kernel_size=K, dtype=dt_code, activation=1,
                               x_stride=W, y_stride=di, x=_p(proj, off_x), history=None, weight=_p(conv_w),
                               bias=_p(conv_b), split=di, y2_stride=2 * bc, y2=_p(bcr), dy2=None)
+        if o["reverse_heads"]:
+            # direction-major bands (mamba3.rs:352-370): the second half of x, of B and of C belongs to
+            # the heads that walk right to left; their convolution runs right to left as well
+            cdesc.n_reversed = 3
+            for i, (lo, hi) in enumerate(((di // 2, di), (di + bc // 2, di + bc), (di + bc + bc // 2, di + 2 * bc))):
+                cdesc.reversed_lo[i], cdesc.reversed_hi[i] = lo, hi
         ctx.check(lib.m3_conv_forward(hd, C.byref(cdesc), _p(x), None))
         # 2. B / C: groups -> heads, bias, RMS norm, rank last
         b, c = new(B, T, H, N, R), new(B, T, H, N, R)
@@ -298,11 +304,11 @@ class MixerCore(torch.nn.Module):
             raise ShapeError(f"expected [batch, seq, {s.in_proj_width}], got {tuple(proj.shape)}")
         if proj.dtype not in _DTYPES:
             raise UnsupportedError(f"element type {proj.dtype}: float32 and bfloat16 are served")
-        if self.bidirectional:
-            raise UnsupportedError("the bidirectional cut of the projection (direction-major bands) is served by "
-                                   "the scan's reverse_heads; the convolution over reversed bands is not built")
+        # Bidirectional (mamba3.rs:97-112): every piece of the projection is direction-major; the second
+        # half of the heads walks right to left inside the convolution and the scan, and nothing is
+        # reversed in memory.
         o = {"shape": s, "chunk": self.chunk, "eps": self.eps, "norm": self.use_norm, "disc": int(self.disc),
-             "path": path, "reverse_heads": 0}
+             "path": path, "reverse_heads": s.heads // 2 if self.bidirectional else 0}
         f = lambda t: None if t is None else t.to(torch.float32).contiguous()
         return _MixerCore.apply(o, proj.contiguous(), f(self.conv_w), f(self.conv_b), f(self.dt_bias), f(self.a_log),
                                 f(self.d_skip), f(self.b_bias), f(self.c_bias), f(self.norm_w))

@@ -44,7 +44,8 @@ def rms_norm(v, weight=None, eps: float = 1e-5):
 
 def mixer_core(proj, p: dict, heads: int, head_dim: int, d_state: int, rank: int = 1, groups: Optional[int] = None,
                chunk: int = 64, learned_lambda: bool = True, rotational: bool = True, eps: float = 1e-5,
-               conv_history=None, state=None, want_state: bool = False, fixed_lambda: float = 1.0):
+               conv_history=None, state=None, want_state: bool = False, fixed_lambda: float = 1.0,
+               bidirectional: bool = False):
     """Everything Mamba3Mixer does between its input and output projections
     (src/models/mamba3.rs:340-461, :475-484, :540-556, no post_gate_norm, one direction):
     split the projection into z | x B C | dt | lambda | theta, convolve x|B|C and apply SiLU, expand
@@ -61,6 +62,18 @@ def mixer_core(proj, p: dict, heads: int, head_dim: int, d_state: int, rank: int
     n_lam = H if learned_lambda else 0
     n_th = H * N // 2 if rotational else 0
     assert W == 2 * d_inner + 2 * bc + H + n_lam + n_th, "projection width"
+    if bidirectional:
+        # mamba3.rs:352-370: every piece is direction-major; the backward half of every piece that
+        # feeds the convolution or the scan is reversed in time (z is not: the gate is per position).
+        pieces, offset = [], d_inner
+        for width in (d_inner, bc, bc, H, n_lam, n_th):
+            if width:
+                pieces.append((offset + width // 2, offset + width))
+                offset += width
+        cols = torch.zeros(W, dtype=torch.bool)
+        for lo, hi in pieces:
+            cols[lo:hi] = True
+        proj = torch.where(cols.reshape(1, 1, W), proj.flip(1), proj)
     z, xbc, dt_raw, lam_raw, th_raw = torch.split(proj, [d_inner, d_inner + 2 * bc, H, n_lam, n_th], dim=-1)
     xbc, hist = causal_conv1d(xbc, p["conv_w"], p.get("conv_b"), conv_history, True)
     x, b_flat, c_flat = torch.split(xbc, [d_inner, bc, bc], dim=-1)
@@ -79,5 +92,8 @@ def mixer_core(proj, p: dict, heads: int, head_dim: int, d_state: int, rank: int
     lam = torch.sigmoid(lam_raw) if learned_lambda else torch.full_like(dt, fixed_lambda)
     theta = th_raw.reshape(B, T, H, N // 2) if rotational else None
     y, st = O.mamba3_scan(x5, b, c, dt, p["a_log"], lam, theta, p.get("d_skip"), state, chunk, want_state)
-    gated = y.reshape(B, T, d_inner) * F.silu(z)                    # :475-484
+    y = y.reshape(B, T, d_inner)
+    if bidirectional:                                               # :548-556: the backward heads' output back
+        y = torch.cat([y[..., :d_inner // 2], y[..., d_inner // 2:].flip(1)], dim=-1)
+    gated = y * F.silu(z)                                           # :475-484
     return gated, hist, st

@@ -693,3 +693,43 @@ def test_mixer_core_decode_matches_the_parallel_pass(rank, dtype):
     o1, ca = core.forward_cached(proj[:, :7])
     o2, _ = core.forward_cached(proj[:, 7:], ca)
     assert ref_metric(torch.cat([o1, o2], 1).float(), whole.float()) <= tol
+
+
+@pytest.mark.parametrize("dtype,rank", [(torch.float32, 1), (torch.float32, 2), (torch.bfloat16, 1)])
+def test_mixer_core_bidirectional_matches_the_oracle(dtype, rank):
+    """Mamba3Mixer::with_bidirectional (mamba3.rs:97-112): direction-major bands, the second half of the
+    heads right to left; the oracle reverses those bands in time around the one-direction path, the
+    kernels walk them backwards in place."""
+    from mamba_trainer_b200.nn import MixerCore, MixerShape
+    from oracle.mixer import mixer_core as oracle_core
+    small = dtype == torch.float32
+    H, P, N = (4, 4, 8) if small else (2, 64, 128)
+    B, T = 2, (23 if small else 200)
+    shape = MixerShape(H, P, N, rank)
+    torch.manual_seed(3 + rank)
+    core = MixerCore(shape, chunk=8 if small else 64, bidirectional=True, device="cuda")
+    g = torch.Generator().manual_seed(11)
+    r = lambda *s: torch.randn(*s, generator=g)
+    p = {"conv_w": r(4, shape.conv_channels) * 0.4, "conv_b": r(shape.conv_channels) * 0.2, "dt_bias": r(H) * 0.3 - 2.0,
+         "a_log": torch.rand(H, generator=g), "d_skip": r(H), "b_bias": r(H, N) * 0.3, "c_bias": r(H, N) * 0.3,
+         "norm_w": 1.0 + r(N) * 0.2}
+    _core_params(core, p)
+    proj = r(B, T, shape.in_proj_width).to(dtype)
+    dgated = r(B, T, shape.d_inner).to(dtype)
+    pd = proj.cuda().requires_grad_(True)
+    out = core(pd)
+    names = list(p)
+    grads = torch.autograd.grad(out, [pd] + [getattr(core, n) for n in names], grad_outputs=dgated.cuda())
+    pc = proj.double().requires_grad_(True)
+    pt = {n: v.double().requires_grad_(True) for n, v in p.items()}
+    eo, _, _ = oracle_core(pc, pt, H, P, N, rank, None, 8 if small else 64, True, True, bidirectional=True)
+    eg = torch.autograd.grad(eo, [pc] + [pt[n] for n in names], grad_outputs=dgated.double())
+    check = check_f32 if small else check_bf16
+    check("gated", out, eo.detach())
+    di, bc = shape.d_inner, shape.bc_width
+    for name, (lo, hi) in {"z": (0, di), "x": (di, 2 * di), "B": (2 * di, 2 * di + bc), "C": (2 * di + bc, 2 * di + 2 * bc),
+                           "dt": (2 * di + 2 * bc, 2 * di + 2 * bc + H)}.items():
+        check("dproj." + name, grads[0][..., lo:hi], eg[0][..., lo:hi])
+    for n, a_, e_ in zip(names, grads[1:], eg[1:]):
+        if small or n not in ("a_log", "dt_bias"):
+            check("d" + n, a_, e_)
