@@ -307,6 +307,8 @@ class MixerCore(torch.nn.Module):
         # Bidirectional (mamba3.rs:97-112): every piece of the projection is direction-major; the second
         # half of the heads walks right to left inside the convolution and the scan, and nothing is
         # reversed in memory.
+        if proj.shape[1] == 0:                      # nothing to scan (scan.rs:134-144)
+            return proj.new_zeros((proj.shape[0], 0, s.d_inner)) + 0.0 * proj.sum()
         o = {"shape": s, "chunk": self.chunk, "eps": self.eps, "norm": self.use_norm, "disc": int(self.disc),
              "path": path, "reverse_heads": s.heads // 2 if self.bidirectional else 0}
         f = lambda t: None if t is None else t.to(torch.float32).contiguous()

@@ -733,3 +733,26 @@ def test_mixer_core_bidirectional_matches_the_oracle(dtype, rank):
     for n, a_, e_ in zip(names, grads[1:], eg[1:]):
         if small or n not in ("a_log", "dt_bias"):
             check("d" + n, a_, e_)
+
+
+def test_mixer_core_degenerate_lengths():
+    """A single position and an empty window through the training path."""
+    from mamba_trainer_b200.nn import MixerCore, MixerShape
+    from oracle.mixer import mixer_core as oracle_core
+    H, P, N = 2, 4, 6
+    shape = MixerShape(H, P, N)
+    torch.manual_seed(0)
+    core = MixerCore(shape, chunk=4, device="cuda")
+    p = {n: getattr(core, n).detach().cpu().double() for n in ("conv_w", "conv_b", "dt_bias", "a_log", "d_skip", "b_bias",
+                                                              "c_bias", "norm_w")}
+    proj = torch.randn(3, 1, shape.in_proj_width)
+    pd = proj.cuda().requires_grad_(True)
+    out = core(pd)
+    (gp,) = torch.autograd.grad(out.sum(), [pd])
+    pc = proj.double().requires_grad_(True)
+    eo, _, _ = oracle_core(pc, p, H, P, N, chunk=4)
+    (ep,) = torch.autograd.grad(eo.sum(), [pc])
+    check_f32("gated", out, eo.detach())
+    check_f32("dproj", gp, ep)
+    empty = core(torch.zeros(3, 0, shape.in_proj_width, device="cuda", requires_grad=True))
+    assert tuple(empty.shape) == (3, 0, shape.d_inner)
