@@ -1,5 +1,6 @@
 // Host-side interface of the tensor-core kernel family.
 #pragma once
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -20,7 +21,17 @@ inline int tc_tiles(int seq, int rank) { return (seq + tc_tile_steps(rank) - 1) 
 // Start delay per CTA group in cycles (M3_TC_STAGGER overrides; 0 disables).
 int tc_stagger_cycles(bool backward);
 
+// A tensor map that lands a [128 tokens x cols] bf16 tile of a dense [B, T, H, cols] tensor directly in
+// the kernels' operand layout (8 x 8 core matrices tiled [rows/8][cols/8]): dimensions
+// (8 elements, 8 tokens, H*cols/8 column groups, B*T/8 token groups), box (8, 8, cols/8, 16), so the
+// tile of (batch b, head h, first token t0) is the box at (0, 0, h*cols/8, (b*T + t0)/8).  Needs T % 8 == 0
+// and a 16-byte aligned base.  Returns false when the driver refuses (the caller then takes the
+// register path).
+bool tc_make_tile_map(CUtensorMap* map, const void* base, int B, int T, int H, int cols);
+
 struct TcFwdParams {
+  alignas(64) CUtensorMap tm_b, tm_c, tm_x;   // valid when use_tma
+  int use_tma;        // rank 1, real dynamics, T % 8 == 0, no right-to-left heads
   const __nv_bfloat16 *x, *b, *c, *dt, *lam, *theta;
   const float *a_log, *d_skip, *h0, *lu0, *angle0;
   __nv_bfloat16* y;

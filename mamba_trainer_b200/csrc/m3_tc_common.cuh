@@ -93,6 +93,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
+// Bulk tensor copies (TMA) of this GPU's own memory into this CTA's shared memory, completion
+// counted in bytes on an mbarrier.  expect_tx arms the barrier for one phase.
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// One box of a 4-D tiled tensor map whose two inner coordinates are zero (see tc_make_tile_map).
+__device__ __forceinline__ void tma_load_tile(void* dst, const void* tensor_map, uint64_t* bar, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(tensor_map), "r"(smem_u32(bar)), "r"(0), "r"(0), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }

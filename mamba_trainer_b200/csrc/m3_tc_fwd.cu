@@ -25,6 +25,13 @@ constexpr uint32_t OFF_C = 0, OFF_B = 32768, OFF_X = 65536, OFF_XW = 81920, OFF_
 // scalar arrays: dt, lam, a, ac, g, w, sw, eac ; then carry[64], quarter sums[4][64]
 constexpr uint32_t kSmemBytes = OFF_SC + (2 * kNumScal * kScal + 64 + 256) * 4 + 64;
 constexpr uint32_t TM_G = 0, TM_Y = 128, TM_H = 192, TM_COLS = 256;
+// The TMA-fed variant (rank 1, real dynamics): C^, B^ and X~ are the raw rows, landed in operand layout
+// by bulk tensor copies, and exist twice so that the next tile arrives while this one computes; no
+// angle buffer.
+constexpr uint32_t TO_C0 = 0, TO_C1 = 65536, TO_X0 = 131072, TO_X1 = 147456,  // B^ follows its C^ at + 32768
+                   TO_XW = 163840, TO_H = 180224, TO_SC = 196608;
+constexpr uint32_t kSmemBytesTma = TO_SC + (2 * kNumScal * kScal + 64 + 256) * 4 + 64;
+constexpr uint32_t kTileBytesTma = 2 * kRows * kN * 2 + kRows * kP * 2;  // C, B and x of one tile
 
 #ifdef M3_TC_TIMING
 __device__ long long g_tc_timing[16];
@@ -35,17 +42,18 @@ __device__ long long g_tc_timing[16];
 #define TOCK(i) do { } while (0)
 #endif
 
-template <int R, bool ROT>
-__global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
+template <int R, bool ROT, bool TMA>
+__global__ void __launch_bounds__(256, 1) tc_fwd_kernel(const __grid_constant__ TcFwdParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
+  static_assert(!TMA || (R == 1 && !ROT), "the TMA-fed variant serves rank 1 with real dynamics");
   constexpr int LT = kRows / R;  // time steps per tile
-  uint8_t* sC = smem + OFF_C;    // C^ operand, later M = G o band
-  uint8_t* sB = smem + OFF_B;
-  uint8_t* sX = smem + OFF_X;
-  uint8_t* sXw = smem + OFF_XW;
-  uint8_t* sH = smem + OFF_H;    // bf16 H [p][n]
-  float* sPhi = reinterpret_cast<float*>(smem + OFF_PHI);
-  float* sc = reinterpret_cast<float*>(smem + OFF_SC);
+  uint8_t* sC = smem + (TMA ? TO_C0 : OFF_C);    // C^ operand, later M = G o band
+  uint8_t* sB = smem + (TMA ? TO_C0 + 32768 : OFF_B);
+  uint8_t* sX = smem + (TMA ? TO_X0 : OFF_X);
+  uint8_t* sXw = smem + (TMA ? TO_XW : OFF_XW);
+  uint8_t* sH = smem + (TMA ? TO_H : OFF_H);    // bf16 H [p][n]
+  float* sPhi = reinterpret_cast<float*>(smem + OFF_PHI);  // not used by the TMA-fed variant
+  float* sc = reinterpret_cast<float*>(smem + (TMA ? TO_SC : OFF_SC));
   // Two sets of per-token scalars: the next tile's are computed while this tile's products run.
   auto scal_set = [&](int i) {
     float* q = sc + i * kNumScal * kScal;
@@ -54,8 +62,8 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
   };
   float* s_carry = sc + 2 * kNumScal * kScal;  // [64] running angle
   float* s_q = s_carry + 64;             // [4][64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_q + 256);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_q + 256);  // [0], [1]: tensor-core phases; [2], [3]: tile arrivals
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
@@ -74,6 +82,8 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
   if (tid == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
+    mbar_init(&bars[2], 1);
+    mbar_init(&bars[3], 1);
   }
   if (warp == 0) tmem_alloc(tmem_slot, TM_COLS);
   if (ROT && tid < kNH) s_carry[tid] = p.angle0 ? p.angle0[(size_t)bh * kNH + tid] : 0.0f;
@@ -122,7 +132,21 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
   RawBC<R, ROT> raw_bc;
   RawPX<R> raw_x;
   RawTheta<R> raw_th;
-  {
+  // TMA-fed variant: one thread asks for the three tiles of a time block; they land in operand layout.
+  auto request_tile = [&](int kk) {
+    uint64_t* bar = &bars[2 + (kk & 1)];
+    uint8_t* base = smem + ((kk & 1) ? TO_C1 : TO_C0);
+    const int tg = (b * T + kk * LT) / 8;  // token group of the tile's first row (T % 8 == 0)
+    mbar_expect_tx(bar, kTileBytesTma);
+    tma_load_tile(base, &p.tm_c, bar, h * (kN / 8), tg);
+    tma_load_tile(base + 32768, &p.tm_b, bar, h * (kN / 8), tg);
+    tma_load_tile(smem + ((kk & 1) ? TO_X1 : TO_X0), &p.tm_x, bar, h * (kP / 8), tg);
+  };
+  int requested = 0;  // tiles asked for so far (the same in every thread)
+  if (TMA) {
+    if (tid == 0) request_tile(0);
+    requested = 1;
+  } else {
     const size_t tok_first = tok_at(0);
     issue_bc<R, ROT>(raw_bc, p.b, p.c, tok_first, Hs, T, 0);
     issue_px<R>(raw_x, p.x, tok_first, Hs, T, 0);
@@ -157,6 +181,16 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
     float *s_ac = ts.ac, *s_eac = ts.eac;
     TICK(0);
     const size_t tok0 = tok_at(t0);  // token-head index of l = 0 (stride Hs per step)
+    if (TMA) {
+      sC = smem + ((k & 1) ? TO_C1 : TO_C0);
+      sB = sC + 32768;
+      sX = smem + ((k & 1) ? TO_X1 : TO_X0);
+      // the other set was last touched by tile k-1, whose products and reads are complete
+      if (k + 1 < ntiles) {
+        if (tid == 0) request_tile(k + 1);
+        requested = k + 2;
+      }
+    }
     // ---- 1. the tile's raw inputs were put in flight one tile ago -----------------------------
     if (p.ckpt_h) {  // the bf16 state entering this tile, for the backward pass
       const uint4* src = reinterpret_cast<const uint4*>(sH);
@@ -168,8 +202,40 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
     TICK(2);
     TICK(3);
     // ---- 3. convert and store the operands -----------------------------------------------------
-    commit_bc<R, ROT>(raw_bc, sB, sC, sPhi);
-    commit_px<R>(raw_x, sX, sXw, ts.sw);
+    if (TMA) {
+      {
+        const bool ok = mbar_wait(&bars[2 + (k & 1)], (k >> 1) & 1);
+        if (__syncthreads_or(!ok)) { failed = true; break; }
+      }
+      const int nv = T - t0;  // rows of this tile that exist; the box ran on into the next sequence
+      if (nv < kRows) {
+        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+        for (int q = tid; q < kRows * (kN / 8); q += 256) {
+          const int r = q / (kN / 8), g8 = q % (kN / 8);
+          if (r >= nv) {
+            *reinterpret_cast<uint4*>(sC + tile_off(r, 8 * g8, kN)) = z;
+            *reinterpret_cast<uint4*>(sB + tile_off(r, 8 * g8, kN)) = z;
+            if (g8 < kP / 8) *reinterpret_cast<uint4*>(sX + tile_off(r, 8 * g8, kP)) = z;
+          }
+        }
+        __syncthreads();
+      }
+      // sigma_w X~: the scaled copy of x for the state update
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int q = tid + 256 * i;  // 16-byte chunk of the [128 x 64] tile: [r/8][c/8][r%8]
+        const int r = (q >> 6) * 8 + (q & 7);
+        float v[8];
+        load_chunk(sX, (uint32_t)q * 16u, v);
+        const float sw = ts.sw[r];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] *= sw;
+        store_chunk(sXw, (uint32_t)q * 16u, v);
+      }
+    } else {
+      commit_bc<R, ROT>(raw_bc, sB, sC, sPhi);
+      commit_px<R>(raw_x, sX, sXw, ts.sw);
+    }
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -183,10 +249,12 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
       umma_commit(&bars[0]);
     }
     if (k + 1 < ntiles) {  // next tile's loads: in flight during both products and epilogues
-      const size_t tok1 = tok0 + (size_t)LT * Hs;
-      issue_bc<R, ROT>(raw_bc, p.b, p.c, tok1, Hs, T, t0 + LT);
-      issue_px<R>(raw_x, p.x, tok1, Hs, T, t0 + LT);
-      if (ROT) issue_theta<R>(raw_th, p.theta, tok1, Hs, T, t0 + LT);
+      if (!TMA) {
+        const size_t tok1 = tok0 + (size_t)LT * Hs;
+        issue_bc<R, ROT>(raw_bc, p.b, p.c, tok1, Hs, T, t0 + LT);
+        issue_px<R>(raw_x, p.x, tok1, Hs, T, t0 + LT);
+        if (ROT) issue_theta<R>(raw_th, p.theta, tok1, Hs, T, t0 + LT);
+      }
       prepare_scalars(k + 1);   // while G and Yoff are being computed
     }
     {
@@ -334,12 +402,18 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
     }
     __syncthreads();
     copy_out<R, kP>(sXw, p.y, tok0, Hs, T, t0);
+    if (TMA) fence_async_smem();  // this tile's writes to its operand set, before a bulk copy reuses it
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     TICK(8);
   }
   if (failed && tid == 0 && p.err) atomicExch(p.err, 1);
+  if (TMA && failed) {
+    // A wait gave up: the bulk copies already requested still target this CTA's shared memory.
+    // Give each of them one more bounded wait before the CTA lets go of it.
+    for (int kk = requested > 2 ? requested - 2 : 0; kk < requested; ++kk) mbar_wait(&bars[2 + (kk & 1)], (kk >> 1) & 1);
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, TM_COLS);
@@ -347,10 +421,18 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(TcFwdParams p) {
 
 template <int R>
 cudaError_t launch_r(cudaStream_t st, const TcFwdParams& p, bool rot) {
-  auto kern = rot ? tc_fwd_kernel<R, true> : tc_fwd_kernel<R, false>;
+  auto kern = rot ? tc_fwd_kernel<R, true, false> : tc_fwd_kernel<R, false, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return e;
   kern<<<p.B * p.H, 256, kSmemBytes, st>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_tma(cudaStream_t st, const TcFwdParams& p) {
+  auto kern = tc_fwd_kernel<1, false, true>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytesTma);
+  if (e != cudaSuccess) return e;
+  kern<<<p.B * p.H, 256, kSmemBytesTma, st>>>(p);
   return cudaGetLastError();
 }
 
@@ -374,7 +456,28 @@ int tc_stagger_cycles(bool backward) {
   return backward ? 6000 : 3000;
 }
 
+bool tc_make_tile_map(CUtensorMap* map, const void* base, int B, int T, int H, int cols) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess) fn = nullptr;
+    return reinterpret_cast<EncodeFn>(fn);
+  }();
+  if (!encode || T % 8 || cols % 8 || (reinterpret_cast<uintptr_t>(base) & 15)) return false;
+  const cuuint64_t dims[4] = {8, 8, (cuuint64_t)H * cols / 8, (cuuint64_t)B * T / 8};
+  const cuuint64_t strides[3] = {(cuuint64_t)H * cols * 2, 16, (cuuint64_t)8 * H * cols * 2};
+  const cuuint32_t box[4] = {8, 8, (cuuint32_t)cols / 8, 16};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 cudaError_t tc_forward(cudaStream_t st, const TcFwdParams& p, bool rot) {
+  if (p.use_tma && p.R == 1 && !rot) return launch_tma(st, p);
   switch (p.R) {
     case 1: return launch_r<1>(st, p, rot);
     case 2: return launch_r<2>(st, p, rot);

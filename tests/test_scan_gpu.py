@@ -315,6 +315,8 @@ def tc_workload(rank, rot, seq, batch=2, heads=2, disc=Discretization.LearnedTra
     (1, False, 300, True, Discretization.LearnedTrapezoid),
     (1, True, 256, False, Discretization.LearnedTrapezoid),
     (1, False, 128, False, Discretization.Euler),
+    (1, False, 200, True, Discretization.LearnedTrapezoid),    # bulk-copy path with a ragged last tile
+    (1, False, 384, False, Discretization.Trapezoid),          # bulk-copy path, three full tiles
     (2, True, 200, True, Discretization.LearnedTrapezoid),
     (4, True, 130, True, Discretization.Trapezoid),
     (4, False, 64, False, Discretization.LearnedTrapezoid),
@@ -336,6 +338,8 @@ def test_tensor_core_forward(rank, rot, seq, state, disc):
     (1, False, 300, True, Discretization.LearnedTrapezoid),
     (1, True, 256, False, Discretization.LearnedTrapezoid),
     (1, False, 128, False, Discretization.Euler),
+    (1, False, 200, True, Discretization.LearnedTrapezoid),    # bulk-copy path with a ragged last tile
+    (1, False, 384, False, Discretization.Trapezoid),          # bulk-copy path, three full tiles
     (2, True, 200, True, Discretization.LearnedTrapezoid),
     (4, True, 130, True, Discretization.Trapezoid),
     (4, False, 64, False, Discretization.LearnedTrapezoid),
