@@ -47,6 +47,8 @@ struct TcFwdParams {
 cudaError_t tc_forward(cudaStream_t st, const TcFwdParams& p, bool rotational);
 
 struct TcBwdParams {
+  alignas(64) CUtensorMap tm_b, tm_c, tm_x, tm_dy;   // valid when use_tma (as in TcFwdParams)
+  int use_tma;
   const __nv_bfloat16 *x, *b, *c, *dt, *lam, *theta, *dy;
   const float *a_log, *d_skip, *h0, *lu0;
   const float *dh, *dlu, *dangle;        // gradients reaching the returned state, or NULL

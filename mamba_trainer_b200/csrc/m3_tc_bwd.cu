@@ -21,7 +21,8 @@ namespace {
 
 constexpr uint32_t OFF_C = 0, OFF_B = 32768, OFF_X = 65536, OFF_DY = 81920, OFF_XW = 98304, OFF_DYE = 114688,
                    OFF_M = 131072, OFF_DG = 163840, OFF_HS = 196608, OFF_SC = 212992;
-constexpr int kScalFloats = kNumScal * kScal + 256 * 4 + 512 + 256 + 132 + 132 + 16 + 64 + 64 + 256;
+constexpr int kScalFloats = 2 * kNumScal * kScal + 256 * 4 + 512 + 256 + 132 + 132 + 16 + 64 + 64 + 256;
+static_assert(OFF_SC + kScalFloats * 4 + 64 <= 232448, "backward shared memory exceeds the 227 KB a CTA can have");
 constexpr uint32_t kSmemBytes = OFF_SC + kScalFloats * 4 + 64;
 constexpr uint32_t TM_G = 0, TM_DM = 128, TM_T1 = 256, TM_DH = 384, TM_COLS = 512;
 // phase B reuse: dB^ accumulates over G's columns, dX~ and U over dM's.
@@ -34,18 +35,26 @@ __device__ long long g_tcb_timing[16];
 #define TICK(i) do { } while (0)
 #endif
 
-template <int R, bool ROT>
-__global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
+// TMA: rank 1 with real dynamics; C^, B^, X~ and dY~ are the raw rows, landed in operand layout by bulk
+// tensor copies that are requested as soon as the previous tile has read its own, the checkpoint
+// by a plain bulk copy.
+template <int R, bool ROT, bool TMA>
+__global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ TcBwdParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
+  static_assert(!TMA || (R == 1 && !ROT), "the TMA-fed variant serves rank 1 with real dynamics");
   constexpr int LT = kRows / R;
   uint8_t *sC = smem + OFF_C, *sB = smem + OFF_B, *sX = smem + OFF_X, *sXw = smem + OFF_XW, *sDY = smem + OFF_DY,
           *sDYe = smem + OFF_DYE, *sM = smem + OFF_M, *sDG = smem + OFF_DG, *sHS = smem + OFF_HS;
   float* sPhi = reinterpret_cast<float*>(smem + OFF_M);    // alive while staging and again after phase B
   float* sDphi = reinterpret_cast<float*>(smem + OFF_DG);  // alive after phase B
   float* sc = reinterpret_cast<float*>(smem + OFF_SC);
-  TileScalars ts{sc, sc + kScal, sc + 2 * kScal, sc + 3 * kScal, sc + 4 * kScal, sc + 5 * kScal, sc + 6 * kScal,
-                 sc + 7 * kScal, sc + 8 * kScal};
-  float* part_row = sc + kNumScal * kScal;   // [2][128]
+  // Two sets of per-token scalars: the next tile's are computed while this tile's phase-B products run.
+  auto scal_set = [&](int i) {
+    float* q = sc + i * kNumScal * kScal;
+    return TileScalars{q, q + kScal, q + 2 * kScal, q + 3 * kScal, q + 4 * kScal, q + 5 * kScal, q + 6 * kScal,
+                       q + 7 * kScal, q + 8 * kScal};
+  };
+  float* part_row = sc + 2 * kNumScal * kScal;   // [2][128]
   float* part_t1 = part_row + 256;    // [2][128]
   float* part_q = part_t1 + 256;      // [2][128]
   float* part_dg = part_q + 256;      // [2][128]
@@ -57,8 +66,8 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
   float* s_carry = s_red + 16;        // [64] angle entering the tile
   float* s_dcar = s_carry + 64;       // [64] sum of d phi over later tiles
   float* s_q = s_dcar + 64;           // [4][64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_q + 256);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_q + 256);  // [0], [1]: tensor-core phases; [2]: x, dy; [3]: checkpoint; [4]: C, B
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
@@ -78,6 +87,9 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
   if (tid == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
+    mbar_init(&bars[2], 1);
+    mbar_init(&bars[3], 1);
+    mbar_init(&bars[4], 1);
   }
   if (warp == 0) tmem_alloc(tmem_slot, TM_COLS);
   if (tid < kNH) s_dcar[tid] = 0.0f;
@@ -105,6 +117,38 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
   bool failed = false;
   float nx_dt, nx_lam;  // dt / lambda of the next tile to process, loaded one tile ahead
   load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, (ntiles - 1) * LT, rev);
+  // TMA-fed variant: one thread asks for a tile's rows / its checkpoint.
+  auto request_cb = [&](int kk) {
+    const int tg = (b * T + kk * LT) / 8;  // token group of the tile's first row (T % 8 == 0)
+    mbar_expect_tx(&bars[4], 2 * kRows * kN * 2);
+    tma_load_tile(sC, &p.tm_c, &bars[4], h * (kN / 8), tg);
+    tma_load_tile(sB, &p.tm_b, &bars[4], h * (kN / 8), tg);
+  };
+  auto request_xdy = [&](int kk) {
+    const int tg = (b * T + kk * LT) / 8;
+    mbar_expect_tx(&bars[2], 2 * kRows * kP * 2);
+    tma_load_tile(sX, &p.tm_x, &bars[2], h * (kP / 8), tg);
+    tma_load_tile(sDY, &p.tm_dy, &bars[2], h * (kP / 8), tg);
+  };
+  auto request_ckpt = [&](int kk) {
+    mbar_expect_tx(&bars[3], kN * kP * 2);
+    bulk_load(sHS, p.ckpt_h + ((size_t)bh * ntiles + kk) * kN * kP, kN * kP * 2, &bars[3]);
+  };
+  auto prepare_scalars = [&](int kk, int slot) {  // tile kk's scalars, then the loads of the tile after it
+    tile_scalars<R>(scal_set(slot), nx_dt, nx_lam, A, T, kk * LT);
+    load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, (kk - 1) * LT, rev);
+  };
+  prepare_scalars(ntiles - 1, 0);
+  int rows_requested = 0, ckpt_requested = 0, cb_requested = 0;  // the same in every thread
+  bool early_cb = false;
+  if (TMA) {
+    if (tid == 0) {
+      request_cb(ntiles - 1);
+      request_xdy(ntiles - 1);
+      request_ckpt(ntiles - 1);
+    }
+    rows_requested = ckpt_requested = cb_requested = 1;
+  }
 #ifdef M3_TC_TIMING
   long long tick_ = clock64();
 #endif
@@ -118,18 +162,17 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
     RawPX<R> raw_x, raw_dy;
     RawTheta<R> raw_th;
     uint4 raw_h[4];
-    issue_bc<R, ROT>(raw_bc, p.b, p.c, tok0, Hs, T, t0);
-    issue_px<R>(raw_x, p.x, tok0, Hs, T, t0);
-    issue_px<R>(raw_dy, p.dy, tok0, Hs, T, t0);
-    if (ROT) issue_theta<R>(raw_th, p.theta, tok0, Hs, T, t0);
-    {
+    if (!TMA) {
+      issue_bc<R, ROT>(raw_bc, p.b, p.c, tok0, Hs, T, t0);
+      issue_px<R>(raw_x, p.x, tok0, Hs, T, t0);
+      issue_px<R>(raw_dy, p.dy, tok0, Hs, T, t0);
+      if (ROT) issue_theta<R>(raw_th, p.theta, tok0, Hs, T, t0);
       const uint4* src = reinterpret_cast<const uint4*>(p.ckpt_h + ((size_t)bh * ntiles + k) * kN * kP);
 #pragma unroll
       for (int i = 0; i < 4; ++i) raw_h[i] = __ldg(src + tid + 256 * i);
     }
     TICK(0);
-    tile_scalars<R>(ts, nx_dt, nx_lam, A, T, t0);
-    load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, t0 - LT, rev);
+    const TileScalars ts = scal_set(it & 1);  // filled during the previous tile's phase-B wait (or the prologue)
     if (ROT) {
       if (tid < kNH) s_carry[tid] = p.ckpt_angle[((size_t)bh * ntiles + k) * kNH + tid];
       commit_theta<R>(raw_th, sPhi);
@@ -139,10 +182,46 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
     __syncthreads();
     TICK(1);
     // ---- 2-3. operands ------------------------------------------------------------------------------
-    commit_bc<R, ROT>(raw_bc, sB, sC, sPhi);
-    commit_px<R>(raw_x, sX, sXw, ts.sw);
-    commit_px<R>(raw_dy, sDY, sDYe, ts.eac);
-    {  // H_k, the bf16 state entering the tile, already in operand layout [p][n]
+    if (TMA) {
+      {
+        const bool ok = mbar_wait(&bars[4], it & 1) && mbar_wait(&bars[2], it & 1) && mbar_wait(&bars[3], it & 1);
+        if (__syncthreads_or(!ok)) { failed = true; break; }
+      }
+      const int nv = T - t0;  // rows of this tile that exist; the box ran on into the next sequence
+      if (nv < kRows) {
+        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+        for (int q = tid; q < kRows * (kN / 8); q += 256) {
+          const int r = q / (kN / 8), g8 = q % (kN / 8);
+          if (r >= nv) {
+            *reinterpret_cast<uint4*>(sC + tile_off(r, 8 * g8, kN)) = z;
+            *reinterpret_cast<uint4*>(sB + tile_off(r, 8 * g8, kN)) = z;
+            if (g8 < kP / 8) {
+              *reinterpret_cast<uint4*>(sX + tile_off(r, 8 * g8, kP)) = z;
+              *reinterpret_cast<uint4*>(sDY + tile_off(r, 8 * g8, kP)) = z;
+            }
+          }
+        }
+        __syncthreads();
+      }
+      // the scaled copies sigma_w X~ and exp(acum) dY~
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int q = tid + 256 * i;  // 16-byte chunk of a [128 x 64] tile: [r/8][c/8][r%8]
+        const int r = (q >> 6) * 8 + (q & 7);
+        float v[8], u[8];
+        load_chunk(sX, (uint32_t)q * 16u, v);
+        load_chunk(sDY, (uint32_t)q * 16u, u);
+        const float sw = ts.sw[r], ea = ts.eac[r];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v[j] *= sw; u[j] *= ea; }
+        store_chunk(sXw, (uint32_t)q * 16u, v);
+        store_chunk(sDYe, (uint32_t)q * 16u, u);
+      }
+    } else {
+      commit_bc<R, ROT>(raw_bc, sB, sC, sPhi);
+      commit_px<R>(raw_x, sX, sXw, ts.sw);
+      commit_px<R>(raw_dy, sDY, sDYe, ts.eac);
+      // H_k, the bf16 state entering the tile, already in operand layout [p][n]
       uint4* dst = reinterpret_cast<uint4*>(sHS);
 #pragma unroll
       for (int i = 0; i < 4; ++i) dst[tid + 256 * i] = raw_h[i];
@@ -152,7 +231,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
     __syncthreads();
     TICK(2);
 #ifndef M3_NO_L2_PREFETCH
-    if (k > 0)  // warm L2 with the tile after this one (behind this tile's own loads)
+    if (!TMA && k > 0)  // warm L2 with the tile after this one (behind this tile's own loads)
       prefetch_tile_l2<R, ROT>(p.b, p.c, p.x, p.dy, p.theta, p.ckpt_h + ((size_t)bh * ntiles + k - 1) * kN * kP,
                                tok0 - (size_t)LT * Hs, Hs, T, t0 - LT);
 #endif
@@ -210,19 +289,35 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
           load_col_scalars<R>(cs, ts, c0 + 16 * hb);
           const int s0 = (c0 + 16 * hb) / R;
           const float rf = row_factor(acl, ts.ac[s0 + 16 / R - 1]);  // one exponential per chunk
+          // A chunk whose last step precedes the first row of this warp lies strictly below the
+          // diagonal for all 32 rows (the case of most chunks of the lower rows): no selects needed.
+          if (s0 + 16 / R - 1 < (quad * 32) / R) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {  // branch-free selects: below / on / above the diagonal
-            const int si = j / R, s = s0 + si;
-            const bool below = s < rl, on = s == rl;
-            const float dec = rf * cs.cf[si];
-            const float wgt = below ? cs.w[si] * dec : (on ? cs.g[si] : 0.0f);
-            const float gd = g[j] * dec;
-            const float d_ = below ? dm[j] * gd : 0.0f;
-            mv[j] = g[j] * wgt;
-            dgv[j] = dm[j] * wgt;
-            rowE += d_ * cs.w[si];
-            dgp += on ? dm[j] * g[j] : 0.0f;
-            dbd[16 * hb + j] = d_;
+            for (int j = 0; j < 16; ++j) {
+              const int si = j / R;
+              const float dec = rf * cs.cf[si];
+              const float wgt = cs.w[si] * dec;
+              const float d_ = dm[j] * (g[j] * dec);
+              mv[j] = g[j] * wgt;
+              dgv[j] = dm[j] * wgt;
+              rowE = fmaf(d_, cs.w[si], rowE);
+              dbd[16 * hb + j] = d_;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {  // branch-free selects: below / on / above the diagonal
+              const int si = j / R, s = s0 + si;
+              const bool below = s < rl, on = s == rl;
+              const float dec = rf * cs.cf[si];
+              const float wgt = below ? cs.w[si] * dec : (on ? cs.g[si] : 0.0f);
+              const float gd = g[j] * dec;
+              const float d_ = below ? dm[j] * gd : 0.0f;
+              mv[j] = g[j] * wgt;
+              dgv[j] = dm[j] * wgt;
+              rowE += d_ * cs.w[si];
+              dgp += on ? dm[j] * g[j] : 0.0f;
+              dbd[16 * hb + j] = d_;
+            }
           }
           float lo[8], hi[8];
 #pragma unroll
@@ -298,12 +393,22 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
       gemm_issue(tm + TM_DH, mn_major(aC, kN), mn_major(smem_u32(sDYe), kP), make_idesc(64, 1, 1), kRows, true);
       umma_commit(&bars[1]);
     }
+    if (k > 0) prepare_scalars(k - 1, (it + 1) & 1);  // while the five products run
     {
       const bool ok = mbar_wait(&bars[1], it & 1);
       if (__syncthreads_or(!ok)) { failed = true; break; }
     }
     tc_fence_after();
     TICK(5);
+    if (TMA && k > 0) {
+      // C^ and B^ of this tile have been read for the last time (only the gradient through last_u of the
+      // final token looks at B^ again): their successors can start to arrive now.
+      early_cb = !(last_tile && p.dlu);
+      if (early_cb) {
+        if (tid == 0) request_cb(k - 1);
+        ++cb_requested;
+      }
+    }
     // ---- 7. epilogue B -------------------------------------------------------------------------
     if (ROT) {  // the angles again (their buffer held M in between)
       RawTheta<R> th2;
@@ -427,13 +532,27 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
       for (int q4 = 0; q4 < 4; ++q4) tmem_ld_fence(gc[q4]);
       finish(gc, sC, sDG, false);    // dG is spent: its buffer stages dC
       TICK(13);
+      if (TMA) fence_async_smem();  // this tile's reads of its rows, before bulk copies replace them
       __syncthreads();
       TICK(14);
+      if (TMA && k > 0) {  // the next tile's rows arrive during the copy-out and the per-token scalars
+        if (tid == 0) {
+          if (!early_cb) request_cb(k - 1);
+          request_xdy(k - 1);
+        }
+        if (!early_cb) ++cb_requested;
+        ++rows_requested;
+      }
       if (p.dx) copy_out<R, kP>(sHS, p.dx, tok0, Hs, T, t0);
       if (p.db) copy_out<R, kN>(sXw, p.db, tok0, Hs, T, t0);
       if (p.dc) copy_out<R, kN>(sDG, p.dc, tok0, Hs, T, t0);
       TICK(15);
+      if (TMA) fence_async_smem();  // dx was staged where the next checkpoint lands
       __syncthreads();
+      if (TMA && k > 0) {
+        if (tid == 0) request_ckpt(k - 1);
+        ++ckpt_requested;
+      }
       if (ROT) {
         // d phi of a time step sums its R rows (adjacent lanes); it then overwrites dG's buffer,
         // which the phase-B products have finished reading.
@@ -606,14 +725,29 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(TcBwdParams p) {
     if (tid == 0) p.ip0[bh] = tot;
   }
   if (failed && tid == 0 && p.err) atomicExch(p.err, 1);
+  if (TMA && failed) {
+    // A wait gave up: bulk copies already requested still target this CTA's shared memory.  Give the
+    // latest request of each kind one more bounded wait before the CTA lets go of it.
+    if (cb_requested > 0) mbar_wait(&bars[4], (cb_requested - 1) & 1);
+    if (rows_requested > 0) mbar_wait(&bars[2], (rows_requested - 1) & 1);
+    if (ckpt_requested > 0) mbar_wait(&bars[3], (ckpt_requested - 1) & 1);
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, TM_COLS);
 }
 
+cudaError_t launch_tma(cudaStream_t st, const TcBwdParams& p) {
+  auto kern = tc_bwd_kernel<1, false, true>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+  if (e != cudaSuccess) return e;
+  kern<<<p.B * p.H, 256, kSmemBytes, st>>>(p);
+  return cudaGetLastError();
+}
+
 template <int R>
 cudaError_t launch_r(cudaStream_t st, const TcBwdParams& p, bool rot) {
-  auto kern = rot ? tc_bwd_kernel<R, true> : tc_bwd_kernel<R, false>;
+  auto kern = rot ? tc_bwd_kernel<R, true, false> : tc_bwd_kernel<R, false, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return e;
   kern<<<p.B * p.H, 256, kSmemBytes, st>>>(p);
@@ -632,6 +766,7 @@ extern "C" void m3_debug_timing_bwd(long long* out, int reset) {
 #endif
 
 cudaError_t tc_backward(cudaStream_t st, const TcBwdParams& p, bool rot) {
+  if (p.use_tma && p.R == 1 && !rot) return launch_tma(st, p);
   switch (p.R) {
     case 1: return launch_r<1>(st, p, rot);
     case 2: return launch_r<2>(st, p, rot);

@@ -309,11 +309,21 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(const __grid_constant__ 
           load_col_scalars<R>(cs, ts, c0);
           const int s0 = c0 / R;
           const float rf = row_factor(acl, s_ac[s0 + 16 / R - 1]);  // one exponential per chunk
+          if (s0 + 16 / R - 1 < (quad * 32) / R) {
+            // strictly below the diagonal for all 32 rows of this warp: the weight needs no selects and,
+            // for one rank, is shared by every row up to the row factor
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {  // branch-free: select between below / on / above the diagonal
-            const int si = j / R, s = s0 + si;
-            const float wgt = s < l ? cs.w[si] * (rf * cs.cf[si]) : (s == l ? cs.g[si] : 0.0f);
-            m[j] = g[cc][j] * wgt;
+            for (int j = 0; j < 16; ++j) {
+              const int si = j / R;
+              m[j] = g[cc][j] * (cs.w[si] * cs.cf[si] * rf);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {  // branch-free: select between below / on / above the diagonal
+              const int si = j / R, s = s0 + si;
+              const float wgt = s < l ? cs.w[si] * (rf * cs.cf[si]) : (s == l ? cs.g[si] : 0.0f);
+              m[j] = g[cc][j] * wgt;
+            }
           }
         }
         float lo[8], hi[8];
