@@ -58,12 +58,19 @@ __device__ __forceinline__ Operand mn_major(uint32_t addr, int cols) {
   return Operand{addr, (uint32_t)(cols >> 3) << 7, 128u, (uint32_t)(cols >> 3) << 8};
 }
 
-// D[128 x n] (+)= A * B over k_total (multiple of 16); issued by ONE thread.
+// D[128 x n] (+)= A * B over k_total (multiple of 16); issued by ONE thread.  The descriptors of
+// step k differ from those of step 0 only in the start address (low 14 bits, in 16-byte units,
+// which cannot carry out of the field for shared-memory addresses), so they are built once and
+// advanced by an add: the issuing thread is on the critical path of every tile.
 __device__ __forceinline__ void gemm_issue(uint32_t tmem_d, Operand a, Operand b, uint32_t idesc, int k_total,
                                            bool accumulate_first) {
+  uint64_t da = make_desc(a.addr, a.lbo, a.sbo), db = make_desc(b.addr, b.lbo, b.sbo);
+  const uint64_t sa = a.kstep >> 4, sb = b.kstep >> 4;
+#pragma unroll 4
   for (int k = 0; k < k_total / 16; ++k) {
-    umma(tmem_d, make_desc(a.addr + k * a.kstep, a.lbo, a.sbo), make_desc(b.addr + k * b.kstep, b.lbo, b.sbo), idesc,
-         (accumulate_first || k > 0) ? 1u : 0u);
+    umma(tmem_d, da, db, idesc, (accumulate_first || k > 0) ? 1u : 0u);
+    da += sa;
+    db += sb;
   }
 }
 
