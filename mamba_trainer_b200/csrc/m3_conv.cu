@@ -215,7 +215,8 @@ __global__ void k_conv_history(ConvDims d, const T* __restrict__ x, const T* __r
 // Backward: g = dy * act'(pre) with pre recomputed; dx[t] = sum_delay w[K-1-delay] g[t+delay];
 // per-block partial sums of dw[k] = sum g[t] x[t-(K-1-k)] and dbias = sum g[t].
 template <class T, int V, int KT>
-__global__ void __launch_bounds__(kLanesT* kLanesC)
+// two blocks per SM: the kernel is bound by instruction issue and needs the warps
+__global__ void __launch_bounds__(kLanesT* kLanesC, 2)
     k_conv_bwd(ConvDims d, const T* __restrict__ x, const T* __restrict__ hist, const float* __restrict__ w,
                const float* __restrict__ bias, const T* __restrict__ dy, const T* __restrict__ dy2, T* __restrict__ dx,
                T* __restrict__ dhist, float* __restrict__ part) {
