@@ -115,16 +115,22 @@ __device__ __forceinline__ float row_factor(float ac_l, float ac_e) {
   return __expf(fminf(fmaxf(ac_l - ac_e, -87.0f), 80.0f));
 }
 
-// dt and lambda of step t0 + tid (threads tid <= LT; one step of look-ahead), as registers, so
+// The per-tile scalars are the work of warps 1-7: warp 0 holds the thread that issues the tensor-core
+// products, and that thread is held up by the tensor pipe for as long as the products run, so it must
+// not be needed at a barrier meanwhile.  Warps 1-7 meet at named barrier 1 (224 threads); every one
+// of their threads must reach each of its uses.
+__device__ __forceinline__ void scalar_warps_sync() { asm volatile("bar.sync 1, 224;" ::: "memory"); }
+
+// dt and lambda of step t0 + i in thread 32 + i (i <= LT: one step of look-ahead), as registers, so
 // the loads of the NEXT tile can be in flight while the current one computes.
 template <int R>
 __device__ __forceinline__ void load_dt_lam(float& vdt, float& vl, const __nv_bfloat16* dt, const __nv_bfloat16* lam,
                                             int disc, int b, int h, int H, int T, int t0, bool rev) {
   constexpr int LT = kRows / R;
-  const int tid = threadIdx.x, t = t0 + tid;
+  const int tid = (int)threadIdx.x - 32, t = t0 + tid;
   vdt = 0.0f;
   vl = 1.0f;
-  if (tid <= LT && t >= 0 && t < T) {
+  if (tid >= 0 && tid <= LT && t >= 0 && t < T) {
     const size_t i = ((size_t)b * T + (rev ? T - 1 - t : t)) * H + h;  // t is a scan position
     vdt = bf(dt, i);
     vl = disc == 0 ? 1.0f : (disc == 1 ? 0.5f : bf(lam, i));
@@ -133,16 +139,17 @@ __device__ __forceinline__ void load_dt_lam(float& vdt, float& vl, const __nv_bf
 
 // g, w (shifted add), a = dt A, its inclusive cumulative sum ac, sw = exp(cd - ac) w,
 // eac = exp(ac) and the column factors cf, from the (dt, lambda) registers of load_dt_lam.
-// The caller's next __syncthreads makes sw / eac / cf visible.
+// The caller's next __syncthreads makes them visible to everyone (warp 0 included).
 template <int R>
 __device__ __forceinline__ void tile_scalars(const TileScalars& s, float vdt, float vl, float A, int T, int t0) {
   constexpr int LT = kRows / R;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (threadIdx.x < 32) return;  // warp 0 takes no part (see scalar_warps_sync)
+  const int tid = (int)threadIdx.x - 32, warp = tid >> 5, lane = tid & 31;
   if (tid <= LT) {
     s.dt[tid] = vdt;
     s.lam[tid] = vl;
   }
-  __syncthreads();
+  scalar_warps_sync();
   if (tid < LT) {
     const int t = t0 + tid;
     float gv = 0.0f, wv = 0.0f, av = 0.0f;
@@ -154,8 +161,8 @@ __device__ __forceinline__ void tile_scalars(const TileScalars& s, float vdt, fl
     }
     s.g[tid] = gv; s.w[tid] = wv; s.a[tid] = av;
   }
-  __syncthreads();
-  if (warp == 0) {
+  scalar_warps_sync();
+  if (warp == 0) {  // the first of the seven
     constexpr int EPL = LT / 32;
     float loc[EPL];
     float run = 0.0f;
@@ -171,7 +178,7 @@ __device__ __forceinline__ void tile_scalars(const TileScalars& s, float vdt, fl
 #pragma unroll
     for (int i = 0; i < EPL; ++i) s.ac[lane * EPL + i] = base + loc[i];
   }
-  __syncthreads();
+  scalar_warps_sync();
   if (tid < LT) {
     constexpr int SPC = 16 / R;  // time steps per 16-column chunk
     const float cd = s.ac[LT - 1], ac = s.ac[tid];
