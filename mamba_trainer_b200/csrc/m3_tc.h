@@ -47,7 +47,7 @@ struct TcFwdParams {
 cudaError_t tc_forward(cudaStream_t st, const TcFwdParams& p, bool rotational);
 
 struct TcBwdParams {
-  alignas(64) CUtensorMap tm_b, tm_c, tm_x, tm_dy;   // valid when use_tma (as in TcFwdParams)
+  alignas(64) CUtensorMap tm_b, tm_c;   // valid when use_tma (as in TcFwdParams; x and dy go through registers)
   int use_tma;
   const __nv_bfloat16 *x, *b, *c, *dt, *lam, *theta, *dy;
   const float *a_log, *d_skip, *h0, *lu0;

@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
   float* s_carry = s_red + 16;        // [64] angle entering the tile
   float* s_dcar = s_carry + 64;       // [64] sum of d phi over later tiles
   float* s_q = s_dcar + 64;           // [4][64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_q + 256);  // [0], [1]: tensor-core phases; [2]: x, dy; [3]: checkpoint; [4]: C, B
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_q + 256);  // [0], [1]: tensor-core phases; [2]: unused; [3]: checkpoint; [4]: C, B
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -124,12 +124,6 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
     tma_load_tile(sC, &p.tm_c, &bars[4], h * (kN / 8), tg);
     tma_load_tile(sB, &p.tm_b, &bars[4], h * (kN / 8), tg);
   };
-  auto request_xdy = [&](int kk) {
-    const int tg = (b * T + kk * LT) / 8;
-    mbar_expect_tx(&bars[2], 2 * kRows * kP * 2);
-    tma_load_tile(sX, &p.tm_x, &bars[2], h * (kP / 8), tg);
-    tma_load_tile(sDY, &p.tm_dy, &bars[2], h * (kP / 8), tg);
-  };
   auto request_ckpt = [&](int kk) {
     mbar_expect_tx(&bars[3], kN * kP * 2);
     bulk_load(sHS, p.ckpt_h + ((size_t)bh * ntiles + kk) * kN * kP, kN * kP * 2, &bars[3]);
@@ -139,15 +133,14 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
     load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, (kk - 1) * LT, rev);
   };
   prepare_scalars(ntiles - 1, 0);
-  int rows_requested = 0, ckpt_requested = 0, cb_requested = 0;  // the same in every thread
+  int ckpt_requested = 0, cb_requested = 0;  // the same in every thread
   bool early_cb = false;
   if (TMA) {
     if (tid == 0) {
       request_cb(ntiles - 1);
-      request_xdy(ntiles - 1);
       request_ckpt(ntiles - 1);
     }
-    rows_requested = ckpt_requested = cb_requested = 1;
+    ckpt_requested = cb_requested = 1;
   }
 #ifdef M3_TC_TIMING
   long long tick_ = clock64();
@@ -170,6 +163,12 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
       const uint4* src = reinterpret_cast<const uint4*>(p.ckpt_h + ((size_t)bh * ntiles + k) * kN * kP);
 #pragma unroll
       for (int i = 0; i < 4; ++i) raw_h[i] = __ldg(src + tid + 256 * i);
+    } else {
+      // x and dy come through registers even here: a bulk tensor copy moves these tiles in 16-byte
+      // pieces, and the copy engine's piece rate, not memory, then sets when the tile can start.  The
+      // rows were asked into L2 one tile ago, and the scaled copies are made from the same registers.
+      issue_px<R>(raw_x, p.x, tok0, Hs, T, t0);
+      issue_px<R>(raw_dy, p.dy, tok0, Hs, T, t0);
     }
     TICK(0);
     const TileScalars ts = scal_set(it & 1);  // filled during the previous tile's phase-B wait (or the prologue)
@@ -184,7 +183,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
     // ---- 2-3. operands ------------------------------------------------------------------------------
     if (TMA) {
       {
-        const bool ok = mbar_wait(&bars[4], it & 1) && mbar_wait(&bars[2], it & 1) && mbar_wait(&bars[3], it & 1);
+        const bool ok = mbar_wait(&bars[4], it & 1) && mbar_wait(&bars[3], it & 1);
         if (__syncthreads_or(!ok)) { failed = true; break; }
       }
       const int nv = T - t0;  // rows of this tile that exist; the box ran on into the next sequence
@@ -195,27 +194,14 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
           if (r >= nv) {
             *reinterpret_cast<uint4*>(sC + tile_off(r, 8 * g8, kN)) = z;
             *reinterpret_cast<uint4*>(sB + tile_off(r, 8 * g8, kN)) = z;
-            if (g8 < kP / 8) {
-              *reinterpret_cast<uint4*>(sX + tile_off(r, 8 * g8, kP)) = z;
-              *reinterpret_cast<uint4*>(sDY + tile_off(r, 8 * g8, kP)) = z;
-            }
           }
         }
-        __syncthreads();
       }
-      // the scaled copies sigma_w X~ and exp(acum) dY~
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int q = tid + 256 * i;  // 16-byte chunk of a [128 x 64] tile: [r/8][c/8][r%8]
-        const int r = (q >> 6) * 8 + (q & 7);
-        float v[8], u[8];
-        load_chunk(sX, (uint32_t)q * 16u, v);
-        load_chunk(sDY, (uint32_t)q * 16u, u);
-        const float sw = ts.sw[r], ea = ts.eac[r];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { v[j] *= sw; u[j] *= ea; }
-        store_chunk(sXw, (uint32_t)q * 16u, v);
-        store_chunk(sDYe, (uint32_t)q * 16u, u);
+      commit_px<R>(raw_x, sX, sXw, ts.sw);      // with the scaled copies sigma_w X~ and exp(acum) dY~
+      commit_px<R>(raw_dy, sDY, sDYe, ts.eac);
+      if (k > 0) {  // the next tile's x (threads 0-127) and dy rows, one 128-byte line each, into L2
+        const __nv_bfloat16* g = (tid < 128) ? p.x : p.dy;
+        prefetch_l2(g + (tok0 - (size_t)LT * Hs + (size_t)(tid & 127) * Hs) * kP);
       }
     } else {
       commit_bc<R, ROT>(raw_bc, sB, sC, sPhi);
@@ -538,10 +524,8 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
       if (TMA && k > 0) {  // the next tile's rows arrive during the copy-out and the per-token scalars
         if (tid == 0) {
           if (!early_cb) request_cb(k - 1);
-          request_xdy(k - 1);
         }
         if (!early_cb) ++cb_requested;
-        ++rows_requested;
       }
       if (p.dx) copy_out<R, kP>(sHS, p.dx, tok0, Hs, T, t0);
       if (p.db) copy_out<R, kN>(sXw, p.db, tok0, Hs, T, t0);
@@ -729,7 +713,6 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
     // A wait gave up: bulk copies already requested still target this CTA's shared memory.  Give the
     // latest request of each kind one more bounded wait before the CTA lets go of it.
     if (cb_requested > 0) mbar_wait(&bars[4], (cb_requested - 1) & 1);
-    if (rows_requested > 0) mbar_wait(&bars[2], (rows_requested - 1) & 1);
     if (ckpt_requested > 0) mbar_wait(&bars[3], (ckpt_requested - 1) & 1);
   }
   tc_fence_before();
