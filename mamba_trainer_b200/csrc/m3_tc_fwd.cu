@@ -119,7 +119,8 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(const __grid_constant__ 
     }
     tmem_wait_st();
   }
-  __syncthreads();  // the bf16 seed is read by other threads (checkpoint copy, first product)
+  fence_async_smem();
+  __syncthreads();  // the bf16 seed is read by the checkpoint's bulk copy and the first product
 
   if (p.stagger > 0) {  // spread the CTAs' memory phases: a fixed, bounded delay per CTA group
     const long long until = clock64() + (long long)(blockIdx.x & 3) * p.stagger;
@@ -193,10 +194,11 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(const __grid_constant__ 
     }
     // ---- 1. the tile's raw inputs were put in flight one tile ago -----------------------------
     if (p.ckpt_h) {  // the bf16 state entering this tile, for the backward pass
-      const uint4* src = reinterpret_cast<const uint4*>(sH);
-      uint4* dst = reinterpret_cast<uint4*>(p.ckpt_h + ((size_t)bh * ntiles + k) * kN * kP);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) dst[tid + 256 * i] = src[tid + 256 * i];
+      // one contiguous 16 KB bulk copy, in flight until the state's bf16 copy is refreshed in step 7
+      if (tid == 0) {
+        bulk_store(p.ckpt_h + ((size_t)bh * ntiles + k) * kN * kP, sH, kN * kP * 2);
+        bulk_commit();
+      }
     }
     TICK(1);
     TICK(2);
@@ -220,18 +222,6 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(const __grid_constant__ 
         }
         __syncthreads();
       }
-      // sigma_w X~: the scaled copy of x for the state update
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int q = tid + 256 * i;  // 16-byte chunk of the [128 x 64] tile: [r/8][c/8][r%8]
-        const int r = (q >> 6) * 8 + (q & 7);
-        float v[8];
-        load_chunk(sX, (uint32_t)q * 16u, v);
-        const float sw = ts.sw[r];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] *= sw;
-        store_chunk(sXw, (uint32_t)q * 16u, v);
-      }
     } else {
       commit_bc<R, ROT>(raw_bc, sB, sC, sPhi);
       commit_px<R>(raw_x, sX, sXw, ts.sw);
@@ -247,6 +237,21 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(const __grid_constant__ 
       gemm_issue(tm + TM_Y, aC, k_major(smem_u32(sH), kN), make_idesc(64, 0, 0), kN, false);
       gemm_issue(tm + TM_G, aC, k_major(smem_u32(sB), kN), make_idesc(128, 0, 0), kN, false);
       umma_commit(&bars[0]);
+    }
+    if (TMA) {
+      // sigma_w X~, the scaled copy of x for the state update, is first needed by the second pair of
+      // products: it is made while the first pair runs
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int q = tid + 256 * i;  // 16-byte chunk of the [128 x 64] tile: [r/8][c/8][r%8]
+        const int r = (q >> 6) * 8 + (q & 7);
+        float v[8];
+        load_chunk(sX, (uint32_t)q * 16u, v);
+        const float sw = ts.sw[r];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] *= sw;
+        store_chunk(sXw, (uint32_t)q * 16u, v);
+      }
     }
     if (k + 1 < ntiles) {  // next tile's loads: in flight during both products and epilogues
       if (!TMA) {
@@ -354,6 +359,7 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(const __grid_constant__ 
       umma_commit(&bars[1]);
     }
     if (k + 1 < ntiles) prepare_angles(k + 1);  // while Y and the state update are being computed
+    if (p.ckpt_h && tid == 0) bulk_wait_read();   // the checkpoint has left the state's bf16 copy
     {
       const bool ok = mbar_wait(&bars[1], k & 1);
       if (__syncthreads_or(!ok)) { failed = true; break; }
@@ -412,7 +418,7 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(const __grid_constant__ 
     }
     __syncthreads();
     copy_out<R, kP>(sXw, p.y, tok0, Hs, T, t0);
-    if (TMA) fence_async_smem();  // this tile's writes to its operand set, before a bulk copy reuses it
+    fence_async_smem();  // this tile's writes to its operand set and to the state's bf16 copy, before bulk copies touch them
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -424,6 +430,7 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(const __grid_constant__ 
     // Give each of them one more bounded wait before the CTA lets go of it.
     for (int kk = requested > 2 ? requested - 2 : 0; kk < requested; ++kk) mbar_wait(&bars[2 + (kk & 1)], (kk >> 1) & 1);
   }
+  if (tid == 0) bulk_wait_all();  // a checkpoint copy may still be reading this CTA's shared memory
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, TM_COLS);
