@@ -229,6 +229,9 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
       gemm_issue(tm + TM_T1, k_major(smem_u32(sDY), kP), mn_major(smem_u32(sHS), kN), make_idesc(128, 0, 1), kP, false);
       umma_commit(&bars[0]);
     }
+    // Without a rotation nothing reuses dG's buffer before the next band epilogue, so the 32 KB of dC
+    // staged there by the previous tile leave now, while every warp would only wait for the products.
+    if (!ROT && it > 0 && p.dc) copy_out<R, kN>(sDG, p.dc, tok0 + (size_t)LT * Hs, Hs, T, t0 + LT);
     {
       const bool ok = mbar_wait(&bars[0], it & 1);
       if (__syncthreads_or(!ok)) { failed = true; break; }
@@ -529,7 +532,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
       }
       if (p.dx) copy_out<R, kP>(sHS, p.dx, tok0, Hs, T, t0);
       if (p.db) copy_out<R, kN>(sXw, p.db, tok0, Hs, T, t0);
-      if (p.dc) copy_out<R, kN>(sDG, p.dc, tok0, Hs, T, t0);
+      if (p.dc && (ROT || k == 0)) copy_out<R, kN>(sDG, p.dc, tok0, Hs, T, t0);
       TICK(15);
       if (TMA) fence_async_smem();  // dx was staged where the next checkpoint lands
       __syncthreads();
