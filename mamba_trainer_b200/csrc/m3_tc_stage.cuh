@@ -9,7 +9,7 @@
 namespace m3tc {
 
 constexpr int kP = 64, kN = 128, kNH = 64, kRows = 128;
-constexpr int kScal = 132;  // floats per per-token scalar array
+constexpr int kScal = 132;  // floats per per-token scalar array (a multiple of 4: 16-byte reads of runs of columns)
 constexpr float kInvTwoPi = 0.15915494309189535f, kTwoPiF = 6.283185307179586f;
 
 __device__ __forceinline__ float bf(const __nv_bfloat16* p, size_t i) { return __bfloat162float(p[i]); }
@@ -383,9 +383,19 @@ struct ColScalars {
 };
 template <int R>
 __device__ __forceinline__ void load_col_scalars(ColScalars<R>& c, const TileScalars& ts, int c0) {
+  // s0 is a multiple of NS (4, 8 or 16) and every scalar array starts on a 16-byte boundary (kScal is
+  // a multiple of 4): 16-byte broadcast reads, a quarter of the instructions of scalar ones
   const int s0 = c0 / R;
+  const float4* qc = reinterpret_cast<const float4*>(ts.cf + s0);
+  const float4* qw = reinterpret_cast<const float4*>(ts.w + s0);
+  const float4* qg = reinterpret_cast<const float4*>(ts.g + s0);
 #pragma unroll
-  for (int i = 0; i < ColScalars<R>::NS; ++i) { c.cf[i] = ts.cf[s0 + i]; c.w[i] = ts.w[s0 + i]; c.g[i] = ts.g[s0 + i]; }
+  for (int i = 0; i < ColScalars<R>::NS / 4; ++i) {
+    const float4 a = qc[i], b = qw[i], d = qg[i];
+    c.cf[4 * i] = a.x; c.cf[4 * i + 1] = a.y; c.cf[4 * i + 2] = a.z; c.cf[4 * i + 3] = a.w;
+    c.w[4 * i] = b.x; c.w[4 * i + 1] = b.y; c.w[4 * i + 2] = b.z; c.w[4 * i + 3] = b.w;
+    c.g[4 * i] = d.x; c.g[4 * i + 1] = d.y; c.g[4 * i + 2] = d.z; c.g[4 * i + 3] = d.w;
+  }
 }
 
 // ---------------------------------------------------------------------------------------
