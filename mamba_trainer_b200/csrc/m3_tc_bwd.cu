@@ -281,17 +281,24 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
           // A chunk whose last step precedes the first row of this warp lies strictly below the
           // diagonal for all 32 rows (the case of most chunks of the lower rows): no selects needed.
           if (s0 + 16 / R - 1 < (quad * 32) / R) {
+            // two columns per instruction (packed fp32 pairs): the epilogues are bound by instruction issue
+            const float2 rf2 = make_float2(rf, rf);
+            float2 rowE2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int si = j / R;
-              const float dec = rf * cs.cf[si];
-              const float wgt = cs.w[si] * dec;
-              const float d_ = dm[j] * (g[j] * dec);
-              mv[j] = g[j] * wgt;
-              dgv[j] = dm[j] * wgt;
-              rowE = fmaf(d_, cs.w[si], rowE);
-              dbd[16 * hb + j] = d_;
+            for (int j = 0; j < 16; j += 2) {
+              const int sa = j / R, sb = (j + 1) / R;
+              const float2 w2 = make_float2(cs.w[sa], cs.w[sb]);
+              const float2 dec = __fmul2_rn(rf2, make_float2(cs.cf[sa], cs.cf[sb]));
+              const float2 wgt = __fmul2_rn(w2, dec);
+              const float2 g2 = make_float2(g[j], g[j + 1]), dm2 = make_float2(dm[j], dm[j + 1]);
+              const float2 d2 = __fmul2_rn(dm2, __fmul2_rn(g2, dec));
+              const float2 m2 = __fmul2_rn(g2, wgt), dg2 = __fmul2_rn(dm2, wgt);
+              rowE2 = __ffma2_rn(d2, w2, rowE2);
+              mv[j] = m2.x; mv[j + 1] = m2.y;
+              dgv[j] = dg2.x; dgv[j + 1] = dg2.y;
+              dbd[16 * hb + j] = d2.x; dbd[16 * hb + j + 1] = d2.y;
             }
+            rowE += rowE2.x + rowE2.y;
           } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {  // branch-free selects: below / on / above the diagonal

@@ -317,10 +317,13 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(const __grid_constant__ 
           if (s0 + 16 / R - 1 < (quad * 32) / R) {
             // strictly below the diagonal for all 32 rows of this warp: the weight needs no selects and,
             // for one rank, is shared by every row up to the row factor
+            const float2 rf2 = make_float2(rf, rf);  // two columns per instruction (packed fp32 pairs)
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int si = j / R;
-              m[j] = g[cc][j] * (cs.w[si] * cs.cf[si] * rf);
+            for (int j = 0; j < 16; j += 2) {
+              const int sa = j / R, sb = (j + 1) / R;
+              const float2 wc = __fmul2_rn(make_float2(cs.w[sa], cs.w[sb]), make_float2(cs.cf[sa], cs.cf[sb]));
+              const float2 m2 = __fmul2_rn(make_float2(g[cc][j], g[cc][j + 1]), __fmul2_rn(wc, rf2));
+              m[j] = m2.x; m[j + 1] = m2.y;
             }
           } else {
 #pragma unroll
