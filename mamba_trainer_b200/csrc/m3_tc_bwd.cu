@@ -342,7 +342,8 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) tmem_ld_fence(dhv[cc]);
       const float eac = ts.eac[rl];
-      float dot = 0.0f;
+      const float2 eac2 = make_float2(eac, eac);
+      float2 dot2 = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
         const int n0 = 64 * ch + 16 * cc;
@@ -350,12 +351,18 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
         load_chunk(sC, tile_off(row, n0, kN), c1);
         load_chunk(sC, tile_off(row, n0 + 8, kN), c2);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { dot += t1[cc][j] * c1[j] + t1[cc][8 + j] * c2[j]; }
+        for (int j = 0; j < 8; j += 2) {
+          dot2 = __ffma2_rn(make_float2(t1[cc][j], t1[cc][j + 1]), make_float2(c1[j], c1[j + 1]), dot2);
+          dot2 = __ffma2_rn(make_float2(t1[cc][8 + j], t1[cc][9 + j]), make_float2(c2[j], c2[j + 1]), dot2);
+        }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) t1[cc][j] *= eac;
+        for (int j = 0; j < 16; j += 2) {
+          const float2 v = __fmul2_rn(make_float2(t1[cc][j], t1[cc][j + 1]), eac2);
+          t1[cc][j] = v.x; t1[cc][j + 1] = v.y;
+        }
         tmem_st16(tmem_addr(tm, quad * 32, TM_T1 + n0), t1[cc]);
       }
-      part_t1[ch * 128 + row] = dot;
+      part_t1[ch * 128 + row] = dot2.x + dot2.y;
       // state gradient: lanes are n, columns p
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
@@ -367,7 +374,10 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
           *slot = __float2bfloat16_rn(dhv[cc][j]);           // dS_k replaces H_k
         }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) dhv[cc][j] *= ecd;
+        for (int j = 0; j < 16; j += 2) {
+          const float2 v = __fmul2_rn(make_float2(dhv[cc][j], dhv[cc][j + 1]), make_float2(ecd, ecd));
+          dhv[cc][j] = v.x; dhv[cc][j + 1] = v.y;
+        }
         tmem_st16(tmem_addr(tm, quad * 32, TM_DH + p0), dhv[cc]);
       }
     }
@@ -437,7 +447,8 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
     float dD_part = 0.0f;
     {  // dx = M^T dY~ + sw (B^ dS^T) + D dy ; q = <U, x>
       const float sw = ts.sw[rl];
-      float qp = 0.0f;
+      const float2 sw2 = make_float2(sw, sw), dsk2 = make_float2(dsk, dsk);
+      float2 qp2 = make_float2(0.0f, 0.0f), dD2 = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int p0 = 32 * ch + 16 * cc;
@@ -447,10 +458,13 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
         load_chunk(sDY, tile_off(row, p0, kP), *reinterpret_cast<float(*)[8]>(&dyv[0]));
         load_chunk(sDY, tile_off(row, p0 + 8, kP), *reinterpret_cast<float(*)[8]>(&dyv[8]));
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          qp += u[cc][j] * xv[j];
-          dD_part += dyv[j] * xv[j];
-          acc[cc][j] += sw * u[cc][j] + dsk * dyv[j];
+        for (int j = 0; j < 16; j += 2) {
+          const float2 u2 = make_float2(u[cc][j], u[cc][j + 1]), x2 = make_float2(xv[j], xv[j + 1]);
+          const float2 dy2 = make_float2(dyv[j], dyv[j + 1]);
+          qp2 = __ffma2_rn(u2, x2, qp2);
+          dD2 = __ffma2_rn(dy2, x2, dD2);
+          const float2 a2 = __ffma2_rn(sw2, u2, __ffma2_rn(dsk2, dy2, make_float2(acc[cc][j], acc[cc][j + 1])));
+          acc[cc][j] = a2.x; acc[cc][j + 1] = a2.y;
         }
         if (at_end && p.dlu) {  // gradient through last_u = sum_r x (x) B^ at the final token
 #pragma unroll 1
@@ -468,7 +482,8 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
         }
         stage_store16<kP>(sHS, row, p0, acc[cc]);  // dS is spent: its buffer stages dx
       }
-      part_q[ch * 128 + row] = qp;
+      part_q[ch * 128 + row] = qp2.x + qp2.y;
+      dD_part = dD2.x + dD2.y;
     }
     TICK(7);
     {  // dB^ (TM_DB, operand sB, out db) then dC^ (TM_T1, operand sC, out dc)

@@ -297,7 +297,12 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(const __grid_constant__ 
       for (int cc = 0; cc < 2; ++cc) {
         const int p0 = 32 * ch + 16 * cc;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) { yv[cc][j] *= eac; hv[cc][j] *= ecd; }
+        for (int j = 0; j < 16; j += 2) {  // packed fp32 pairs
+          const float2 y2 = __fmul2_rn(make_float2(yv[cc][j], yv[cc][j + 1]), make_float2(eac, eac));
+          const float2 h2 = __fmul2_rn(make_float2(hv[cc][j], hv[cc][j + 1]), make_float2(ecd, ecd));
+          yv[cc][j] = y2.x; yv[cc][j + 1] = y2.y;
+          hv[cc][j] = h2.x; hv[cc][j + 1] = h2.y;
+        }
         tmem_st16(tmem_addr(tm, quad * 32, TM_Y + p0), yv[cc]);
         tmem_st16(tmem_addr(tm, quad * 32, TM_H + p0), hv[cc]);
       }
@@ -390,7 +395,11 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_kernel(const __grid_constant__ 
             float xv[8];
             load_chunk(sX, tile_off(row, p0 + 8 * hh, kP), xv);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[8 * hh + j] += dsk * xv[j];
+            for (int j = 0; j < 8; j += 2) {
+              const float2 a2 = __ffma2_rn(make_float2(dsk, dsk), make_float2(xv[j], xv[j + 1]),
+                                           make_float2(v[8 * hh + j], v[8 * hh + j + 1]));
+              v[8 * hh + j] = a2.x; v[8 * hh + j + 1] = a2.y;
+            }
           }
         }
         stage_store16<kP>(sXw, row, p0, v);  // sigma_w X~ is spent: its buffer stages y
