@@ -149,6 +149,23 @@ __device__ __forceinline__ typename Vec<T, V>::raw_t load_x(const ConvDims& d, c
 
 // The kernels are compiled for KT in {2, 4, 8} taps; a K-tap convolution runs as the KT-tap one
 // whose first KT-K taps are zero, so every loop over taps is static.
+// acc[i] += a[i] * b[i] over a thread's V channels, two channels per instruction (packed fp32 pairs) when
+// V is even: these kernels are bound by instruction issue.
+template <int V>
+__device__ __forceinline__ void fma_vec(const float (&a)[V], const float (&b)[V], float (&acc)[V]) {
+  if constexpr (V % 2 == 0) {
+#pragma unroll
+    for (int i = 0; i < V; i += 2) {
+      const float2 r = __ffma2_rn(make_float2(a[i], a[i + 1]), make_float2(b[i], b[i + 1]), make_float2(acc[i], acc[i + 1]));
+      acc[i] = r.x;
+      acc[i + 1] = r.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = fmaf(a[i], b[i], acc[i]);
+  }
+}
+
 template <class T, int V, int KT>
 __global__ void __launch_bounds__(kLanesT* kLanesC)
     k_conv_fwd(ConvDims d, const T* __restrict__ x, const T* __restrict__ hist, const float* __restrict__ w,
@@ -187,9 +204,7 @@ __global__ void __launch_bounds__(kLanesT* kLanesC)
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = bs[i];
 #pragma unroll
-    for (int k = 0; k < KT; ++k)
-#pragma unroll
-      for (int i = 0; i < V; ++i) acc[i] = fmaf(wt[k][i], win[k][i], acc[i]);
+    for (int k = 0; k < KT; ++k) fma_vec<V>(wt[k], win[k], acc);
     if (d.act) {
 #pragma unroll
       for (int i = 0; i < V; ++i) acc[i] = silu(acc[i]);
@@ -279,17 +294,16 @@ __global__ void __launch_bounds__(kLanesT* kLanesC, 2)
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = bs[i];
 #pragma unroll
-        for (int k = 0; k < KT; ++k)
-#pragma unroll
-          for (int i = 0; i < V; ++i) acc[i] = fmaf(wt[k][i], win[k][i], acc[i]);
+        for (int k = 0; k < KT; ++k) fma_vec<V>(wt[k], win[k], acc);
 #pragma unroll
         for (int i = 0; i < V; ++i) gw[KT - 1][i] = valid ? (d.act ? gy[i] * silu_grad(acc[i]) : gy[i]) : 0.0f;
+        float og[V];
 #pragma unroll
-        for (int k = 0; k < KT; ++k)
+        for (int i = 0; i < V; ++i) og[i] = own * gw[KT - 1][i];
 #pragma unroll
-          for (int i = 0; i < V; ++i) pw[k][i] = fmaf(own * gw[KT - 1][i], win[k][i], pw[k][i]);
+        for (int k = 0; k < KT; ++k) fma_vec<V>(og, win[k], pw[k]);
 #pragma unroll
-        for (int i = 0; i < V; ++i) pb[i] = fmaf(own, gw[KT - 1][i], pb[i]);
+        for (int i = 0; i < V; ++i) pb[i] += og[i];
       }
       const int te = s - (KT - 1);  // dx[te] = sum_delay w[KT-1-delay] g[te+delay] = sum_j w[KT-1-j] gw[j]
       if (te >= emit_from && te < t1) {
@@ -297,9 +311,7 @@ __global__ void __launch_bounds__(kLanesT* kLanesC, 2)
 #pragma unroll
         for (int i = 0; i < V; ++i) o[i] = 0.0f;
 #pragma unroll
-        for (int j = 0; j < KT; ++j)
-#pragma unroll
-          for (int i = 0; i < V; ++i) o[i] = fmaf(wt[KT - 1 - j][i], gw[j][i], o[i]);
+        for (int j = 0; j < KT; ++j) fma_vec<V>(wt[KT - 1 - j], gw[j], o);
         if (te >= 0) {
           if (dx) Vec<T, V>::store(dx + ((size_t)b * d.T + at_time(d, rev, te)) * d.xs + c0, o);
         } else {
