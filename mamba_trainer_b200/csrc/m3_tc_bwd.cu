@@ -399,6 +399,8 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
       gemm_issue(tm + TM_DH, mn_major(aC, kN), mn_major(smem_u32(sDYe), kP), make_idesc(64, 1, 1), kRows, true);
       umma_commit(&bars[1]);
     }
+    RawTheta<R> th2;  // the tile's theta rows again (step 7), asked for now so that they arrive behind the products
+    if (ROT) issue_theta<R>(th2, p.theta, tok0, Hs, T, t0);
     if (k > 0) prepare_scalars(k - 1, (it + 1) & 1);  // while the five products run
     {
       const bool ok = mbar_wait(&bars[1], it & 1);
@@ -417,8 +419,6 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
     }
     // ---- 7. epilogue B -------------------------------------------------------------------------
     if (ROT) {  // the angles again (their buffer held M in between)
-      RawTheta<R> th2;
-      issue_theta<R>(th2, p.theta, tok0, Hs, T, t0);
       commit_theta<R>(th2, sPhi);
       __syncthreads();
       tile_angles_smem<R, true>(sPhi, s_q, s_carry, ts.dt, T, t0, nullptr);  // (cos, sin) table this time
