@@ -28,7 +28,7 @@ from mamba_trainer_b200 import synthetic  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one tc_bwd_kernel launch, from the committed ncu
 # capture of this workload (bytes per launch; None where no capture was taken).
-NCU_TRAFFIC_BYTES = {"cfg1_siso_trapezoid_bf16": 266990336}
+NCU_TRAFFIC_BYTES = {"cfg1_siso_trapezoid_bf16": 267403520}
 
 METRIC = "mamba3_ssd_scan_fwd_bwd_throughput"
 UNIT = "Mtokens/s"
