@@ -117,10 +117,11 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.sm)}
 
 
-def cpu_oracle_throughput(w, budget_s: float = 20.0):
-    """Time the CPU oracle (fp32, forward + backward) on a bounded slice of the workload:
-    one batch row and as many heads as finish in the budget; the scan is independent
-    across batch and heads, so throughput in token-heads/s carries over."""
+def cpu_oracle_throughput(w, steps: int = 8, warmup: int = 1, budget_s: float = 20.0):
+    """Time the CPU oracle (fp32, forward + backward) on a bounded slice of the workload: one batch row
+    and two heads per step (the scan is independent across batch and heads, so throughput in
+    token-heads/s carries over).  `warmup` untimed steps (at most 3), then up to `steps` timed ones, cut
+    short when `budget_s` seconds are spent; the value is the mean over the timed steps."""
     from oracle import m3_oracle as O
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
@@ -129,33 +130,41 @@ def cpu_oracle_throughput(w, budget_s: float = 20.0):
     sw = w.scaled(batch=1, heads=heads, seq=seq)
     t = synthetic.make_inputs(sw, seed=0)
     names = [n for n in ("x", "b", "c", "dt", "a_log", "lam", "theta", "d_skip") if t.get(n) is not None]
-    best, reps, t_start = None, 0, time.perf_counter()
-    while reps < 4 and (reps < 2 or time.perf_counter() - t_start < budget_s):
+
+    def one():
         leaf = {n: t[n].float().requires_grad_(True) for n in names}
         t0 = time.perf_counter()
         y, _ = O.mamba3_scan(leaf["x"], leaf["b"], leaf["c"], leaf["dt"], leaf["a_log"], leaf["lam"],
                              leaf.get("theta"), leaf.get("d_skip"), None, sw.chunk, False)
         torch.autograd.grad((y * t["dy"].float()).sum(), [leaf[n] for n in names])
-        dt_ = time.perf_counter() - t0
-        if reps > 0:
-            best = dt_ if best is None else min(best, dt_)
-        reps += 1
-    tok_heads_per_s = sw.tokens * sw.heads / best
+        return time.perf_counter() - t0
+
+    warm = max(1, min(warmup, 3))
+    for _ in range(warm):
+        one()
+    times, t_start = [], time.perf_counter()
+    while len(times) < max(1, steps) and (not times or time.perf_counter() - t_start < budget_s):
+        times.append(one())
+    mean = sum(times) / len(times)
+    tok_heads_per_s = sw.tokens * sw.heads / mean
     value = tok_heads_per_s / w.heads / 1e6   # Mtokens/s of the full-head workload
-    sample = f"batch 1 x seq {seq} x {heads} of {w.heads} heads, fp32, best of {reps - 1} after 1 warm-up, scaled by heads"
+    sample = (f"batch 1 x seq {seq} x {heads} of {w.heads} heads per step, fp32, mean of {len(times)} steps after "
+              f"{warm} warm-up, scaled by heads")
     return value, cores, sample
 
 
 def run_reference(args, w, rank):
     if rank != 0:
         return
-    steps = max(1, args.steps)
-    value, cores, sample = cpu_oracle_throughput(w, budget_s=min(60.0, 6.0 * steps))
+    value, cores, sample = cpu_oracle_throughput(w, steps=args.steps, warmup=args.warmup, budget_s=120.0)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": w.tokens / (value * 1e6) * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": w.name},
+        "data": "synthetic",
+        "config": {"workload": w.name, "batch_per_gpu": w.batch, "seq_len": w.seq, "heads": w.heads,
+                   "head_dim": w.head_dim, "d_state": w.d_state, "rank": w.rank, "chunk": w.chunk,
+                   "call": "CPU oracle (fp32 restatement of the reference's scan) on a bounded sample per step"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -199,8 +208,8 @@ def mixer_core_leg(w, dev):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--config", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", type=int, default=0, help="0 auto, 1 generic, 2 tensor-core")
