@@ -141,8 +141,19 @@ int m3_ctx_create(int device, m3_ctx **out);
 int m3_ctx_destroy(m3_ctx *ctx);
 /* Run on a caller-owned cudaStream_t instead (NULL = the legacy default stream). */
 int m3_ctx_set_stream(m3_ctx *ctx, void *cuda_stream);
-/* Block until everything enqueued on the context has finished. */
+/* Block until everything enqueued on the context has finished.  Returns M3_ERR_TIMEOUT
+ * (and clears the condition) if a kernel's bounded wait gave up since the last report:
+ * every device-side wait of the library has an iteration limit, after which the kernel
+ * raises a flag and returns instead of spinning.  The flag lives in host memory mapped
+ * into the device, so m3_scan_forward / m3_scan_backward / m3_host_pipe_wait also look
+ * at it on entry, at no cost, and report a wait that gave up in an EARLIER call the same
+ * way (the reference has no counterpart: its kernels never wait on one another). */
 int m3_sync(m3_ctx *ctx);
+/* Iteration limit of those bounded waits for calls made through this context; 0 restores
+ * the default (2^18 polls of an mbarrier, far beyond any healthy wait).  Diagnostic: a
+ * limit of 1 makes the first wait of a tensor-core kernel give up, which is how the
+ * failure path is exercised without a fault.  No counterpart in the reference. */
+int m3_ctx_set_wait_limit(m3_ctx *ctx, uint32_t iterations);
 /* Message of the last failure on this context ("" if none).  Never NULL. */
 const char *m3_last_error(const m3_ctx *ctx);
 /* Kernels launched through this context so far (the reference's launch_count(),

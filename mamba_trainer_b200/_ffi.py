@@ -94,6 +94,7 @@ SYMBOLS = {
     "m3_ctx_destroy": (C.c_int, [C.c_void_p]),
     "m3_ctx_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
     "m3_sync": (C.c_int, [C.c_void_p]),
+    "m3_ctx_set_wait_limit": (C.c_int, [C.c_void_p, C.c_uint32]),
     "m3_last_error": (C.c_char_p, [C.c_void_p]),
     "m3_launch_count": (C.c_uint64, [C.c_void_p]),
     "m3_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),

@@ -17,6 +17,7 @@ struct m3_saved {
   m3::GenericWs gws;
   __nv_bfloat16* tc_ckpt_h = nullptr;  // tensor-core family: bf16 state entering each tile
   float* tc_ckpt_angle = nullptr;  // and the angle entering each tile
+  cudaStream_t stream = nullptr;   // the stream the forward ran on: the scratch is freed in its order
 };
 
 namespace m3 {
@@ -33,6 +34,12 @@ int fail(m3_ctx* ctx, int code, const char* fmt, ...) {
 
 int cuda_fail(m3_ctx* ctx, cudaError_t e, const char* what) {
   return fail(ctx, M3_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+int take_device_flag(m3_ctx* ctx, const char* when) {
+  if (!ctx->err_host || !*ctx->err_host) return M3_OK;
+  *ctx->err_host = 0;
+  return fail(ctx, M3_ERR_TIMEOUT, "a bounded device-side wait gave up (%s); results of the affected call are invalid", when);
 }
 
 }  // namespace m3
@@ -115,7 +122,7 @@ int tc_backward_call(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* i
   const size_t per_tok = BH * d.Tp, per_tile = BH * tiles;
   const size_t nfloat = 4 * per_tok + 2 * per_tile + BH;
   float* base = nullptr;
-  M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&base), nfloat * sizeof(float), ctx->stream));
+  M3_CUDA(ctx, m3::scratch_alloc(ctx, reinterpret_cast<void**>(&base), nfloat * sizeof(float), ctx->stream));
   m3::GenericBwdWs bw{};
   bw.da = base; bw.dg = base + per_tok; bw.dw = base + 2 * per_tok; bw.ddt_rot = base + 3 * per_tok;
   bw.partA = base + 4 * per_tok; bw.partD = bw.partA + per_tile; bw.ip0 = bw.partD + per_tile;
@@ -139,7 +146,7 @@ int tc_backward_call(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* i
   p.dangle0 = (d.rot && desc.angle0 && want(M3_GRAD_ANGLE0, g->dangle0)) ? g->dangle0 : nullptr;
   p.err = ctx->dev_err;
   p.B = d.B; p.T = d.T; p.H = d.H; p.R = d.R; p.disc = d.disc; p.rev = d.rev;
-  p.stagger = m3::tc_stagger_cycles(true);
+  p.wait_limit = ctx->wait_limit ? ctx->wait_limit : (1u << 18);
   static const bool tma_off = getenv("M3_TC_NO_TMA") != nullptr;
   p.use_tma = (!tma_off && d.R == 1 && !d.rot && d.rev == 0 && d.T % 8 == 0 && !(reinterpret_cast<uintptr_t>(p.ckpt_h) & 15) &&
                m3::tc_make_tile_map(&p.tm_b, p.b, d.B, d.T, d.H, 128) && m3::tc_make_tile_map(&p.tm_c, p.c, d.B, d.T, d.H, 128)) ? 1 : 0;
@@ -177,18 +184,31 @@ int m3_ctx_create(int device, m3_ctx** out) {
     return M3_ERR_CUDA;
   }
   ctx->own_stream = true;
-  if (cudaMalloc(reinterpret_cast<void**>(&ctx->dev_err), sizeof(int)) != cudaSuccess ||
-      cudaMemset(ctx->dev_err, 0, sizeof(int)) != cudaSuccess) {
+  int* flag = nullptr;
+  if (cudaHostAlloc(reinterpret_cast<void**>(&flag), sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+      cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->dev_err), flag, 0) != cudaSuccess) {
+    if (flag) cudaFreeHost(flag);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
     return M3_ERR_CUDA;
   }
-  // Keep freed scratch in the stream-ordered pool instead of returning it to the
-  // driver, so steady-state calls do not pay for allocation.
-  cudaMemPool_t pool;
-  if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+  *flag = 0;
+  ctx->err_host = flag;
+  // Scratch comes from a pool of this context's own, which keeps freed memory for the next call
+  // (steady-state calls then do not allocate) and gives it back when the context is destroyed; the
+  // device's default pool and its settings are left alone.  Where the driver refuses a pool, calls
+  // fall back to the default pool as it is.
+  cudaMemPoolProps props{};
+  props.allocType = cudaMemAllocationTypePinned;
+  props.handleTypes = cudaMemHandleTypeNone;
+  props.location.type = cudaMemLocationTypeDevice;
+  props.location.id = device;
+  if (cudaMemPoolCreate(&ctx->pool, &props) == cudaSuccess) {
     uint64_t keep = UINT64_MAX;
-    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    cudaMemPoolSetAttribute(ctx->pool, cudaMemPoolAttrReleaseThreshold, &keep);
+  } else {
+    ctx->pool = nullptr;
+    cudaGetLastError();
   }
   *out = ctx;
   return M3_OK;
@@ -201,7 +221,9 @@ int m3_ctx_destroy(m3_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     cudaStreamDestroy(ctx->stream);
   }
-  if (ctx->dev_err) cudaFree(ctx->dev_err);
+  cudaDeviceSynchronize();  // scratch freed on other streams (a saved handle's) must be back in the pool
+  if (ctx->pool) cudaMemPoolDestroy(ctx->pool);
+  if (ctx->err_host) cudaFreeHost(const_cast<int*>(ctx->err_host));
   delete ctx;
   return M3_OK;
 }
@@ -222,12 +244,12 @@ int m3_sync(m3_ctx* ctx) {
   if (!ctx) return M3_ERR_NULL;
   M3_CUDA(ctx, cudaSetDevice(ctx->device));
   M3_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  int flag = 0;
-  M3_CUDA(ctx, cudaMemcpy(&flag, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
-  if (flag) {
-    cudaMemset(ctx->dev_err, 0, sizeof(int));
-    return fail(ctx, M3_ERR_TIMEOUT, "a bounded device-side wait gave up; results of the affected call are invalid");
-  }
+  return m3::take_device_flag(ctx, "seen at m3_sync");
+}
+
+int m3_ctx_set_wait_limit(m3_ctx* ctx, uint32_t iterations) {
+  if (!ctx) return M3_ERR_NULL;
+  ctx->wait_limit = iterations;
   return M3_OK;
 }
 
@@ -288,8 +310,10 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
   if (saved) *saved = nullptr;
   if (!ctx) return M3_ERR_NULL;
   if (!desc || !out) return fail(ctx, M3_ERR_NULL, "descriptor and outputs are required");
+  int rc = m3::take_device_flag(ctx, "in an earlier call, seen on entry to m3_scan_forward");
+  if (rc != M3_OK) return rc;
   m3::Dims d;
-  int rc = make_dims(ctx, *desc, &d);
+  rc = make_dims(ctx, *desc, &d);
   if (rc != M3_OK) return rc;
   M3_CUDA(ctx, cudaSetDevice(ctx->device));
   const size_t PN = (size_t)d.P * d.N, BH = (size_t)d.B * d.H;
@@ -327,20 +351,29 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
     p.angle_out = (desc->want_state && d.rot) ? out->angle : nullptr;
     p.err = ctx->dev_err;
     p.B = d.B; p.T = d.T; p.H = d.H; p.R = d.R; p.disc = d.disc; p.rev = d.rev;
-    p.stagger = m3::tc_stagger_cycles(false);
+    p.wait_limit = ctx->wait_limit ? ctx->wait_limit : (1u << 18);
     // Rank 1 with real dynamics needs no conversion of its rows: bulk tensor copies land them in
     // operand layout (every head left to right, T a multiple of 8, 16-byte aligned tensors).
     static const bool tma_off = getenv("M3_TC_NO_TMA") != nullptr;
     p.use_tma = (!tma_off && d.R == 1 && !d.rot && d.rev == 0 && d.T % 8 == 0 &&
                  m3::tc_make_tile_map(&p.tm_b, p.b, d.B, d.T, d.H, 128) && m3::tc_make_tile_map(&p.tm_c, p.c, d.B, d.T, d.H, 128) &&
                  m3::tc_make_tile_map(&p.tm_x, p.x, d.B, d.T, d.H, 64)) ? 1 : 0;
+    if (!p.use_tma) {
+      // every other shape: the raw rows of b and c are fetched by bulk tensor copies, a tile at a time
+      const int steps = m3::tc_tile_steps(d.R);
+      if (!m3::tc_make_row_map(&p.tm_b, p.b, d.B, d.T, d.H, 128 * d.R, steps, true) ||
+          !m3::tc_make_row_map(&p.tm_c, p.c, d.B, d.T, d.H, 128 * d.R, steps, true))
+        return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family needs 16-byte aligned b and c");
+      if (d.rot && !m3::tc_make_row_map(&p.tm_th, p.theta, d.B, d.T, d.H, 64, steps, false))
+        return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family needs a 16-byte aligned theta");
+    }
     char* base = nullptr;
     size_t bytes = 0;
     if (saved) {  // the backward pass needs the state and the angle entering every tile
       const size_t tiles = (size_t)m3::tc_tiles(d.T, d.R);
       const size_t nh = BH * tiles * 128 * 64, na = BH * tiles * 64;
       bytes = nh * sizeof(__nv_bfloat16) + na * sizeof(float);
-      M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&base), bytes, ctx->stream));
+      M3_CUDA(ctx, m3::scratch_alloc(ctx, reinterpret_cast<void**>(&base), bytes, ctx->stream));
       p.ckpt_h = reinterpret_cast<__nv_bfloat16*>(base);
       p.ckpt_angle = reinterpret_cast<float*>(base + nh * sizeof(__nv_bfloat16));
     }
@@ -363,13 +396,14 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
       sv->ws_bytes = bytes;
       sv->tc_ckpt_h = p.ckpt_h;
       sv->tc_ckpt_angle = p.ckpt_angle;
+      sv->stream = ctx->stream;
       *saved = sv;
     }
     return M3_OK;
   }
   const size_t bytes = m3::generic_ws_layout(d, nullptr, nullptr);
   char* base = nullptr;
-  M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&base), bytes, ctx->stream));
+  M3_CUDA(ctx, m3::scratch_alloc(ctx, reinterpret_cast<void**>(&base), bytes, ctx->stream));
   m3::GenericWs ws;
   m3::generic_ws_layout(d, &ws, base);
   cudaError_t e = m3::generic_forward(ctx->stream, d, *desc, *out, ws, &ctx->launches);
@@ -389,6 +423,7 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
     sv->ws_base = base;
     sv->ws_bytes = bytes;
     sv->gws = ws;
+    sv->stream = ctx->stream;
     *saved = sv;
   } else {
     M3_CUDA(ctx, cudaFreeAsync(base, ctx->stream));
@@ -401,12 +436,16 @@ int m3_scan_backward(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* i
   if (!ctx) return M3_ERR_NULL;
   if (!saved || !in || !grads) return fail(ctx, M3_ERR_NULL, "saved context, upstream gradients and outputs are required");
   if (!in->dy) return fail(ctx, M3_ERR_NULL, "dy is required");
+  {
+    const int rc = m3::take_device_flag(ctx, "in an earlier call, seen on entry to m3_scan_backward");
+    if (rc != M3_OK) return rc;
+  }
   M3_CUDA(ctx, cudaSetDevice(ctx->device));
   if (saved->path == M3_PATH_TENSOR) return tc_backward_call(ctx, saved, in, grad_mask, grads);
   const m3::Dims& d = saved->dims;
   const size_t bytes = m3::generic_bwd_ws_layout(d, nullptr, nullptr);
   char* base = nullptr;
-  M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&base), bytes, ctx->stream));
+  M3_CUDA(ctx, m3::scratch_alloc(ctx, reinterpret_cast<void**>(&base), bytes, ctx->stream));
   m3::GenericBwdWs bw;
   m3::generic_bwd_ws_layout(d, &bw, base);
   cudaError_t e = m3::generic_backward(ctx->stream, d, saved->desc, saved->gws, bw, *in, grad_mask, *grads,
@@ -421,7 +460,10 @@ int m3_saved_free(m3_ctx* ctx, m3_saved* saved) {
   if (!ctx) return M3_ERR_NULL;
   if (!saved) return M3_OK;
   cudaSetDevice(ctx->device);
-  cudaError_t e = saved->ws_base ? cudaFreeAsync(saved->ws_base, ctx->stream) : cudaSuccess;
+  // Freed in the order of the stream the forward (and, by the tape's order, the backward) ran on: the
+  // context may have been rebound to another stream since, and the pool must not hand this block
+  // to a later allocation while kernels of the old stream still read it.
+  cudaError_t e = saved->ws_base ? cudaFreeAsync(saved->ws_base, saved->stream ? saved->stream : ctx->stream) : cudaSuccess;
   delete saved;
   if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFreeAsync");
   return M3_OK;

@@ -477,7 +477,7 @@ int m3_conv_backward(m3_ctx* ctx, const m3_conv_desc* c, const void* dy, void* d
   const int nblk = d.B * ((d.T + kLanesT * kRunBwd - 1) / (kLanesT * kRunBwd));
   float* part = nullptr;
   if (want_par)
-    M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&part), (size_t)nblk * (d.K + 1) * d.C * sizeof(float), ctx->stream));
+    M3_CUDA(ctx, m3::scratch_alloc(ctx, reinterpret_cast<void**>(&part), (size_t)nblk * (d.K + 1) * d.C * sizeof(float), ctx->stream));
   dim3 grid;
   cudaError_t e;
   if (c->dtype == M3_BF16) {

@@ -59,7 +59,6 @@ struct m3_host_pipe {
   cudaEvent_t sums_ready = nullptr, sums_out = nullptr;
   bool sums_used = false;
   cudaEvent_t ticket[kTickets] = {};
-  int* flag_host = nullptr;  // [kTickets] page-locked copies of the context's device error flag
   uint64_t runs = 0, slices_done = 0;
 };
 
@@ -88,7 +87,6 @@ int free_pipe(m3_host_pipe* p) {
     if (e) cudaEventDestroy(e);
   if (p->s_in) cudaStreamDestroy(p->s_in);
   if (p->s_out) cudaStreamDestroy(p->s_out);
-  if (p->flag_host) cudaFreeHost(p->flag_host);
   delete p;
   return M3_OK;
 }
@@ -137,8 +135,6 @@ int build_pipe(m3_host_pipe* p) {
   M3_CUDA(ctx, cudaEventCreateWithFlags(&p->sums_ready, cudaEventDisableTiming));
   M3_CUDA(ctx, cudaEventCreateWithFlags(&p->sums_out, cudaEventDisableTiming));
   for (cudaEvent_t& e : p->ticket) M3_CUDA(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-  M3_CUDA(ctx, cudaHostAlloc(reinterpret_cast<void**>(&p->flag_host), kTickets * sizeof(int), cudaHostAllocDefault));
-  for (int i = 0; i < kTickets; ++i) p->flag_host[i] = 0;
   return M3_OK;
 }
 
@@ -279,7 +275,6 @@ int m3_host_pipe_run(m3_host_pipe* p, const m3_host_in* in, const m3_host_out* o
     M3_CUDA(ctx, cudaMemcpyAsync(out->dd_skip, p->sum_dskip, s.heads * sizeof(float), cudaMemcpyDeviceToHost, p->s_out));
   M3_CUDA(ctx, cudaEventRecord(p->sums_out, p->s_out));
   p->sums_used = true;
-  M3_CUDA(ctx, cudaMemcpyAsync(&p->flag_host[p->runs % kTickets], ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost, p->s_out));
   M3_CUDA(ctx, cudaEventRecord(p->ticket[p->runs % kTickets], p->s_out));
   if (ticket) *ticket = p->runs;
   ++p->runs;
@@ -293,10 +288,9 @@ int m3_host_pipe_wait(m3_host_pipe* p, uint64_t ticket) {
   M3_CUDA(ctx, cudaSetDevice(ctx->device));
   // A slot reused by a later run waits for that later run, which finishes after this one.
   M3_CUDA(ctx, cudaEventSynchronize(p->ticket[ticket % kTickets]));
-  if (p->flag_host[ticket % kTickets]) {
-    p->flag_host[ticket % kTickets] = 0;
-    cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), p->s_out);
-    return m3::fail(ctx, M3_ERR_TIMEOUT, "a bounded device-side wait gave up; results of the affected run are invalid");
+  {
+    const int rc = m3::take_device_flag(ctx, "in a run of the host pipeline that has finished by now");
+    if (rc != M3_OK) return rc;
   }
   return M3_OK;
 }

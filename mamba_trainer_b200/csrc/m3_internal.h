@@ -13,9 +13,24 @@ struct m3_ctx {
   cudaStream_t stream = nullptr;
   bool own_stream = false;
   uint64_t launches = 0;
-  int* dev_err = nullptr;  // device flag raised by a kernel whose bounded wait gave up
+  // Flag raised by a kernel whose bounded wait gave up.  One int of page-locked host memory mapped
+  // into the device's address space: kernels store through `dev_err`, the host reads `err_host`
+  // without a copy - at m3_sync and on entry to every scan call.
+  int* dev_err = nullptr;
+  volatile int* err_host = nullptr;
+  uint32_t wait_limit = 0;          // iteration limit of the kernels' bounded waits; 0 = the default
+  cudaMemPool_t pool = nullptr;     // this context's own scratch pool (freed memory is kept for reuse)
   char err[512] = {0};
 };
+
+namespace m3 {
+// Scratch for a call, from the context's own stream-ordered pool, ordered on `st`.
+inline cudaError_t scratch_alloc(m3_ctx* ctx, void** out, size_t bytes, cudaStream_t st) {
+  return ctx->pool ? cudaMallocFromPoolAsync(out, bytes, ctx->pool, st) : cudaMallocAsync(out, bytes, st);
+}
+// Report (and clear) a wait that gave up in an earlier call; M3_OK if none did.
+int take_device_flag(m3_ctx* ctx, const char* when);
+}  // namespace m3
 
 namespace m3 {
 

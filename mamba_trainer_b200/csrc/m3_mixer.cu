@@ -532,7 +532,7 @@ int m3_bc_backward(m3_ctx* ctx, const m3_bc_desc* s, const void* db, const void*
   const size_t smem = (size_t)kBcWarps * width * sizeof(float);
   if (smem > 200 * 1024) return m3::fail(ctx, M3_ERR_UNSUPPORTED, "heads per group %d x d_state %d needs %zu bytes of shared memory", d.PG, d.N, smem);
   float* part = nullptr;
-  M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&part), (size_t)nblk_tok * d.G * width * sizeof(float), ctx->stream));
+  M3_CUDA(ctx, m3::scratch_alloc(ctx, reinterpret_cast<void**>(&part), (size_t)nblk_tok * d.G * width * sizeof(float), ctx->stream));
   const dim3 grid(nblk_tok, d.G);
   cudaError_t e = cudaSuccess;
   for (int which = 0; which < 2 && e == cudaSuccess; ++which) {
@@ -622,7 +622,7 @@ int m3_dt_lambda_backward(m3_ctx* ctx, const m3_act_desc* s, const void* ddt, co
   const int nruns = (ntok + kActRun - 1) / kActRun;
   float* part = nullptr;
   const bool want_bias = ddt_bias && s->dt_bias;
-  if (want_bias) M3_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void**>(&part), (size_t)nruns * s->heads * sizeof(float), ctx->stream));
+  if (want_bias) M3_CUDA(ctx, m3::scratch_alloc(ctx, reinterpret_cast<void**>(&part), (size_t)nruns * s->heads * sizeof(float), ctx->stream));
   const size_t nthreads = (size_t)nruns * s->heads;
   const unsigned grid = (unsigned)((nthreads + 127) / 128);
   if (s->dtype == M3_BF16) {

@@ -18,9 +18,6 @@ inline bool tc_supported(const m3_scan_desc& s) {
 inline int tc_tile_steps(int rank) { return 128 / rank; }
 inline int tc_tiles(int seq, int rank) { return (seq + tc_tile_steps(rank) - 1) / tc_tile_steps(rank); }
 
-// Start delay per CTA group in cycles (M3_TC_STAGGER overrides; 0 disables).
-int tc_stagger_cycles(bool backward);
-
 // A tensor map that lands a [128 tokens x cols] bf16 tile of a dense [B, T, H, cols] tensor directly in
 // the kernels' operand layout (8 x 8 core matrices tiled [rows/8][cols/8]): dimensions
 // (8 elements, 8 tokens, H*cols/8 column groups, B*T/8 token groups), box (8, 8, cols/8, 16), so the
@@ -29,8 +26,17 @@ int tc_stagger_cycles(bool backward);
 // register path).
 bool tc_make_tile_map(CUtensorMap* map, const void* base, int B, int T, int H, int cols);
 
+// A tensor map over the rows of a dense [B, T, H, cols] bf16 tensor as the caller stores them:
+// dimensions (cols, H, T, B), box (64, 1, steps, 1), so 64 columns of `steps` consecutive time steps of
+// one (batch, head) land as a dense [steps][128 bytes] panel (one request per 64 columns), rows past
+// either end of the sequence arriving as zeros.  With `swizzle` the 16-byte chunks of a panel row are
+// XOR-swizzled by row & 7 (the 128-byte swizzle; the panel must then start on a 1024-byte boundary).
+// cols a multiple of 64; needs a 16-byte aligned base.
+bool tc_make_row_map(CUtensorMap* map, const void* base, int B, int T, int H, int cols, int steps, bool swizzle);
+
 struct TcFwdParams {
-  alignas(64) CUtensorMap tm_b, tm_c, tm_x;   // valid when use_tma
+  alignas(64) CUtensorMap tm_b, tm_c, tm_x;   // tile maps of the direct form when use_tma, else row maps of b and c
+  alignas(64) CUtensorMap tm_th;              // row map of theta (rotational dynamics, role-split kernel)
   int use_tma;        // rank 1, real dynamics, T % 8 == 0, no right-to-left heads
   const __nv_bfloat16 *x, *b, *c, *dt, *lam, *theta;
   const float *a_log, *d_skip, *h0, *lu0, *angle0;
@@ -41,10 +47,12 @@ struct TcFwdParams {
   int* err;           // device flag set when a bounded wait gave up
   int B, T, H, R, disc;
   int rev;            // the last `rev` heads walk time right to left
-  int stagger;        // cycles of start delay per CTA group (blockIdx & 3), 0 = none
+  uint32_t wait_limit; // iteration limit of the bounded waits (m3_ctx_set_wait_limit)
 };
 
 cudaError_t tc_forward(cudaStream_t st, const TcFwdParams& p, bool rotational);
+// The direct form (rank 1, real dynamics, use_tma): m3_tc_fwd_direct.cu.
+cudaError_t tc_forward_direct(cudaStream_t st, const TcFwdParams& p);
 
 struct TcBwdParams {
   alignas(64) CUtensorMap tm_b, tm_c;   // valid when use_tma (as in TcFwdParams; x and dy go through registers)
@@ -62,7 +70,7 @@ struct TcBwdParams {
   int* err;
   int B, T, H, R, disc;
   int rev;            // the last `rev` heads walk time right to left
-  int stagger;
+  uint32_t wait_limit;
 };
 
 cudaError_t tc_backward(cudaStream_t st, const TcBwdParams& p, bool rotational);

@@ -110,10 +110,6 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
   }
   tmem_wait_st();
 
-  if (p.stagger > 0) {  // spread the CTAs' memory phases: a fixed, bounded delay per CTA group
-    const long long until = clock64() + (long long)(blockIdx.x & 3) * p.stagger;
-    while (clock64() < until) {}
-  }
   bool failed = false;
   float nx_dt, nx_lam;  // dt / lambda of the next tile to process, loaded one tile ahead
   load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, (ntiles - 1) * LT, rev);
@@ -733,7 +729,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
     const float tot = cta_sum(ip, s_red);
     if (tid == 0) p.ip0[bh] = tot;
   }
-  if (failed && tid == 0 && p.err) atomicExch(p.err, 1);
+  if (failed && tid == 0 && p.err) raise_flag(p.err);
   if (TMA && failed) {
     // A wait gave up: bulk copies already requested still target this CTA's shared memory.  Give the
     // latest request of each kind one more bounded wait before the CTA lets go of it.

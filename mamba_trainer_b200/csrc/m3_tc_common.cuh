@@ -86,9 +86,10 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 // Wait for a phase of an mbarrier with an iteration limit.  Returns false if it gave up;
 // the caller reports that through an error flag and leaves the kernel - it never spins
 // without bound.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+constexpr uint32_t kWaitLimit = 1u << 18;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = kWaitLimit) {
   const uint32_t a = smem_u32(bar);
-  for (int it = 0; it < (1 << 18); ++it) {
+  for (uint32_t it = 0; it < limit; ++it) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
@@ -98,6 +99,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (done) return true;
   }
   return false;
+}
+
+// Report a wait that gave up: the flag is one int of host memory mapped into this GPU's address
+// space (the host reads it without a copy), so a plain store and a system-wide fence.
+__device__ __forceinline__ void raise_flag(int* flag) {
+  *reinterpret_cast<volatile int*>(flag) = 1;
+  __threadfence_system();
 }
 
 // Bulk tensor copies (TMA) of this GPU's own memory into this CTA's shared memory, completion
@@ -111,6 +119,16 @@ __device__ __forceinline__ void tma_load_tile(void* dst, const void* tensor_map,
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
           smem_u32(dst)),
       "l"(tensor_map), "r"(smem_u32(bar)), "r"(0), "r"(0), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// One box of a row map (tc_make_row_map): columns from `col`, head h, time steps from t (may be negative
+// or run past the end: those rows arrive as zeros), batch b.
+__device__ __forceinline__ void tma_load_rows(void* dst, const void* tensor_map, uint64_t* bar, int col, int h, int t, int b) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(tensor_map), "r"(smem_u32(bar)), "r"(col), "r"(h), "r"(t), "r"(b)
       : "memory");
 }
 

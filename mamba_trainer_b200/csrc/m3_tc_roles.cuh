@@ -1,0 +1,289 @@
+// Warp roles of the tensor-core stripe kernels (384 threads per CTA):
+//   warps 0-7   epilogue warps: stage the operands of a tile, run the TMEM epilogues, write outputs;
+//   warp 8      issuer: every tcgen05.mma / tcgen05.commit of the CTA, and the state checkpoint's bulk
+//               copy, so that no epilogue warp is held by the tensor pipe while products are issued;
+//   warp 9      look-ahead warp: the per-token scalars of the NEXT tile (dt and lambda of the tile after
+//               that wait in its registers), while the epilogue warps work on this one;
+//   warp 10     copy warp: the bulk tensor copy requests of the next tile's raw rows.  A request holds
+//               its thread until the copy engine accepts it, and the engine is slow to drain while the
+//               tensor pipe and the epilogues keep shared memory busy (about 6.5 B per cycle measured
+//               inside these kernels against 25-40 alone), so no warp with other duties issues them;
+//   warp 11     idle.  It exists because a warp's registers come from its scheduler's file of 16 K (a
+//               ninth warp alone would be a third warp on scheduler 0 and cap every thread at 168) and
+//               because budgets move between warps only per group of four (setmaxnreg): warps 8-11 give
+//               registers back, the eight epilogue warps take them.
+// The groups meet at named barriers (one side arrives, the other syncs); every barrier operation is
+// executed unconditionally, tile after tile, so a warp that gave up a bounded wait keeps the protocol
+// alive and nobody is left waiting at a barrier.  The helpers' work is kept off every critical path by
+// a whole tile of lead time: a warp that runs a little code once per tile finds it evicted from the
+// instruction caches by the epilogues' long straight-line bodies (60-160 KB per kernel) and pays a fetch
+// from L2 for every cache line of it - 200 instructions took most of a tile period - whether it is a
+// helper warp or one epilogue warp taking a branch of its own (the scalars on an epilogue warp inside
+// the wait for the first products made every tile 2.4 K cycles longer).
+#pragma once
+#include "m3_tc_stage.cuh"
+
+namespace m3tc {
+
+constexpr int kEpiThreads = 256, kCtaThreads = 384, kPairCount = kEpiThreads + 32;
+constexpr int kIssuerWarp = 8, kScalarWarp = 9, kCopyWarp = 10;
+
+// Named barriers (0 is __syncthreads).
+enum : int {
+  BAR_EPI = 1,    // 256: the epilogue warps among themselves
+  BAR_OPS = 2,    // 320: operands of a tile are staged (epilogue warps arrive; issuer and copy warp sync)
+  BAR_MID = 3,    // 288: the second group of operands is staged (epilogue warps arrive; issuer syncs)
+  BAR_AHEAD = 4,  // 288: scalars of a tile are ready (look-ahead warp arrives; epilogue warps sync)
+  BAR_FREE = 5,   // 288: a set of scalars is free again (epilogue warps arrive; look-ahead warp syncs)
+  BAR_TAIL = 6,   // 288: a tile's outputs are staged / its buffers free (epilogue warps arrive; copy warp syncs)
+};
+
+
+__device__ __forceinline__ void bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(int id, int count) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void epi_sync() { bar_sync(BAR_EPI, kEpiThreads); }
+
+// Register budget per role (the CTA's 384 threads start with 168 each).
+__device__ __forceinline__ void regs_for_epilogue() { asm volatile("setmaxnreg.inc.sync.aligned.u32 232;"); }
+__device__ __forceinline__ void regs_for_helpers() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
+
+// true if every lane's wait succeeded (tcgen05.ld is warp-collective, so a warp gives up as one)
+__device__ __forceinline__ bool warp_all(bool ok) { return __all_sync(0xffffffffu, ok); }
+
+// ---------------------------------------------------------------------------------------
+// Per-token scalars of one tile, by ONE warp (the arithmetic of tile_scalars): g, w (shifted add),
+// a = dt A, inclusive cumulative sum ac, sw = exp(cd - ac) w, eac = exp(ac), column factors cf.
+// Lane i owns the EPL consecutive steps i*EPL .. i*EPL + EPL - 1.
+// ---------------------------------------------------------------------------------------
+template <int R>
+struct ScalarLoads {
+  static constexpr int EPL = (kRows / R) / 32;
+  float dt[EPL + 1], lam[EPL + 1];
+};
+// dt and lambda of the steps lane * EPL .. lane * EPL + EPL of the tile at t0 (one step of look-ahead),
+// requested a whole tile before they are used: the loads are few but each is a sector of its own.
+template <int R>
+__device__ __forceinline__ void lookahead_load(ScalarLoads<R>& v, const __nv_bfloat16* dt, const __nv_bfloat16* lam,
+                                               int disc, int b, int h, int H, int T, int t0, bool rev) {
+  constexpr int EPL = ScalarLoads<R>::EPL;
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int i = 0; i <= EPL; ++i) {
+    const int t = t0 + lane * EPL + i;
+    v.dt[i] = 0.0f;
+    v.lam[i] = 1.0f;
+    if (t < T) {
+      const size_t idx = ((size_t)b * T + (rev ? T - 1 - t : t)) * H + h;
+      v.dt[i] = bf(dt, idx);
+      v.lam[i] = disc == 0 ? 1.0f : (disc == 1 ? 0.5f : bf(lam, idx));
+    }
+  }
+}
+template <int R>
+__device__ __forceinline__ void lookahead_scalars(const TileScalars& s, const ScalarLoads<R>& v, float A, int T, int t0) {
+  constexpr int LT = kRows / R, EPL = LT / 32, SPC = 16 / R;
+  const int lane = threadIdx.x & 31;
+  float loc[EPL], wv[EPL];
+  float run = 0.0f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int l = lane * EPL + i, t = t0 + l;
+    float gv = 0.0f, w = 0.0f, av = 0.0f;
+    if (t < T) {
+      gv = v.lam[i] * v.dt[i];
+      const float f = (t + 1 < T) ? (1.0f - v.lam[i + 1]) * v.dt[i + 1] : 0.0f;
+      w = gv + f;
+      av = v.dt[i] * A;
+    }
+    s.dt[l] = v.dt[i]; s.lam[l] = v.lam[i]; s.g[l] = gv; s.w[l] = w; s.a[l] = av;
+    wv[i] = w;
+    run += av;
+    loc[i] = run;
+  }
+  if (lane == 31) { s.dt[LT] = v.dt[EPL]; s.lam[LT] = v.lam[EPL]; }
+  float tot = run;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float n = __shfl_up_sync(0xffffffffu, tot, o);
+    if (lane >= o) tot += n;
+  }
+  const float base = tot - run;
+  const float cd = __shfl_sync(0xffffffffu, tot, 31);
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    loc[i] += base;
+    s.ac[lane * EPL + i] = loc[i];
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int l = lane * EPL + i;
+    s.sw[l] = expc(cd - loc[i]) * wv[i];
+    s.eac[l] = expc(loc[i]);
+    s.cf[l] = __expf(fmaxf(s.ac[(l / SPC) * SPC + SPC - 1] - loc[i], -87.0f));
+  }
+}
+
+// Wrapped cumulative angle of one tile as a table of half2(cos phi, sin phi) words, [LT][64] at
+// phi_idx(l, m), by the 256 threads of the epilogue warps: thread (q, m) owns plane m over the quarter q
+// of the tile's steps.  The tile's raw theta rows ([LT][64] bf16, landed by a bulk tensor copy; for a head
+// that walks right to left in memory order, i.e. step l in row LT - 1 - l) sit at the start of the table's
+// own buffer and are consumed before any table word is written (one barrier separates the passes).
+// `carry` [64] holds the angle entering the tile and receives the wrapped angle leaving it; `s_q` is
+// [4][64] floats of exchange space; dt comes from the tile's scalars.  sin / cos come from the
+// special-function unit (the argument is wrapped into [-pi, pi] first, where its error is far below the
+// half-precision table's).  Contains two barriers of the epilogue warps; the caller's next one
+// publishes the table.
+template <int R>
+__device__ __forceinline__ void epi_angle_table(float* tab, float* s_q, float* carry, const float* s_dt, int T, int t0,
+                                                bool rev, float* ckpt_slot, float* angle_out_bh) {
+  constexpr int LT = kRows / R, LQ = LT / 4;
+  const __nv_bfloat16* raw = reinterpret_cast<const __nv_bfloat16*>(tab);
+  const int tid = threadIdx.x, q = tid >> 6, m = tid & 63;
+  float loc[LQ];
+  float run = 0.0f;
+#pragma unroll
+  for (int i = 0; i < LQ; ++i) {
+    const int l = q * LQ + i;
+    run = fmaf(s_dt[l], __bfloat162float(raw[(rev ? LT - 1 - l : l) * kNH + m]), run);
+    loc[i] = run;
+  }
+  s_q[q * 64 + m] = run;
+  const float cin = carry[m];
+  if (ckpt_slot && q == 0) ckpt_slot[m] = cin;
+  epi_sync();
+  float off = cin;
+  for (int qq = 0; qq < q; ++qq) off += s_q[qq * 64 + m];
+  if (q == 3) carry[m] = wrap2pi(off + run);
+#pragma unroll
+  for (int i = 0; i < LQ; ++i) {
+    const int l = q * LQ + i;
+    const float wv = wrap2pi(loc[i] + off);
+    const __half2 h2 = __floats2half2_rn(__cosf(wv), __sinf(wv));
+    tab[phi_idx(l, m)] = __uint_as_float(*reinterpret_cast<const uint32_t*>(&h2));
+    if (angle_out_bh && t0 + l == T - 1) angle_out_bh[m] = wv;
+  }
+}
+
+// (cos, sin) of the eight planes [m0, m0 + 8) of step l from the table (m0 a multiple of 8).
+__device__ __forceinline__ void table_cos_sin(const float* tab, int l, int m0, float (&cs)[8], float (&sn)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(&tab[phi_idx(l, m0)]);
+  const float4 b = *reinterpret_cast<const float4*>(&tab[phi_idx(l, m0 + 4)]);
+  const uint32_t w[8] = {__float_as_uint(a.x), __float_as_uint(a.y), __float_as_uint(a.z), __float_as_uint(a.w),
+                         __float_as_uint(b.x), __float_as_uint(b.y), __float_as_uint(b.z), __float_as_uint(b.w)};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+    cs[j] = f.x;
+    sn[j] = f.y;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Raw rows of a tile as the caller stores them, [step][col * R + r], landed by bulk tensor copies of a
+// row map (tc_make_row_map): panels of [LT][<= 256 elements], one per 256 columns.  Heads that walk right
+// to left receive the tile's time range in memory order, so scan step l sits in row LT - 1 - l.
+// Work items are the (step, 16-byte group) pairs of commit_bc.
+// ---------------------------------------------------------------------------------------
+template <int R>
+struct RawTile {
+  static constexpr int LT = kRows / R;
+  static constexpr uint32_t kPanelBytes = (uint32_t)LT * 128u;   // [LT][64 elements], 16-byte chunks XOR-swizzled by row & 7
+  static constexpr uint32_t panels(int cols) { return (uint32_t)(cols * R) / 64u; }
+  static constexpr uint32_t bytes(int cols) { return panels(cols) * kPanelBytes; }
+  // byte offset of the 16-byte piece holding elements [e, e + 8) of scan step l (e a multiple of 8)
+  static __device__ __forceinline__ uint32_t piece(int l, uint32_t e, bool rev) {
+    const uint32_t rowi = (uint32_t)(rev ? LT - 1 - l : l);
+    return (e >> 6) * kPanelBytes + rowi * 128u + ((((e >> 3) & 7u) ^ (rowi & 7u)) << 4);
+  }
+};
+// Requests for one tile's rows of one tensor, by the lanes [lane0, lane0 + panels) of a warp, one panel
+// each (a request occupies its thread for hundreds of cycles; side by side they cost one): first scan
+// step t0, head h, batch b.  `dst` is 1024-byte aligned (the swizzle pattern repeats every eight rows of
+// 128 bytes).  Returns the number of lanes used.
+template <int R>
+__device__ __forceinline__ int request_raw_tile(int lane0, uint8_t* dst, const void* map, uint64_t* bar, int cols, int b,
+                                                int h, int T, int t0, bool rev) {
+  using RT = RawTile<R>;
+  const int t = rev ? T - t0 - RT::LT : t0;
+  const int pn = (int)(threadIdx.x & 31) - lane0;
+  if (pn >= 0 && pn < (int)RT::panels(cols))
+    tma_load_rows(dst + (uint32_t)pn * RT::kPanelBytes, map, bar, pn * 64, h, t, b);
+  return (int)RT::panels(cols);
+}
+
+// R consecutive 16-byte pieces of a staged row, starting at element e, as 4 R words.
+template <int R>
+__device__ __forceinline__ void load_raw_pieces(const uint8_t* base, int l, uint32_t e, bool rev, uint32_t (&raw)[4 * R]) {
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const uint4 v = *reinterpret_cast<const uint4*>(base + RawTile<R>::piece(l, e + 8u * i, rev));
+    raw[4 * i] = v.x; raw[4 * i + 1] = v.y; raw[4 * i + 2] = v.z; raw[4 * i + 3] = v.w;
+  }
+}
+
+// The work items of a tile's conversion: (time step l, 16-byte column group grp) pairs, 4 steps x 8
+// groups per warp as in item_coords, with the bits of the group index permuted so that the two groups a
+// quarter warp touches lie 4 / R apart: its eight lanes (4 steps x 2 groups) then read eight different
+// 16-byte columns of the swizzled staging rows (a group is R pieces wide; the swizzle XORs the column
+// with step & 7).
+template <int GB, int R>
+__device__ __forceinline__ void convert_coords(int i, int& l, int& grp) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int w = warp + 8 * i;
+  constexpr int GB8 = GB / 2;
+  const int g3 = lane >> 2;
+  const int gp = R == 4 ? g3 : (R == 2 ? (((g3 & 1) << 1) | ((g3 >> 1) & 1) | (g3 & 4))
+                                       : (((g3 & 1) << 2) | (g3 & 2) | ((g3 >> 2) & 1)));
+  l = (w / GB8) * 4 + (lane & 3);
+  grp = (w % GB8) * 8 + gp;
+}
+
+// Staged raw rows -> rotated (by -phi, from the table), rank-de-interleaved bf16 operands B^, C^.
+template <int R, bool ROT>
+__device__ __forceinline__ void convert_bc(const uint8_t* rawB, const uint8_t* rawC, uint8_t* sB, uint8_t* sC,
+                                           const float* tab, bool rev) {
+  using RB = RawBC<R, ROT>;
+#pragma unroll
+  for (int i = 0; i < RB::NIT; ++i) {
+    int l, grp;
+    convert_coords<RB::GB, R>(i, l, grp);
+    const int n0 = grp * 8;
+    float cs[8], sn[8];
+    if (ROT) table_cos_sin(tab, l, n0, cs, sn);
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const uint8_t* src = which ? rawC : rawB;
+      uint8_t* dst = which ? sC : sB;
+      uint32_t v[RB::NP][4 * R];
+#pragma unroll
+      for (int part = 0; part < RB::NP; ++part)
+        load_raw_pieces<R>(src, l, (uint32_t)(n0 + part * kNH) * R, rev, v[part]);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        if (ROT) {
+          float o1[8], o2[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float v1 = elem(v[0], j * R + r), v2 = elem(v[RB::NP - 1], j * R + r);
+            o1[j] = v1 * cs[j] + v2 * sn[j];
+            o2[j] = v2 * cs[j] - v1 * sn[j];
+          }
+          store_chunk(dst, tile_off(l * R + r, n0, kN), o1);
+          store_chunk(dst, tile_off(l * R + r, n0 + kNH, kN), o2);
+        } else {
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = elem(v[0], j * R + r);
+          store_chunk(dst, tile_off(l * R + r, n0, kN), o);
+        }
+      }
+    }
+  }
+}
+
+}  // namespace m3tc

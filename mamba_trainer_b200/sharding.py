@@ -56,8 +56,17 @@ _PER_HEAD = ("a_log", "d_skip")                              # [H]
 _STATE = ("h0", "last_u0", "angle0")                         # [B, H, ...]
 
 
+def shard_reverse_heads(heads: int, reverse_heads: int, shard: Shard) -> int:
+    """How many of a shard's heads walk time right to left, when the last `reverse_heads` of all
+    `heads` do (the bidirectional scan): those of the shard's head range that fall in the reversed
+    tail, which is again a tail of the shard because head ranges are contiguous."""
+    first_reversed = heads - reverse_heads
+    return max(0, shard.heads.stop - max(shard.heads.start, first_reversed))
+
+
 def shard_inputs(t: Dict[str, Optional[torch.Tensor]], shard: Shard) -> Dict[str, Optional[torch.Tensor]]:
-    """This rank's contiguous copy of every scan input."""
+    """This rank's contiguous copy of every scan input.  A bidirectional scan passes
+    `shard_reverse_heads(...)` as the shard's own `reverse_heads`."""
     out = {}
     for k, v in t.items():
         if v is None:
@@ -74,15 +83,22 @@ def shard_inputs(t: Dict[str, Optional[torch.Tensor]], shard: Shard) -> Dict[str
 
 
 def gather_per_token(local: torch.Tensor, batch: int, heads: int, group=None) -> torch.Tensor:
-    """All-gather shards of a [B_s, T, H_s, ...] tensor back into [B, T, H, ...] (verification only)."""
+    """All-gather shards of a [B_s, T, H_s, ...] tensor back into [B, T, H, ...] (verification only).
+    The pieces travel as tensors on the device they live on - NCCL between GPUs, gloo between CPU
+    ranks - one broadcast-free `all_gather` of equally sized, padded pieces; a shard's own tensor is
+    the only memory any rank's kernels ever read."""
     import torch.distributed as dist
-    world, rank = dist.get_world_size(group), dist.get_rank(group)
-    pieces = [None] * world
-    dist.all_gather_object(pieces, local.cpu(), group=group)
-    full = torch.empty((batch, local.shape[1], heads) + tuple(local.shape[3:]), dtype=local.dtype)
-    for r, piece in enumerate(pieces):
-        s = shard_plan(batch, heads, world, r)
-        full[s.batch, :, s.heads] = piece
+    world = dist.get_world_size(group)
+    shards = [shard_plan(batch, heads, world, r) for r in range(world)]
+    nb, nh = max(s.n_batch for s in shards), max(s.n_heads for s in shards)
+    tail = tuple(local.shape[3:])
+    padded = torch.zeros((nb, local.shape[1], nh) + tail, dtype=local.dtype, device=local.device)
+    padded[:local.shape[0], :, :local.shape[2]] = local
+    pieces = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(pieces, padded, group=group)
+    full = torch.empty((batch, local.shape[1], heads) + tail, dtype=local.dtype, device=local.device)
+    for s, piece in zip(shards, pieces):
+        full[s.batch, :, s.heads] = piece[:s.n_batch, :, :s.n_heads]
     return full
 
 

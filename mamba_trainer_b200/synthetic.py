@@ -118,3 +118,29 @@ def make_inputs(w: Workload, seed: int = 0, device="cpu", with_state: bool = Fal
         if out[k] is not None:
             out[k] = out[k].to(w.dtype)
     return out
+
+
+def make_inputs_chunked(w: Workload, seed: int = 0, device="cpu", chunk: int = 8) -> dict:
+    """The same distributions as `make_inputs`, generated `chunk` sequences at a time into tensors
+    allocated once at their final element type: the float32 temporaries of the generator then stay a
+    fraction of the result (a 64-sequence scaling workload would otherwise need twice its own size
+    again while it is being made).  Chunk i is `make_inputs` of `chunk` sequences with seed
+    `seed + i`; the per-head parameters (a_log, d_skip) are those of chunk 0."""
+    if w.batch <= chunk:
+        return make_inputs(w, seed=seed, device=device)
+    out = None
+    for i, b0 in enumerate(range(0, w.batch, chunk)):
+        nb = min(chunk, w.batch - b0)
+        part = make_inputs(w.scaled(batch=nb), seed=seed + i, device=device)
+        if out is None:
+            out = {}
+            for k, v in part.items():
+                if v is None or v.dim() < 3:
+                    out[k] = v
+                else:
+                    out[k] = torch.empty((w.batch,) + tuple(v.shape[1:]), dtype=v.dtype, device=v.device)
+        for k, v in part.items():
+            if v is not None and v.dim() >= 3:
+                out[k][b0:b0 + nb] = v
+        del part
+    return out
