@@ -15,7 +15,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libm3scan.so"
-SOURCES = ["m3_api.cu", "m3_generic_fwd.cu", "m3_generic_bwd.cu", "m3_noalloc.cu", "m3_tc_fwd.cu", "m3_tc_fwd_direct.cu", "m3_tc_bwd.cu", "m3_step.cu",
+SOURCES = ["m3_api.cu", "m3_generic_fwd.cu", "m3_generic_bwd.cu", "m3_noalloc.cu", "m3_tc_fwd.cu", "m3_tc_fwd_direct.cu", "m3_tc_bwd.cu", "m3_tc_bwd_direct.cu", "m3_step.cu",
            "m3_host_pipe.cu", "m3_conv.cu", "m3_mixer.cu", "m3_reduce.cu"]
 
 

@@ -150,6 +150,16 @@ int tc_backward_call(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* i
   static const bool tma_off = getenv("M3_TC_NO_TMA") != nullptr;
   p.use_tma = (!tma_off && d.R == 1 && !d.rot && d.rev == 0 && d.T % 8 == 0 && !(reinterpret_cast<uintptr_t>(p.ckpt_h) & 15) &&
                m3::tc_make_tile_map(&p.tm_b, p.b, d.B, d.T, d.H, 128) && m3::tc_make_tile_map(&p.tm_c, p.c, d.B, d.T, d.H, 128)) ? 1 : 0;
+  if (!p.use_tma) {
+    if (!m3::tc_make_row_map(&p.tm_b, p.b, d.B, d.T, d.H, 128 * d.R, steps, true) ||
+        !m3::tc_make_row_map(&p.tm_c, p.c, d.B, d.T, d.H, 128 * d.R, steps, true) ||
+        !m3::tc_make_row_map(&p.tm_x, p.x, d.B, d.T, d.H, 64 * d.R, steps, true) ||
+        !m3::tc_make_row_map(&p.tm_dy, p.dy, d.B, d.T, d.H, 64 * d.R, steps, true) ||
+        (d.rot && !m3::tc_make_row_map(&p.tm_th, p.theta, d.B, d.T, d.H, 64, steps, false))) {
+      cudaFreeAsync(base, ctx->stream);
+      return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family needs 16-byte aligned b, c, x, dy and theta");
+    }
+  }
   cudaError_t e = m3::tc_backward(ctx->stream, p, d.rot != 0);
   if (e == cudaSuccess) {
     ctx->launches += 1;

@@ -55,7 +55,8 @@ cudaError_t tc_forward(cudaStream_t st, const TcFwdParams& p, bool rotational);
 cudaError_t tc_forward_direct(cudaStream_t st, const TcFwdParams& p);
 
 struct TcBwdParams {
-  alignas(64) CUtensorMap tm_b, tm_c;   // valid when use_tma (as in TcFwdParams; x and dy go through registers)
+  alignas(64) CUtensorMap tm_b, tm_c;   // tile maps of the direct form when use_tma, else row maps of b and c
+  alignas(64) CUtensorMap tm_x, tm_dy, tm_th;  // row maps of x, dy and theta (role-split kernel)
   int use_tma;
   const __nv_bfloat16 *x, *b, *c, *dt, *lam, *theta, *dy;
   const float *a_log, *d_skip, *h0, *lu0;
@@ -74,5 +75,7 @@ struct TcBwdParams {
 };
 
 cudaError_t tc_backward(cudaStream_t st, const TcBwdParams& p, bool rotational);
+// The direct form (rank 1, real dynamics, use_tma): m3_tc_bwd_direct.cu.
+cudaError_t tc_backward_direct(cudaStream_t st, const TcBwdParams& p);
 
 }  // namespace m3

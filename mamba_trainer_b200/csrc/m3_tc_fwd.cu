@@ -100,16 +100,28 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
     // Copy warp: the raw rows of tile k + 1 are requested as soon as tile k is staged (staging buffers
     // and angle table spent), one request per lane; theta rows land at the start of the table's buffer.
     // --------------------------------------------------------------------------------------------
+#ifdef M3_TC_TIMING
+    long long acc_issue = 0, acc_land = 0;
+#endif
     auto request_rows = [&](int kk) {
       if (lane == 0) {
         mbar_expect_tx(&bars[2], 2u * SM::kRaw);
         if (ROT) mbar_expect_tx(&bars[3], SM::kTheta);
       }
       __syncwarp();
+#ifdef M3_TC_TIMING
+      long long c0_ = clock64();
+#endif
       int l0 = request_raw_tile<R>(0, rawB, &p.tm_b, &bars[2], kN, b, h, T, kk * LT, rev);
       l0 += request_raw_tile<R>(l0, rawC, &p.tm_c, &bars[2], kN, b, h, T, kk * LT, rev);
       if (ROT && lane == l0) tma_load_rows(sTab, &p.tm_th, &bars[3], 0, h, rev ? T - kk * LT - LT : kk * LT, b);
       __syncwarp();
+#ifdef M3_TC_TIMING
+      long long c1_ = clock64();
+      acc_issue += c1_ - c0_;
+      mbar_wait(&bars[2], kk & 1);
+      acc_land += clock64() - c1_;
+#endif
     };
     request_rows(0);
     int requested = 1;
@@ -129,6 +141,9 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
     // no copy of this CTA may be in flight when it lets go of its shared memory
     mbar_wait(&bars[2], (requested - 1) & 1);
     if (ROT) mbar_wait(&bars[3], (requested - 1) & 1);
+#ifdef M3_TC_TIMING
+    if (blockIdx.x == 0 && lane == 0) { g_tc_timing[12] += acc_issue; g_tc_timing[13] += acc_land; }
+#endif
   } else if (warp == kScalarWarp) {
     regs_for_helpers();
     // --------------------------------------------------------------------------------------------
@@ -142,7 +157,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
     for (int j = 0; j < ntiles; ++j) {
       if (j > 0) bar_sync(BAR_FREE, kPairCount);
       lookahead_scalars<R>(scal_set(j & 1), ld, A, T, j * LT);
-      bar_arrive(BAR_AHEAD, kPairCount);
+      bar_arrive(bar_ahead(j), kPairCount);
       if (j + 1 < ntiles) lookahead_load<R>(ld, p.dt, p.lam, p.disc, b, h, H, T, (j + 1) * LT, rev);
     }
   } else if (warp > kIssuerWarp) {
@@ -227,11 +242,11 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
     issue_px<R>(raw_x, p.x, tok_at(0), Hs, T, 0);
     // The angle table of tile j from its theta rows and its scalars (which this call waits for).
     auto angle_table = [&](int j) {
-      bar_sync(BAR_AHEAD, kPairCount);  // scalars of tile j
+      bar_sync(bar_ahead(j), kPairCount);  // scalars of tile j
       if (ROT) {
         if (!dead) dead = !warp_all(mbar_wait(&bars[3], j & 1, wait_limit));
         if (!dead)
-          epi_angle_table<R>(sTab, s_q, s_carry, scal_set(j & 1).dt, T, j * LT, rev,
+          epi_angle_table<R>(sTab, s_q, s_carry, s_carry, scal_set(j & 1).dt, T, j * LT, rev,
                              p.ckpt_angle ? p.ckpt_angle + ((size_t)bh * ntiles + j) * kNH : nullptr,
                              p.angle_out ? p.angle_out + (size_t)bh * kNH : nullptr);
         else
@@ -239,7 +254,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
       }
     };
     angle_table(0);
-    if (ntiles > 1) bar_arrive(BAR_FREE, kPairCount);  // set 1 has never been used
+    if (ntiles > 1) epi_signal(BAR_FREE, kPairCount, dead);  // set 1 has never been used
     epi_sync();
     TICK_INIT;
     for (int k = 0; k < ntiles; ++k) {
@@ -256,7 +271,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
       }
       fence_async_smem();
       tc_fence_before();
-      bar_arrive(BAR_OPS, kEpiThreads + 64);
+      epi_signal(BAR_OPS, kEpiThreads + 64, dead);
       if (warp == 7) TICK(2);
       if (!dead && k + 1 < ntiles) issue_px<R>(raw_x, p.x, tok0 + (size_t)LT * Hs, Hs, T, t0 + LT);
       // ---- 2. band, decays ---------------------------------------------------------------------
@@ -340,7 +355,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
       }
       fence_async_smem();
       tc_fence_before();
-      bar_arrive(BAR_MID, kPairCount);
+      epi_signal(BAR_MID, kPairCount, dead);
       if (warp == 7) TICK(4);
       // ---- 3. the next tile's angle table, while the second group of products runs -------------------
       if (k + 1 < ntiles) angle_table(k + 1);
@@ -404,7 +419,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
       }
       if (warp == 7) TICK(6);
       // this tile's scalars are spent: the look-ahead warp may overwrite their set with tile k + 2's
-      if (k + 2 < ntiles) bar_arrive(BAR_FREE, kPairCount);
+      if (k + 2 < ntiles) epi_signal(BAR_FREE, kPairCount, dead);
       epi_sync();
       if (warp == 7) TICK(7);
       if (!dead) copy_out<R, kP>(sXw, p.y, tok0, Hs, T, t0);

@@ -33,9 +33,12 @@ enum : int {
   BAR_EPI = 1,    // 256: the epilogue warps among themselves
   BAR_OPS = 2,    // 320: operands of a tile are staged (epilogue warps arrive; issuer and copy warp sync)
   BAR_MID = 3,    // 288: the second group of operands is staged (epilogue warps arrive; issuer syncs)
-  BAR_AHEAD = 4,  // 288: scalars of a tile are ready (look-ahead warp arrives; epilogue warps sync)
+  BAR_AHEAD = 4,  // 288: scalars of a tile are ready (look-ahead warp arrives; epilogue warps sync); even tiles
+  BAR_AHEAD_ODD = 7,  // the same for odd tiles: the look-ahead warp may finish a tile before its predecessor's
+                      // scalars have been picked up, and a barrier holds one pending phase only
   BAR_FREE = 5,   // 288: a set of scalars is free again (epilogue warps arrive; look-ahead warp syncs)
-  BAR_TAIL = 6,   // 288: a tile's outputs are staged / its buffers free (epilogue warps arrive; copy warp syncs)
+  BAR_TAIL = 6,   // 288: a tile's gradients are staged, its operands spent (epilogue warps arrive; copy warp syncs)
+  BAR_TAIL2 = 8,  // 288: the gradients have left their staging buffers (epilogue warps arrive; copy warp syncs)
 };
 
 
@@ -46,8 +49,17 @@ __device__ __forceinline__ void bar_arrive(int id, int count) {
   asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 __device__ __forceinline__ void epi_sync() { bar_sync(BAR_EPI, kEpiThreads); }
+__device__ __forceinline__ int bar_ahead(int tile_index) { return (tile_index & 1) ? BAR_AHEAD_ODD : BAR_AHEAD; }
+// An epilogue warp's side of a barrier a helper warp syncs on: arrive and go on - unless the warp has
+// given up a bounded wait and only keeps the protocol alive: then it waits for the helper like everyone,
+// so that it cannot run tiles ahead of a helper that is still inside a (bounded, but long) wait and pile
+// a second phase of arrivals onto a barrier that holds one.
+__device__ __forceinline__ void epi_signal(int id, int count, bool dead) {
+  if (dead) bar_sync(id, count); else bar_arrive(id, count);
+}
 
-// Register budget per role (the CTA's 384 threads start with 168 each).
+// Register budget per role.  The CTA's 384 threads start with 168 each and budgets only move inside that
+// allocation: 256 x 232 + 128 x 40 = 384 x 168.  A request for more than the CTA owns never returns.
 __device__ __forceinline__ void regs_for_epilogue() { asm volatile("setmaxnreg.inc.sync.aligned.u32 232;"); }
 __device__ __forceinline__ void regs_for_helpers() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
 
@@ -133,14 +145,16 @@ __device__ __forceinline__ void lookahead_scalars(const TileScalars& s, const Sc
 // of the tile's steps.  The tile's raw theta rows ([LT][64] bf16, landed by a bulk tensor copy; for a head
 // that walks right to left in memory order, i.e. step l in row LT - 1 - l) sit at the start of the table's
 // own buffer and are consumed before any table word is written (one barrier separates the passes).
-// `carry` [64] holds the angle entering the tile and receives the wrapped angle leaving it; `s_q` is
-// [4][64] floats of exchange space; dt comes from the tile's scalars.  sin / cos come from the
+// `carry_in` [64] holds the angle entering the tile (shared or global memory), `carry_out` (may be NULL,
+// may alias carry_in) receives the wrapped angle leaving it; `s_q` is [4][64] floats of exchange space; dt
+// comes from the tile's scalars.  sin / cos come from the
 // special-function unit (the argument is wrapped into [-pi, pi] first, where its error is far below the
-// half-precision table's).  Contains two barriers of the epilogue warps; the caller's next one
-// publishes the table.
+// half-precision table's).  Contains one barrier of the epilogue warps; the caller's next one publishes
+// the table.
 template <int R>
-__device__ __forceinline__ void epi_angle_table(float* tab, float* s_q, float* carry, const float* s_dt, int T, int t0,
-                                                bool rev, float* ckpt_slot, float* angle_out_bh) {
+__device__ __forceinline__ void epi_angle_table(float* tab, float* s_q, const float* carry_in, float* carry_out,
+                                                const float* s_dt, int T, int t0, bool rev, float* ckpt_slot,
+                                                float* angle_out_bh) {
   constexpr int LT = kRows / R, LQ = LT / 4;
   const __nv_bfloat16* raw = reinterpret_cast<const __nv_bfloat16*>(tab);
   const int tid = threadIdx.x, q = tid >> 6, m = tid & 63;
@@ -153,12 +167,12 @@ __device__ __forceinline__ void epi_angle_table(float* tab, float* s_q, float* c
     loc[i] = run;
   }
   s_q[q * 64 + m] = run;
-  const float cin = carry[m];
+  const float cin = carry_in[m];
   if (ckpt_slot && q == 0) ckpt_slot[m] = cin;
   epi_sync();
   float off = cin;
   for (int qq = 0; qq < q; ++qq) off += s_q[qq * 64 + m];
-  if (q == 3) carry[m] = wrap2pi(off + run);
+  if (carry_out && q == 3) carry_out[m] = wrap2pi(off + run);
 #pragma unroll
   for (int i = 0; i < LQ; ++i) {
     const int l = q * LQ + i;
@@ -284,6 +298,102 @@ __device__ __forceinline__ void convert_bc(const uint8_t* rawB, const uint8_t* r
       }
     }
   }
+}
+
+
+// x-like rows ([step][p * R + r], head_dim 64) of a staged tile into registers and back out as the
+// rank-de-interleaved operand plus a copy scaled per time step; same work items as convert_bc, so a
+// tile converted IN PLACE (operand written over the staging rows) needs one barrier of the epilogue
+// warps between the two calls.
+template <int R>
+__device__ __forceinline__ void load_px_staged(RawPX<R>& raw, const uint8_t* src, bool rev) {
+#pragma unroll
+  for (int i = 0; i < RawPX<R>::NIT; ++i) {
+    int l, grp;
+    convert_coords<2, R>(i, l, grp);
+    load_raw_pieces<R>(src, l, (uint32_t)(grp * 8) * R, rev, raw.v[i]);
+  }
+}
+template <int R>
+__device__ __forceinline__ void store_px(const RawPX<R>& raw, uint8_t* s_plain, uint8_t* s_scaled, const float* scale) {
+#pragma unroll
+  for (int i = 0; i < RawPX<R>::NIT; ++i) {
+    int l, grp;
+    convert_coords<2, R>(i, l, grp);
+    const float sv = scale[l];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float o[8], ow[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { o[j] = elem(raw.v[i], j * R + r); ow[j] = o[j] * sv; }
+      store_chunk(s_plain, tile_off(l * R + r, grp * 8, kP), o);
+      store_chunk(s_scaled, tile_off(l * R + r, grp * 8, kP), ow);
+    }
+  }
+}
+// The two halves of convert_bc for a tile converted in place.
+template <int R, bool ROT>
+__device__ __forceinline__ void load_bc_staged(RawBC<R, ROT>& raw, const uint8_t* rawB, const uint8_t* rawC, bool rev) {
+  using RB = RawBC<R, ROT>;
+#pragma unroll
+  for (int i = 0; i < RB::NIT; ++i) {
+    int l, grp;
+    convert_coords<RB::GB, R>(i, l, grp);
+#pragma unroll
+    for (int which = 0; which < 2; ++which)
+#pragma unroll
+      for (int part = 0; part < RB::NP; ++part)
+        load_raw_pieces<R>(which ? rawC : rawB, l, (uint32_t)(grp * 8 + part * kNH) * R, rev, raw.v[i][which][part]);
+  }
+}
+template <int R, bool ROT>
+__device__ __forceinline__ void store_bc(const RawBC<R, ROT>& raw, uint8_t* sB, uint8_t* sC, const float* tab) {
+  using RB = RawBC<R, ROT>;
+#pragma unroll
+  for (int i = 0; i < RB::NIT; ++i) {
+    int l, grp;
+    convert_coords<RB::GB, R>(i, l, grp);
+    const int n0 = grp * 8;
+    float cs[8], sn[8];
+    if (ROT) table_cos_sin(tab, l, n0, cs, sn);
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      uint8_t* dst = which ? sC : sB;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        if (ROT) {
+          float o1[8], o2[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float v1 = elem(raw.v[i][which][0], j * R + r), v2 = elem(raw.v[i][which][RB::NP - 1], j * R + r);
+            o1[j] = v1 * cs[j] + v2 * sn[j];
+            o2[j] = v2 * cs[j] - v1 * sn[j];
+          }
+          store_chunk(dst, tile_off(l * R + r, n0, kN), o1);
+          store_chunk(dst, tile_off(l * R + r, n0 + kNH, kN), o2);
+        } else {
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = elem(raw.v[i][which][0], j * R + r);
+          store_chunk(dst, tile_off(l * R + r, n0, kN), o);
+        }
+      }
+    }
+  }
+}
+
+// Sum over the 256 threads of the epilogue warps; red: >= 8 floats of shared scratch.  Contains two of
+// their barriers.
+__device__ __forceinline__ float epi_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  epi_sync();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  epi_sync();
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s += red[i];
+  return s;
 }
 
 }  // namespace m3tc
