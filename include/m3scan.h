@@ -150,9 +150,10 @@ int m3_ctx_set_stream(m3_ctx *ctx, void *cuda_stream);
  * way (the reference has no counterpart: its kernels never wait on one another). */
 int m3_sync(m3_ctx *ctx);
 /* Iteration limit of those bounded waits for calls made through this context; 0 restores
- * the default (2^18 polls of an mbarrier, far beyond any healthy wait).  Diagnostic: a
- * limit of 1 makes the first wait of a tensor-core kernel give up, which is how the
- * failure path is exercised without a fault.  No counterpart in the reference. */
+ * the default (2^18: a wait polls its mbarrier at most limit - 1 times, far beyond any
+ * healthy wait).  Diagnostic: a limit of 1 makes every wait of the tensor-core kernels
+ * give up at once, which is how the failure path is exercised without a fault.  No
+ * counterpart in the reference. */
 int m3_ctx_set_wait_limit(m3_ctx *ctx, uint32_t iterations);
 /* Message of the last failure on this context ("" if none).  Never NULL. */
 const char *m3_last_error(const m3_ctx *ctx);
@@ -209,12 +210,18 @@ int m3_step_forward(m3_ctx *ctx, const m3_step_desc *desc, const m3_step_out *ou
  * image (so every GPU that loads the library holds that much until the process
  * exits).  Inputs and outputs are still the caller's.  Descriptors whose scratch
  * (m3_scan_scratch_bytes(desc, 0)) exceeds the block are refused with
- * M3_ERR_UNSUPPORTED.  The generic kernel family runs whatever desc->path says.
+ * M3_ERR_UNSUPPORTED.  Shapes the tensor-core family serves run there unless
+ * desc->path says M3_PATH_GENERIC: with nothing kept for a backward pass that family
+ * needs no scratch at all; everything else runs the generic family on the block.
  * The first call on each device looks up the block's device address (with that
- * device current); make that first call before any stream capture.  All calls on a
- * device share the block and it keeps the previous call's contents (nothing in it
- * needs to start at zero): two calls whose kernels overlap on the GPU race - keep
- * them on one stream or order them yourself. */
+ * device current), and - CUDA loads a library's kernels and file-scope device arrays
+ * when they are first touched - it is also the call during which the driver maps the
+ * block and the kernels it launches: make one warm-up call per device and element type
+ * at start-up, before the arena is sized and before any stream capture; from the
+ * second call on nothing is allocated by anyone.  All calls on a device share the
+ * block and it keeps the previous call's contents (nothing in it needs to start at
+ * zero): two calls whose kernels overlap on the GPU race - keep them on one stream or
+ * order them yourself. */
 #define M3_NOALLOC_SCRATCH_BYTES (16u << 20)
 int m3_scan_forward_noalloc(m3_ctx *ctx, const m3_scan_desc *desc, const m3_scan_out *out);
 

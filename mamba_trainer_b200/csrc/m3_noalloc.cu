@@ -14,6 +14,7 @@
 #include <mutex>
 
 #include "m3_internal.h"
+#include "m3_tc.h"
 
 namespace {
 
@@ -52,6 +53,9 @@ extern "C" int m3_scan_forward_noalloc(m3_ctx* ctx, const m3_scan_desc* desc, co
   if (rc != M3_OK) return rc;
   if (d.T == 0) return m3_scan_forward(ctx, desc, out, nullptr);  // that branch only copies the state
   if (!out->y) return m3::fail(ctx, M3_ERR_NULL, "y is required");
+  // Shapes the tensor-core family serves need no scratch at all when nothing is kept for a backward
+  // pass: that call allocates nothing either, and is the fast one.
+  if (m3::tc_supported(*desc) && !d.raw && desc->path != M3_PATH_GENERIC) return m3_scan_forward(ctx, desc, out, nullptr);
   if (ctx->device < 0 || ctx->device >= kMaxDevices)
     return m3::fail(ctx, M3_ERR_UNSUPPORTED, "device ordinal %d outside the table of %d", ctx->device, kMaxDevices);
   const size_t need = m3::generic_ws_layout(d, nullptr, nullptr);

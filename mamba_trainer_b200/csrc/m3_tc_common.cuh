@@ -83,13 +83,13 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
 
-// Wait for a phase of an mbarrier with an iteration limit.  Returns false if it gave up;
-// the caller reports that through an error flag and leaves the kernel - it never spins
-// without bound.
+// Wait for a phase of an mbarrier with an iteration limit: at most limit - 1 polls (each poll may itself
+// block for a hardware-defined time), so a limit of 1 gives up at once.  Returns false if it gave up; the
+// caller reports that through an error flag and stops working - it never spins without bound.
 constexpr uint32_t kWaitLimit = 1u << 18;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = kWaitLimit) {
   const uint32_t a = smem_u32(bar);
-  for (uint32_t it = 0; it < limit; ++it) {
+  for (uint32_t it = 1; it < limit; ++it) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"

@@ -63,7 +63,14 @@ class Context:
         return int(self.lib.m3_launch_count(self.handle))
 
     def sync(self) -> None:
+        """Block until the context's work is done; raises DeviceTimeout if a kernel's bounded wait gave
+        up since the last report (the same condition is also raised by the next scan call, which looks
+        at the host-mapped flag on entry)."""
         self.check(self.lib.m3_sync(self.handle))
+
+    def set_wait_limit(self, iterations: int) -> None:
+        """Iteration limit of the kernels' bounded waits (0 = default); see m3_ctx_set_wait_limit."""
+        self.check(self.lib.m3_ctx_set_wait_limit(self.handle, C.c_uint32(int(iterations))))
 
 
 class _Saved:

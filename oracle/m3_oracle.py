@@ -30,6 +30,55 @@ LOG_DECAY_FLOOR = -60.0  # src/ssm/scan.rs:54-57
 TWO_PI = 2.0 * math.pi
 
 
+class _RoundedMatmul(torch.autograd.Function):
+    """a @ b the way the reference's reduced-precision matmul mode evaluates it: both operands rounded
+    to the narrow type once per call, products accumulated in float32, and every matmul of the backward
+    rule evaluated the same way (src/tensor/ops/matmul.rs:94-128, :1832-1863; backward rules
+    src/autograd/ops.rs:204-264).  Everything outside the matmuls stays in the wide type."""
+
+    @staticmethod
+    def forward(ctx, a, b, narrow):
+        ctx.save_for_backward(a, b)
+        ctx.narrow = narrow
+        return _RoundedMatmul.mm(a, b, narrow)
+
+    @staticmethod
+    def mm(a, b, narrow):
+        wide = a.dtype
+        return (a.to(narrow).to(torch.float32) @ b.to(narrow).to(torch.float32)).to(wide)
+
+    @staticmethod
+    def backward(ctx, grad):
+        a, b = ctx.saved_tensors
+        ga = _RoundedMatmul.mm(grad, b.transpose(-1, -2), ctx.narrow)
+        gb = _RoundedMatmul.mm(a.transpose(-1, -2), grad, ctx.narrow)
+        return ga, gb, None
+
+
+_MATMUL_NARROW = None   # None: exact matmuls in the tensors' own type
+
+
+class matmul_precision:
+    """Context manager: inside it every matmul of `ssd_chunked` runs in the reference's reduced-precision
+    mode with `narrow` operands (e.g. torch.bfloat16).  Used to measure how far the REFERENCE's own bf16
+    mode sits from exact arithmetic on a given input - the yardstick for the CUDA path's bf16 tolerances."""
+
+    def __init__(self, narrow):
+        self.narrow = narrow
+
+    def __enter__(self):
+        global _MATMUL_NARROW
+        self.prev, _MATMUL_NARROW = _MATMUL_NARROW, self.narrow
+
+    def __exit__(self, *exc):
+        global _MATMUL_NARROW
+        _MATMUL_NARROW = self.prev
+
+
+def _mm(a, b):
+    return a @ b if _MATMUL_NARROW is None else _RoundedMatmul.apply(a, b, _MATMUL_NARROW)
+
+
 def wrap_angle(phi: torch.Tensor) -> torch.Tensor:
     """x - round(x / 2pi) * 2pi with an identity gradient.
 
@@ -117,15 +166,15 @@ def ssd_chunked(x, b, c, a, g, w, initial_state=None, chunk_size=64, want_state=
     # 1. intra-chunk (scan.rs:192-205)
     band = _band(rows(acum), rows(w), rows(g))
     c_flat, b_flat, x_flat = heads_first(c, N), heads_first(b, N), heads_first(x, P)
-    cb = c_flat @ b_flat.transpose(1, 2)
-    y_diag = ((cb * band) @ x_flat).reshape(B, C, H, L, P).permute(0, 1, 3, 2, 4)
+    cb = _mm(c_flat, b_flat.transpose(1, 2))
+    y_diag = _mm(cb * band, x_flat).reshape(B, C, H, L, P).permute(0, 1, 3, 2, 4)
 
     # 2. chunk summaries (scan.rs:208-216)
     last_acum = acum[:, :, L - 1:L]
     decay_to_end = (last_acum - acum).clamp(LOG_DECAY_FLOOR, 0.0).exp() * w
     weighted_x = x * decay_to_end.unsqueeze(4)
-    chunk_state = (
-        weighted_x.permute(0, 1, 3, 4, 2).reshape(B * C * H, P, L) @ b_flat
+    chunk_state = _mm(
+        weighted_x.permute(0, 1, 3, 4, 2).reshape(B * C * H, P, L), b_flat
     ).reshape(B, C, H, P, N)
 
     # 3. inter-chunk recurrence as a masked C x C product (scan.rs:219-251)
@@ -136,9 +185,9 @@ def ssd_chunked(x, b, c, a, g, w, initial_state=None, chunk_size=64, want_state=
     strict = (kk.view(C, 1) > kk.view(1, C)).to(x.dtype).view(1, C, C, 1)
     transfer = (before.unsqueeze(2) - through.unsqueeze(1)).clamp(
         LOG_DECAY_FLOOR, 0.0).exp() * strict
-    carry_in = (
-        transfer.permute(0, 3, 1, 2).reshape(B * H, C, C)
-        @ chunk_state.permute(0, 2, 1, 3, 4).reshape(B * H, C, P * N)
+    carry_in = _mm(
+        transfer.permute(0, 3, 1, 2).reshape(B * H, C, C),
+        chunk_state.permute(0, 2, 1, 3, 4).reshape(B * H, C, P * N)
     ).reshape(B, H, C, P, N).permute(0, 2, 1, 3, 4)
     if initial_state is not None:
         scale = before.clamp(LOG_DECAY_FLOOR, 0.0).exp().reshape(B, C, H, 1, 1)
@@ -146,9 +195,9 @@ def ssd_chunked(x, b, c, a, g, w, initial_state=None, chunk_size=64, want_state=
 
     # 4. carry-in read by every position (scan.rs:254-268)
     c_dec = c * acum.clamp(LOG_DECAY_FLOOR, 0.0).exp().unsqueeze(4)
-    y_off = (
-        heads_first(c_dec, N)
-        @ carry_in.permute(0, 1, 2, 4, 3).reshape(B * C * H, N, P)
+    y_off = _mm(
+        heads_first(c_dec, N),
+        carry_in.permute(0, 1, 2, 4, 3).reshape(B * C * H, N, P)
     ).reshape(B, C, H, L, P).permute(0, 1, 3, 2, 4)
     y = (y_diag + y_off).reshape(B, Tp, H, P)[:, :T]
 

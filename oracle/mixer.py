@@ -42,10 +42,23 @@ def rms_norm(v, weight=None, eps: float = 1e-5):
     return out * weight if weight is not None else out
 
 
+class _Narrow(torch.autograd.Function):
+    """Round to a narrow type and back, in both directions of the tape."""
+
+    @staticmethod
+    def forward(ctx, v, narrow):
+        ctx.narrow = narrow
+        return v.to(narrow).to(v.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g.to(ctx.narrow).to(g.dtype), None
+
+
 def mixer_core(proj, p: dict, heads: int, head_dim: int, d_state: int, rank: int = 1, groups: Optional[int] = None,
                chunk: int = 64, learned_lambda: bool = True, rotational: bool = True, eps: float = 1e-5,
                conv_history=None, state=None, want_state: bool = False, fixed_lambda: float = 1.0,
-               bidirectional: bool = False):
+               bidirectional: bool = False, scan_io_dtype=None):
     """Everything Mamba3Mixer does between its input and output projections
     (src/models/mamba3.rs:340-461, :475-484, :540-556, no post_gate_norm, one direction):
     split the projection into z | x B C | dt | lambda | theta, convolve x|B|C and apply SiLU, expand
@@ -54,6 +67,9 @@ def mixer_core(proj, p: dict, heads: int, head_dim: int, d_state: int, rank: int
 
     p: conv_w [K, d_inner + 2 bc], conv_b [same] or None, dt_bias [H], a_log [H], d_skip [H] or None,
     b_bias / c_bias [H, N] or None, norm_w [N] or None ("norm" False in p disables the norm).
+    scan_io_dtype (e.g. torch.bfloat16): the scan's per-token inputs and its output pass through that
+    type (rounded values, identity gradient, gradients rounded likewise) - the benchmark's "bf16 inputs"
+    applied inside the mixer, where the CUDA path hands bf16 tensors from kernel to kernel.
     Returns (gated [B, T, d_inner], new conv history, OracleState or None)."""
     B, T, W = proj.shape
     H, P, N, R = heads, head_dim, d_state, rank
@@ -91,7 +107,11 @@ def mixer_core(proj, p: dict, heads: int, head_dim: int, d_state: int, rank: int
     dt = F.softplus(dt_raw + p["dt_bias"].reshape(1, 1, H))         # :440-442
     lam = torch.sigmoid(lam_raw) if learned_lambda else torch.full_like(dt, fixed_lambda)
     theta = th_raw.reshape(B, T, H, N // 2) if rotational else None
+    if scan_io_dtype is not None:
+        x5, b, c, dt, lam, theta = (None if v is None else _Narrow.apply(v, scan_io_dtype) for v in (x5, b, c, dt, lam, theta))
     y, st = O.mamba3_scan(x5, b, c, dt, p["a_log"], lam, theta, p.get("d_skip"), state, chunk, want_state)
+    if scan_io_dtype is not None:
+        y = _Narrow.apply(y, scan_io_dtype)
     y = y.reshape(B, T, d_inner)
     if bidirectional:                                               # :548-556: the backward heads' output back
         y = torch.cat([y[..., :d_inner // 2], y[..., d_inner // 2:].flip(1)], dim=-1)

@@ -35,10 +35,15 @@ def allclose_excess(a, e, rtol, atol) -> float:
 
 
 def oracle_run(t: dict, chunk: int, want_state=True, dtype=torch.float64, grads=True,
-               dstate=None, use_lam=True, reverse_heads=0):
+               dstate=None, use_lam=True, reverse_heads=0, matmul_narrow=None):
     """Run the composed oracle on CPU.  `t` holds x, b, c, dt, a_log, lam, theta, d_skip
     and optionally h0, last_u0, angle0, dy.  Inputs are upcast (a bf16 tensor is used
-    at its rounded value).  Returns (y, state, {name: grad})."""
+    at its rounded value).  With `matmul_narrow` (e.g. torch.bfloat16) every matmul runs in the
+    reference's reduced-precision mode (operands rounded once per call, float32 accumulation,
+    src/tensor/ops/matmul.rs:94-128, :1832-1863).  Returns (y, state, {name: grad})."""
+    if matmul_narrow is not None:
+        with O.matmul_precision(matmul_narrow):
+            return oracle_run(t, chunk, want_state, dtype, grads, dstate, use_lam, reverse_heads, None)
     names = [n for n in GRAD_NAMES if t.get(n) is not None]
     leaf = {n: t[n].detach().cpu().to(dtype).requires_grad_(grads) for n in names}
     st = None
@@ -95,3 +100,13 @@ def angle_close(a, e, tol) -> bool:
     a, e = a.detach().double().cpu(), e.detach().double().cpu()
     return float((torch.sin(a) - torch.sin(e)).abs().max()) < tol and \
         float((torch.cos(a) - torch.cos(e)).abs().max()) < tol
+
+
+def reference_mode_error(t: dict, chunk: int, exact: dict, names, want_state=False) -> dict:
+    """||r - e|| / ||e|| per gradient in `names`, where r comes from the oracle run in float32 with the
+    REFERENCE's own bf16 matmul mode and e = `exact` from the float64 oracle on the same inputs: how far
+    the reference's reduced-precision arithmetic itself sits from exact arithmetic.  The yardstick for
+    gradients whose bf16 error is dominated by cancellation (d theta: the d phi of a stripe sum to zero;
+    d a_log, d dt_bias: sums over every token)."""
+    _, _, g = oracle_run(t, chunk, want_state, torch.float32, True, matmul_narrow=torch.bfloat16)
+    return {n: norm_rel(g[n].double(), exact[n]) for n in names if n in g and n in exact}

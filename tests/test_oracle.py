@@ -173,3 +173,21 @@ def test_odd_state_with_rotation_is_a_config_error():
     with pytest.raises(ValueError):
         O.mamba3_scan(ex(case.x), ex(case.b), ex(case.c), T64(case.dt), T64(case.a_log), T64(case.lam),
                       T64(np.zeros((1, 4, 1, 1))))
+
+
+def test_reference_bf16_matmul_mode_is_the_yardstick_for_dtheta():
+    """The reference's own reduced-precision mode (matmul operands rounded to bf16 once per call, float32
+    accumulation, every backward matmul likewise: src/tensor/ops/matmul.rs:94-128, :1832-1863) against exact
+    arithmetic on one (batch, head) stripe of the scaling workload: every gradient but d theta stays within a
+    few 1e-3 of the float64 result, d theta - dt times a running sum of d phi terms that cancel over the stripe -
+    is off by several percent.  The GPU parity tests bound the CUDA path's d theta by this figure measured on
+    the very stripe they compare (never below the plain 2e-2)."""
+    from mamba_trainer_b200 import synthetic
+    from tests._util import oracle_run, reference_mode_error
+    w = synthetic.WORKLOADS[4].scaled(batch=1, heads=1, seq=4096)
+    t = synthetic.make_inputs(w, seed=4)
+    _, _, exact = oracle_run(t, w.chunk, False, torch.float64, True)
+    err = reference_mode_error(t, w.chunk, exact, ("x", "b", "c", "dt", "lam", "theta"))
+    for n in ("x", "b", "c", "dt", "lam"):
+        assert err[n] < 1e-2, (n, err[n])
+    assert 2e-2 < err["theta"] < 1e-1, err["theta"]     # measured 4.2e-2 here, 5.2e-2 at 16384 tokens

@@ -17,7 +17,8 @@ from mamba_trainer_b200 import synthetic
 from mamba_trainer_b200.error import ConfigError, RankError, ShapeError
 from mamba_trainer_b200.ssm import Discretization, ScanInputs, SsmState, mamba3_scan
 from oracle.recurrence import Case, recurrence
-from tests._util import (allclose_excess, angle_close, fused_run, norm_rel, oracle_run, ref_metric)
+from tests._util import (allclose_excess, angle_close, fused_run, norm_rel, oracle_run, ref_metric,
+                         reference_mode_error)
 
 pytestmark = pytest.mark.gpu
 
@@ -261,14 +262,18 @@ def test_bf16_configs_full_size(idx):
         for n in ("x", "b", "c", "dt", "lam"):
             check_bf16(f"d{n}[{b_},{h_}]", cut(g[n]), eg[n])
         if "theta" in eg:
-            # d theta = dt * (sum of d phi over every later step), and the d phi of a stripe sum to
-            # zero (rotating B and C together changes nothing): the running sum is a difference of
-            # large cancelling terms, so the bf16 rounding of the tensor-core operands shows up
-            # amplified, growing with sqrt(T) (measured 1.2 % at T = 4096, 3.5 % at T = 16384, as
-            # ||a - e|| / ||e||).  The reference's own measure stays two orders below its 2e-2.
+            # d theta = dt * (sum of d phi over every later step), and the d phi of a stripe sum to zero
+            # (rotating B and C together changes nothing): the running sum is a difference of large
+            # cancelling terms, so ANY bf16 rounding of matmul operands shows up amplified, growing with
+            # sqrt(T).  The yardstick is the reference itself: its own bf16 matmul mode (oracle with
+            # matmul_precision, src/tensor/ops/matmul.rs:94-128) on the same stripe is off from exact
+            # arithmetic by 4-5 % (tests/test_oracle.py pins that figure); the CUDA path must be at least as
+            # close as that, and meet the plain 2e-2 in the reference's own measure.
             a_, e_ = cut(g["theta"]).float(), eg["theta"]
+            yard = reference_mode_error(st, w.chunk, eg, ("theta",))["theta"]
             assert ref_metric(a_, e_) <= 2e-2, f"dtheta[{b_},{h_}]: reference metric {ref_metric(a_, e_):.3e}"
-            assert norm_rel(a_, e_) <= 6e-2, f"dtheta[{b_},{h_}]: norm-relative error {norm_rel(a_, e_):.3e}"
+            assert norm_rel(a_, e_) <= max(2e-2, yard), \
+                f"dtheta[{b_},{h_}]: norm-relative error {norm_rel(a_, e_):.3e}, the reference's bf16 mode: {yard:.3e}"
     # (b) linearity in dy (a factor of two is exact in every format involved)
     g2 = torch.autograd.grad(out.y, [leaf[n] for n in names], grad_outputs=t["dy"] * 2)
     for n, a_, b2 in zip(names, grads, g2):
@@ -280,6 +285,51 @@ def test_bf16_configs_full_size(idx):
         o2 = mamba3_scan(build(slice(half, w.seq), o1.state))
     check_bf16("windows y", torch.cat([o1.y, o2.y], 1), out.y.detach().float())
     check_bf16("windows h", o2.state.h, out.state.h.detach())
+
+
+# ---- a bounded device-side wait that runs out (no fault, no hang: the kernels give up and say so) ----
+
+@pytest.mark.parametrize("idx,kw", [(4, dict(batch=1, heads=2, seq=700)), (1, dict(batch=1, heads=2, seq=512))])
+def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable(idx, kw):
+    """Every device-side wait of the tensor-core kernels has an iteration limit.  With the limit set to one
+    poll (m3_ctx_set_wait_limit) the first wait of every CTA gives up before its products or copies have
+    finished: the kernels must return by themselves, the condition must surface as DeviceTimeout - at
+    Context.sync() and, for callers that never sync, on entry to the next scan call - and once the limit
+    is back to its default the same context must compute correct results again.  Covers the role-split
+    kernels (rank 2, rotational) and the direct form (rank 1, real dynamics)."""
+    from mamba_trainer_b200.error import DeviceTimeout
+    from mamba_trainer_b200.ssm import Context
+    w = synthetic.WORKLOADS[idx].scaled(**kw)
+    t = synthetic.make_inputs(w, seed=21)
+    good_y, _, good_g = fused_run(t, w.chunk, False)
+    ctx = Context.for_device(torch.device("cuda", torch.cuda.current_device()))
+    ctx.sync()
+    try:
+        ctx.set_wait_limit(1)
+        with pytest.raises(DeviceTimeout):
+            fused_run(t, w.chunk, False)      # the forward gives up; the backward call may already see it on entry
+            ctx.sync()                        # ... and if it was too early for that, the sync does
+        torch.cuda.synchronize()
+        try:
+            ctx.sync()                        # whatever the backward raised meanwhile is reported once, then clear
+        except DeviceTimeout:
+            pass
+        ctx.sync()
+        fused_run(t, w.chunk, False, grads=False)
+        torch.cuda.synchronize()
+        with pytest.raises(DeviceTimeout):    # a caller that never syncs learns of it at its next call
+            fused_run(t, w.chunk, False, grads=False)
+    finally:
+        ctx.set_wait_limit(0)
+        torch.cuda.synchronize()
+        try:
+            ctx.sync()
+        except DeviceTimeout:
+            pass
+    y, _, g = fused_run(t, w.chunk, False)
+    assert torch.equal(y, good_y)
+    for n in good_g:
+        assert torch.equal(g[n], good_g[n]), n
 
 
 # ---- error behaviour (src/ssm/scan.rs:462, :485-489; src/error.rs) -------------------
@@ -634,7 +684,7 @@ def test_mixer_core_replays_the_reference_ports_vectors():
 def test_mixer_core_bf16_matches_the_oracle(rank, groups, rot, learned, norm_gain):
     from mamba_trainer_b200.nn import MixerCore, MixerShape
     from oracle.mixer import mixer_core as oracle_core
-    H, P, N, B, T = 2, 64, 128, 2, 200
+    H, P, N, B, T = 2, 64, 128, 6, 400   # enough tokens per head for the per-head sums (a_log, dt_bias) to average
     shape = MixerShape(H, P, N, rank, groups, learned, rot)
     torch.manual_seed(rank * 7 + (groups or 0))
     core = MixerCore(shape, chunk=64, norm_gain=norm_gain, device="cuda")
@@ -661,12 +711,10 @@ def test_mixer_core_bf16_matches_the_oracle(rank, groups, rot, learned, norm_gai
             "dt": (2 * di + 2 * bc, 2 * di + 2 * bc + H)}
     for name, (lo, hi) in cuts.items():
         check_bf16("dproj." + name, grads[0][..., lo:hi], eg[0][..., lo:hi])
+    # every parameter gradient meets the plain bf16 tolerance (a_log and dt_bias are sums over every token
+    # with heavy cancellation: the case has 2400 tokens per head so that they average)
     for n, a_, e_ in zip(names, grads[1:], eg[1:]):
-        if n in ("a_log", "dt_bias"):     # sums over every token with heavy cancellation: bf16 operands show
-            assert ref_metric(a_.float(), e_) <= 2e-2 * max(1.0, float(e_.abs().max())), n
-            assert norm_rel(a_.float(), e_) <= 5e-2, f"d{n}: {norm_rel(a_.float(), e_):.3e}"
-        else:
-            check_bf16("d" + n, a_, e_)
+        check_bf16("d" + n, a_, e_)
 
 
 @pytest.mark.parametrize("rank,dtype", [(1, torch.float32), (2, torch.float32), (1, torch.bfloat16)])
