@@ -76,9 +76,10 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
   float* s_red = s_dast + 132;        // [16]
   float* s_dcar = s_red + 16;         // [64] sum of d phi over later tiles
   float* s_q = s_dcar + 64;           // [4][64]
-  // [0], [1]: tensor-core phases; [2]: arrival of a tile's raw rows; [3]: of its state checkpoint
+  // [0]: phase A; [1]: the first three products of phase B, [4]: the rest of it; [2]: arrival of a tile's raw
+  // rows; [3]: of its state checkpoint
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_q + 256);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
@@ -96,6 +97,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
     mbar_init(&bars[1], 1);
     mbar_init(&bars[2], 2);
     mbar_init(&bars[3], 1);
+    mbar_init(&bars[4], 1);
   }
   if (warp == 0) tmem_alloc(tmem_slot, TM_COLS);
   if (tid < kNH) s_dcar[tid] = 0.0f;
@@ -182,14 +184,19 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
     // --------------------------------------------------------------------------------------------
     bool ckpt_ok = true;
     for (int it = 0; it < ntiles; ++it) {
-      bar_sync(BAR_OPS, kPairCount);  // operands of the tile staged
+      bar_sync(BAR_OPS0, kPairCount);  // X~ and dY~ staged: the two products that need nothing else start now
       if (ckpt_ok) ckpt_ok = warp_all(mbar_wait(&bars[3], it & 1));  // H_k has landed (long ago, as a rule)
       if (lane == 0) {
         if (!ckpt_ok && p.err) raise_flag(p.err);
         tc_fence_after();
-        gemm_issue(tm + TM_G, k_major(smem_u32(sC), kN), k_major(smem_u32(sB), kN), make_idesc(128, 0, 0), kN, false);
         gemm_issue(tm + TM_DM, k_major(smem_u32(sDY), kP), k_major(smem_u32(sX), kP), make_idesc(128, 0, 0), kP, false);
         gemm_issue(tm + TM_T1, k_major(smem_u32(sDY), kP), mn_major(smem_u32(sHS), kN), make_idesc(128, 0, 1), kP, false);
+      }
+      __syncwarp();
+      bar_sync(BAR_OPS, kPairCount);  // C^ and B^ staged
+      if (lane == 0) {
+        tc_fence_after();
+        gemm_issue(tm + TM_G, k_major(smem_u32(sC), kN), k_major(smem_u32(sB), kN), make_idesc(128, 0, 0), kN, false);
         umma_commit(&bars[0]);
       }
       __syncwarp();
@@ -199,17 +206,21 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
         const uint32_t aM = smem_u32(sM), aDG = smem_u32(sDG), aC = smem_u32(sC), aB = smem_u32(sB), aHS = smem_u32(sHS);
         gemm_issue(tm + TM_DX, mn_major(aM, kRows), mn_major(smem_u32(sDY), kP), make_idesc(64, 1, 1), kRows, false);
         gemm_issue(tm + TM_U, k_major(aB, kN), k_major(aHS, kN), make_idesc(64, 0, 0), kN, false);
-        gemm_issue(tm + TM_DB, mn_major(aDG, kRows), mn_major(aC, kN), make_idesc(128, 1, 1), kRows, false);
-        gemm_issue(tm + TM_DB, k_major(smem_u32(sXw), kP), mn_major(aHS, kN), make_idesc(128, 0, 1), kP, true);
+        gemm_issue(tm + TM_DB, k_major(smem_u32(sXw), kP), mn_major(aHS, kN), make_idesc(128, 0, 1), kP, false);
+        // every product that reads dS is in this first group: the dx epilogue, which runs while the other
+        // three products do, stages its result in dS's buffer
+        umma_commit(&bars[1]);
+        gemm_issue(tm + TM_DB, mn_major(aDG, kRows), mn_major(aC, kN), make_idesc(128, 1, 1), kRows, true);
         gemm_issue(tm + TM_T1, k_major(aDG, kRows), mn_major(aB, kN), make_idesc(128, 0, 1), kRows, true);
         gemm_issue(tm + TM_DH, mn_major(aC, kN), mn_major(smem_u32(sDYe), kP), make_idesc(64, 1, 1), kRows, true);
-        umma_commit(&bars[1]);
+        umma_commit(&bars[4]);
       }
       __syncwarp();
     }
     // Nothing of this CTA may be in flight when it lets go of its shared memory and TMEM.
     mbar_wait(&bars[0], (ntiles - 1) & 1);
     mbar_wait(&bars[1], (ntiles - 1) & 1);
+    mbar_wait(&bars[4], (ntiles - 1) & 1);
   } else {
     regs_for_epilogue();
     // --------------------------------------------------------------------------------------------
@@ -263,8 +274,11 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
             load_px_staged<R>(raw_p, rawDY, rev);
             store_px<R>(raw_p, sDY, sDYe, ts.eac);
           }
-          load_bc_staged<R, ROT>(raw_bc, sB, sC, rev);
         }
+        fence_async_smem();
+        tc_fence_before();
+        epi_signal(BAR_OPS0, kPairCount, dead);
+        if (!dead) load_bc_staged<R, ROT>(raw_bc, sB, sC, rev);
         epi_sync();  // every warp holds its share of the rows of B and C (and the angle table is complete)
         if (!dead) {
           store_bc<R, ROT>(raw_bc, sB, sC, sTab);
@@ -454,19 +468,15 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
       for (int j = 0; j < 32; ++j) dphi[j] = 0.0f;
       if (!dead) {
         tc_fence_after();
-        float acc[2][16], u[2][16], gq[4][16];
+        float acc[2][16], u[2][16];
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
           tmem_ld16_issue(tmem_addr(tm, quad * 32, TM_DX + 32 * ch + 16 * cc), acc[cc]);
           tmem_ld16_issue(tmem_addr(tm, quad * 32, TM_U + 32 * ch + 16 * cc), u[cc]);
         }
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) tmem_ld16_issue(tmem_addr(tm, quad * 32, TM_DB + gcol(q4)), gq[q4]);
         tmem_wait_ld();
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) { tmem_ld_fence(acc[cc]); tmem_ld_fence(u[cc]); }
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) tmem_ld_fence(gq[q4]);
         {  // dx = M^T dY~ + sw (B^ dS^T) + D dy ; q = <U, x>
           const float sw = ts.sw[rl];
           const float2 sw2 = make_float2(sw, sw), dsk2 = make_float2(dsk, dsk);
@@ -507,15 +517,22 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
           part_q[ch * 128 + row] = qp2.x + qp2.y;
           dD_part = dD2.x + dD2.y;
         }
+      }
+      if (!dead) dead = !warp_all(mbar_wait(&bars[4], it & 1, wait_limit));  // the other four products
+      if (!dead) {
+        tc_fence_after();
         {  // dB^ (TM_DB, operand sB, out db) then dC^ (TM_T1, operand sC, out dc)
-          float tabv[2][16];
+          float gq[4][16], tabv[2][16];
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) tmem_ld16_issue(tmem_addr(tm, quad * 32, TM_DB + gcol(q4)), gq[q4]);
           if (ROT) {
 #pragma unroll
             for (int mc = 0; mc < 2; ++mc) tmem_ld16_issue(tmem_addr(tm, quad * 32, TM_TAB + 32 * ch + 16 * mc), tabv[mc]);
-            tmem_wait_ld();
-            tmem_ld_fence(tabv[0]);
-            tmem_ld_fence(tabv[1]);
           }
+          tmem_wait_ld();
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) tmem_ld_fence(gq[q4]);
+          if (ROT) { tmem_ld_fence(tabv[0]); tmem_ld_fence(tabv[1]); }
           auto finish = [&](float (&g)[4][16], const uint8_t* sop, uint8_t* stg, bool is_b) {
             if (is_b && at_end && p.dlu) {  // d last_u reaches B^ of the final token: += dlu^T x
 #pragma unroll 1

@@ -38,6 +38,7 @@ enum : int {
                       // scalars have been picked up, and a barrier holds one pending phase only
   BAR_FREE = 5,   // 288: a set of scalars is free again (epilogue warps arrive; look-ahead warp syncs)
   BAR_TAIL = 6,   // 288: a tile's gradients are staged, its operands spent (epilogue warps arrive; copy warp syncs)
+  BAR_OPS0 = 9,   // 288: the x / dy operands of a tile are staged, ahead of B and C (epilogue warps arrive; issuer syncs)
   BAR_TAIL2 = 8,  // 288: the gradients have left their staging buffers (epilogue warps arrive; copy warp syncs)
 };
 
