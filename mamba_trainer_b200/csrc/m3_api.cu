@@ -110,6 +110,24 @@ int make_dims(m3_ctx* ctx, const m3_scan_desc& s, m3::Dims* out) {
 
 namespace {
 
+// Time segments of the stripes for one launch of the role-split kernels: the plan, and - when a stripe is
+// cut - the hand-over scratch (state, angle, flags; the flags zeroed on the stream).  `*scratch` is null
+// when nothing is handed over; the caller frees it on the stream after the launch.
+template <class Params>
+cudaError_t plan_segments(m3_ctx* ctx, Params& p, int tiles, bool allow_split, char** scratch) {
+  *scratch = nullptr;
+  size_t bytes = 0;
+  m3::tc_segment_plan(p.B * p.H, tiles, allow_split, &p.nseg, &p.tps, &p.grid, &bytes);
+  if (p.nseg == 1) return cudaSuccess;
+  cudaError_t e = m3::scratch_alloc(ctx, reinterpret_cast<void**>(scratch), bytes, ctx->stream);
+  if (e != cudaSuccess) return e;
+  const size_t items = (size_t)p.B * p.H * p.nseg;
+  p.seg_state = reinterpret_cast<float*>(*scratch);
+  p.seg_angle = p.seg_state + items * 64 * 128;
+  p.seg_flag = reinterpret_cast<int*>(p.seg_angle + items * 64);
+  return cudaMemsetAsync(p.seg_flag, 0, items * sizeof(int), ctx->stream);
+}
+
 // Backward of a forward that ran the tensor-core family: one stripe kernel, then the shared
 // per-token / per-head finalisation.
 int tc_backward_call(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* in, uint32_t mask,
@@ -160,7 +178,10 @@ int tc_backward_call(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* i
       return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family needs 16-byte aligned b, c, x, dy and theta");
     }
   }
-  cudaError_t e = m3::tc_backward(ctx->stream, p, d.rot != 0);
+  char* seg = nullptr;
+  cudaError_t e = plan_segments(ctx, p, tiles, !p.use_tma, &seg);
+  if (e == cudaSuccess) e = m3::tc_backward(ctx->stream, p, d.rot != 0);
+  if (seg) cudaFreeAsync(seg, ctx->stream);
   if (e == cudaSuccess) {
     ctx->launches += 1;
     void* ddt = want(M3_GRAD_DT, g->ddt) ? g->ddt : nullptr;
@@ -387,7 +408,11 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
       p.ckpt_h = reinterpret_cast<__nv_bfloat16*>(base);
       p.ckpt_angle = reinterpret_cast<float*>(base + nh * sizeof(__nv_bfloat16));
     }
-    cudaError_t te = m3::tc_forward(ctx->stream, p, d.rot != 0);
+    // a caller that must not allocate gets whole stripes: cutting them needs hand-over scratch
+    char* seg = nullptr;
+    cudaError_t te = plan_segments(ctx, p, m3::tc_tiles(d.T, d.R), !p.use_tma && !ctx->no_scratch, &seg);
+    if (te == cudaSuccess) te = m3::tc_forward(ctx->stream, p, d.rot != 0);
+    if (seg) cudaFreeAsync(seg, ctx->stream);
     if (te != cudaSuccess) {
       if (base) cudaFreeAsync(base, ctx->stream);
       return cuda_fail(ctx, te, "tensor-core forward");

@@ -20,6 +20,7 @@ struct m3_ctx {
   volatile int* err_host = nullptr;
   uint32_t wait_limit = 0;          // iteration limit of the kernels' bounded waits; 0 = the default
   cudaMemPool_t pool = nullptr;     // this context's own scratch pool (freed memory is kept for reuse)
+  bool no_scratch = false;          // set for the span of a call that must not allocate
   char err[512] = {0};
 };
 

@@ -55,7 +55,12 @@ extern "C" int m3_scan_forward_noalloc(m3_ctx* ctx, const m3_scan_desc* desc, co
   if (!out->y) return m3::fail(ctx, M3_ERR_NULL, "y is required");
   // Shapes the tensor-core family serves need no scratch at all when nothing is kept for a backward
   // pass: that call allocates nothing either, and is the fast one.
-  if (m3::tc_supported(*desc) && !d.raw && desc->path != M3_PATH_GENERIC) return m3_scan_forward(ctx, desc, out, nullptr);
+  if (m3::tc_supported(*desc) && !d.raw && desc->path != M3_PATH_GENERIC) {
+    ctx->no_scratch = true;  // whole stripes: no hand-over scratch between time segments
+    const int rc = m3_scan_forward(ctx, desc, out, nullptr);
+    ctx->no_scratch = false;
+    return rc;
+  }
   if (ctx->device < 0 || ctx->device >= kMaxDevices)
     return m3::fail(ctx, M3_ERR_UNSUPPORTED, "device ordinal %d outside the table of %d", ctx->device, kMaxDevices);
   const size_t need = m3::generic_ws_layout(d, nullptr, nullptr);

@@ -48,7 +48,16 @@ struct TcFwdParams {
   int B, T, H, R, disc;
   int rev;            // the last `rev` heads walk time right to left
   uint32_t wait_limit; // iteration limit of the bounded waits (m3_ctx_set_wait_limit)
+  // time segments of a stripe (role-split kernel; work distribution in m3_tc_roles.cuh): nseg == 1 hands nothing over
+  int nseg, tps, grid;
+  float *seg_state, *seg_angle;
+  int* seg_flag;
 };
+
+// How a launch of the role-split kernels cuts its stripes in time: enough items to keep every SM busy to
+// the end (about six per SM), segments of at least four tiles.  Returns segments per stripe, tiles per
+// segment and the grid; bytes of hand-over scratch (state, angle, flags) through *scratch_bytes.
+void tc_segment_plan(int BH, int tiles, bool allow_split, int* nseg, int* tps, int* grid, size_t* scratch_bytes);
 
 cudaError_t tc_forward(cudaStream_t st, const TcFwdParams& p, bool rotational);
 // The direct form (rank 1, real dynamics, use_tma): m3_tc_fwd_direct.cu.
@@ -72,6 +81,9 @@ struct TcBwdParams {
   int B, T, H, R, disc;
   int rev;            // the last `rev` heads walk time right to left
   uint32_t wait_limit;
+  int nseg, tps, grid;   // as in TcFwdParams; the gradient of the state and the running sum of d phi are handed over
+  float *seg_state, *seg_angle;
+  int* seg_flag;
 };
 
 cudaError_t tc_backward(cudaStream_t st, const TcBwdParams& p, bool rotational);

@@ -38,16 +38,7 @@ constexpr uint32_t TM_G = 0, TM_DM = 128, TM_T1 = 256, TM_DH = 384, TM_TAB = 448
 // phase B reuse: dB^ accumulates over G's columns, dX~ and U over dM's.
 constexpr uint32_t TM_DB = 0, TM_DX = 128, TM_U = 192;
 
-#ifdef M3_TC_TIMING
-__device__ long long g_tcb_timing[32];
-#define TICK_INIT long long tick_ = clock64()
-#define TICK(i) do { if (blockIdx.x == 0 && threadIdx.x == 224) { long long c_ = clock64(); g_tcb_timing[i] += c_ - tick_; tick_ = c_; } } while (0)
-#else
-#define TICK_INIT do { } while (0)
-#define TICK(i) do { } while (0)
-#endif
-
-template <int R, bool ROT>
+template <int R, bool ROT, bool SPLIT>
 __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_constant__ TcBwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr int LT = kRows / R;
@@ -80,15 +71,26 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
   // rows; [3]: of its state checkpoint
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_q + 256);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  int* s_ok = reinterpret_cast<int*>(tmem_slot + 1);  // outcome of a hand-over wait, for the epilogue warps
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
   const int T = p.T, H = p.H;
-  // Right-to-left heads: scan position s is time T-1-s, reached with a negative token stride.
-  const bool rev = h >= H - p.rev;
-  const int Hs = rev ? -H : H;
-  auto tok_at = [&](int s) { return ((size_t)b * T + (rev ? T - 1 - s : s)) * H + h; };
   const int ntiles = (T + LT - 1) / LT;
+  // Every role walks the same sequence of tiles: those of this CTA's items, each item's from its last tile
+  // to its first, the items of the last segment first - as two nested loops, so that what belongs to the
+  // item (stripe, head, direction) is invariant where the tiles are walked; `it` counts the tiles this CTA
+  // has gone through and picks barrier phases and scalar sets.  Right-to-left heads: scan position s is
+  // time T-1-s, reached with a negative token stride.
+  // SPLIT: stripes cut in time, a grid of at most one CTA per SM that works through its items.  Otherwise
+  // one CTA per stripe, whose single item is known without a decode and whose loops run once.
+  const int nseg = SPLIT ? p.nseg : 1;
+  const int BH = p.B * H, nitems = BH * nseg;
+  auto item_of = [&](int item) {
+    if (SPLIT) return decode_item(item, BH, H, ntiles, nseg, p.tps, 1);
+    ItemInfo r;
+    r.bh = item; r.b = item / H; r.h = item - r.b * H; r.seg = 0; r.k_lo = 0; r.k_hi = ntiles;
+    return r;
+  };
   const int Tp = ntiles * LT;
   const uint32_t wait_limit = p.wait_limit;
 
@@ -100,7 +102,6 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
     mbar_init(&bars[4], 1);
   }
   if (warp == 0) tmem_alloc(tmem_slot, TM_COLS);
-  if (tid < kNH) s_dcar[tid] = 0.0f;
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
     // --------------------------------------------------------------------------------------------
     // bars[2] counts two arrivals per tile: the rows of B, C and theta, then those of x and dy
     constexpr uint32_t kBcBytes = 2u * RT::bytes(kN) + (ROT ? (uint32_t)LT * kNH * 2u : 0u), kXdyBytes = 2u * RT::bytes(kP);
-    auto request_bc = [&](int kk) {
+    auto request_bc = [&](int b, int h, bool rev, int bh, int kk) {
       if (lane == 0) mbar_expect_tx(&bars[2], kBcBytes);
       __syncwarp();
       const int t0 = kk * LT;
@@ -128,7 +129,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
       }
       __syncwarp();
     };
-    auto request_xdy = [&](int kk) {
+    auto request_xdy = [&](int b, int h, bool rev, int kk) {
       if (lane == 0) mbar_expect_tx(&bars[2], kXdyBytes);
       __syncwarp();
       const int t0 = kk * LT;
@@ -136,44 +137,58 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
       request_raw_tile<R>(l0, rawDY, &p.tm_dy, &bars[2], kP, b, h, T, t0, rev);
       __syncwarp();
     };
-    request_bc(ntiles - 1);
-    request_xdy(ntiles - 1);
-    int requested = 1;
+    int it = 0, requested = 0;
     bool copies_ok = true;
-    for (int it = 0; it < ntiles; ++it) {
-      const int k = ntiles - 1 - it;
-      // the gradients have left their staging buffers: operands, angle table and checkpoint are spent
-      bar_sync(BAR_TAIL, kPairCount);
-      if (k > 0 && copies_ok) {
-        // this tile's copies have landed unless the epilogue warps gave up on them: a barrier is armed
-        // again only once its current phase is complete
-        copies_ok = warp_all(mbar_wait(&bars[2], it & 1) && mbar_wait(&bars[3], it & 1));
-        if (copies_ok) request_bc(k - 1);
-      }
-      bar_sync(BAR_TAIL2, kPairCount);  // the reverse scan of d phi is done with dG's buffer
-      if (k > 0 && copies_ok) {
-        request_xdy(k - 1);
-        ++requested;
+    for (int item = blockIdx.x; SPLIT ? item < nitems : item == (int)blockIdx.x; item += SPLIT ? (int)gridDim.x : 1) {
+      const ItemInfo im = item_of(item);
+      const int b = im.b, h = im.h;
+      const bool rev = h >= H - p.rev;
+      for (int k = im.k_hi - 1; k >= im.k_lo; --k, ++it) {
+        if (it > 0) {
+          // the tile before this one: its gradients have left their staging buffers, so operands, angle table
+          // and checkpoint are spent
+          bar_sync(BAR_TAIL, kPairCount);
+          // its copies have landed unless the epilogue warps gave up on them: a barrier is armed again only
+          // once its current phase is complete
+          if (copies_ok) copies_ok = warp_all(mbar_wait(&bars[2], (it - 1) & 1) && mbar_wait(&bars[3], (it - 1) & 1));
+        }
+        if (copies_ok) request_bc(b, h, rev, im.bh, k);
+        if (it > 0) bar_sync(BAR_TAIL2, kPairCount);  // its reverse scan of d phi is done with dG's buffer
+        if (copies_ok) {
+          request_xdy(b, h, rev, k);
+          ++requested;
+        }
       }
     }
+    if (it > 0) {  // the last tile
+      bar_sync(BAR_TAIL, kPairCount);
+      bar_sync(BAR_TAIL2, kPairCount);
+    }
     // no copy of this CTA may be in flight when it lets go of its shared memory
-    mbar_wait(&bars[2], (requested - 1) & 1);
-    mbar_wait(&bars[3], (requested - 1) & 1);
+    if (requested > 0) {
+      mbar_wait(&bars[2], (requested - 1) & 1);
+      mbar_wait(&bars[3], (requested - 1) & 1);
+    }
   } else if (warp == kScalarWarp) {
     regs_for_helpers();
     // --------------------------------------------------------------------------------------------
-    // Look-ahead warp: the scalars of the it-th tile (tiles run from the last to the first) go into set
-    // it & 1 as soon as the epilogue warps have let go of it.
+    // Look-ahead warp: the scalars of the g-th tile this CTA goes through land in set g & 1 as soon as the
+    // epilogue warps have let go of it.
     // --------------------------------------------------------------------------------------------
-    const float A = -expf(p.a_log[h]);
     ScalarLoads<R> ld;
-    lookahead_load<R>(ld, p.dt, p.lam, p.disc, b, h, H, T, (ntiles - 1) * LT, rev);
-    for (int it = 0; it < ntiles; ++it) {
-      const int k = ntiles - 1 - it;
-      if (it > 0) bar_sync(BAR_FREE, kPairCount);
-      lookahead_scalars<R>(scal_set(it & 1), ld, A, T, k * LT);
-      bar_arrive(bar_ahead(it), kPairCount);
-      if (k > 0) lookahead_load<R>(ld, p.dt, p.lam, p.disc, b, h, H, T, (k - 1) * LT, rev);
+    int it = 0;
+    for (int item = blockIdx.x; SPLIT ? item < nitems : item == (int)blockIdx.x; item += SPLIT ? (int)gridDim.x : 1) {
+      const ItemInfo im = item_of(item);
+      const int b = im.b, h = im.h;
+      const bool rev = h >= H - p.rev;
+      const float A = -expf(p.a_log[h]);
+      lookahead_load<R>(ld, p.dt, p.lam, p.disc, b, h, H, T, (im.k_hi - 1) * LT, rev);
+      for (int k = im.k_hi - 1; k >= im.k_lo; --k, ++it) {
+        if (it > 0) bar_sync(BAR_FREE, kPairCount);
+        lookahead_scalars<R>(scal_set(it & 1), ld, A, T, k * LT);
+        bar_arrive(bar_ahead(it), kPairCount);
+        if (k > im.k_lo) lookahead_load<R>(ld, p.dt, p.lam, p.disc, b, h, H, T, (k - 1) * LT, rev);
+      }
     }
   } else if (warp > kIssuerWarp) {
     regs_for_helpers();  // the idle warp of the helpers' group
@@ -183,7 +198,12 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
     // Issuer: both phases of every tile.
     // --------------------------------------------------------------------------------------------
     bool ckpt_ok = true;
-    for (int it = 0; it < ntiles; ++it) {
+    int total = 0;
+    for (int item = blockIdx.x; SPLIT ? item < nitems : item == (int)blockIdx.x; item += SPLIT ? (int)gridDim.x : 1) {
+      const ItemInfo im = item_of(item);
+      total += im.k_hi - im.k_lo;
+    }
+    for (int it = 0; it < total; ++it) {
       bar_sync(BAR_OPS0, kPairCount);  // X~ and dY~ staged: the two products that need nothing else start now
       if (ckpt_ok) ckpt_ok = warp_all(mbar_wait(&bars[3], it & 1));  // H_k has landed (long ago, as a rule)
       if (lane == 0) {
@@ -218,43 +238,67 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
       __syncwarp();
     }
     // Nothing of this CTA may be in flight when it lets go of its shared memory and TMEM.
-    mbar_wait(&bars[0], (ntiles - 1) & 1);
-    mbar_wait(&bars[1], (ntiles - 1) & 1);
-    mbar_wait(&bars[4], (ntiles - 1) & 1);
+    if (total > 0) {
+      mbar_wait(&bars[0], (total - 1) & 1);
+      mbar_wait(&bars[1], (total - 1) & 1);
+      mbar_wait(&bars[4], (total - 1) & 1);
+    }
   } else {
     regs_for_epilogue();
     // --------------------------------------------------------------------------------------------
     // Epilogue warps.
     // --------------------------------------------------------------------------------------------
-    const float dsk = p.d_skip ? p.d_skip[h] : 0.0f;
     const int quad = warp & 3, ch = warp >> 2;
     const int row = quad * 32 + lane;
     const int rl = row / R, rr = row % R;  // time step within the tile and rank of this thread's row
-
-    // dH^T <- gradient reaching the returned h (or zero)
-#pragma unroll
-    for (int cc = 0; cc < 2; ++cc) {
-      const int p0 = 32 * ch + 16 * cc;
-      float v[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) v[j] = p.dh ? p.dh[((size_t)bh * kP + p0 + j) * kN + row] : 0.0f;
-      tmem_st16(tmem_addr(tm, quad * 32, TM_DH + p0), v);
+    int total = 0;  // tiles this CTA goes through in all
+    for (int item = blockIdx.x; SPLIT ? item < nitems : item == (int)blockIdx.x; item += SPLIT ? (int)gridDim.x : 1) {
+      const ItemInfo im = item_of(item);
+      total += im.k_hi - im.k_lo;
     }
-    tmem_wait_st();
 
     bool dead = false;  // a bounded wait of this warp gave up: it keeps the barriers going, nothing else
-    TICK_INIT;
-    for (int k = ntiles - 1, it = 0; k >= 0; --k, ++it) {
+    int it = 0;
+    for (int item = blockIdx.x; SPLIT ? item < nitems : item == (int)blockIdx.x; item += SPLIT ? (int)gridDim.x : 1) {
+      const ItemInfo im = item_of(item);
+      const int bh = im.bh, b = im.b, h = im.h, seg = im.seg, k_lo = im.k_lo, k_hi = im.k_hi;
+      const bool rev = h >= H - p.rev;
+      const int Hs = rev ? -H : H;
+      auto tok_at = [&](int s) { return ((size_t)b * T + (rev ? T - 1 - s : s)) * H + h; };
+      const float dsk = p.d_skip ? p.d_skip[h] : 0.0f;
+      {
+        // dH^T <- gradient reaching the returned h (or zero) for the stripe's last segment, else what the
+        // segment after this one handed over (bounded wait for its flag); likewise the running sum of d phi
+        const bool seeded = seg + 1 < nseg;
+        if (seeded) {
+          if (tid == 0) *s_ok = wait_flag(p.seg_flag + (size_t)bh * nseg + seg + 1, wait_limit << 4) ? 1 : 0;
+          epi_sync();
+          if (!*s_ok) dead = true;
+        }
+        const float* src = seeded ? p.seg_state + ((size_t)bh * nseg + seg + 1) * kP * kN
+                                  : (p.dh ? p.dh + (size_t)bh * kP * kN : nullptr);
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int p0 = 32 * ch + 16 * cc;
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = src ? __ldcg(src + (size_t)(p0 + j) * kN + row) : 0.0f;
+          tmem_st16(tmem_addr(tm, quad * 32, TM_DH + p0), v);
+        }
+        tmem_wait_st();
+        if (tid < kNH) s_dcar[tid] = seeded ? __ldcg(p.seg_angle + ((size_t)bh * nseg + seg + 1) * kNH + tid) : 0.0f;
+        epi_sync();
+      }
+      for (int k = k_hi - 1; k >= k_lo; --k, ++it) {
       const int t0 = k * LT;
       const size_t tok0 = tok_at(t0);
       const bool last_tile = (k == ntiles - 1);
       const int l_end = T - 1 - t0;  // row of the final token when last_tile
       const TileScalars ts = scal_set(it & 1);
       bar_sync(bar_ahead(it), kPairCount);  // the tile's scalars
-      if (it == 0 && ntiles > 1) epi_signal(BAR_FREE, kPairCount, dead);  // the other set has never been used
+      if (it == 0 && total > 1) epi_signal(BAR_FREE, kPairCount, dead);  // the other set has never been used
       // ---- 1. the tile's rows have been landing since the previous tile let go of the buffers --------
       if (!dead) dead = !warp_all(mbar_wait(&bars[2], it & 1, wait_limit));
-      TICK(0);
       if (ROT) {
         if (!dead)
           epi_angle_table<R>(sTab, s_q, p.ckpt_angle + ((size_t)bh * ntiles + k) * kNH, nullptr, ts.dt, T, t0, rev,
@@ -262,7 +306,6 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
         else
           epi_sync();  // the pass's own barrier
       }
-      TICK(1);
       // ---- 2. operands, converted in place --------------------------------------------------------
       {
         RawBC<R, ROT> raw_bc;
@@ -300,9 +343,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
       fence_async_smem();
       tc_fence_before();
       epi_signal(BAR_OPS, kPairCount, dead);
-      TICK(2);
       if (!dead) dead = !warp_all(mbar_wait(&bars[0], it & 1, wait_limit));
-      TICK(3);
       // ---- 3. epilogue A -------------------------------------------------------------------------
       const float acl = ts.ac[rl];
       const float cd = ts.ac[LT - 1];
@@ -452,10 +493,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
       fence_async_smem();
       tc_fence_before();
       epi_signal(BAR_MID, kPairCount, dead);
-      TICK(4);
       // ---- 4. epilogue B -------------------------------------------------------------------------
       if (!dead) dead = !warp_all(mbar_wait(&bars[1], it & 1, wait_limit));
-      TICK(5);
       const int t = t0 + rl;
       const bool live = t < T;
       const bool at_end = last_tile && rl == l_end;
@@ -584,14 +623,12 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
           finish(gq, sC, sDG, false);    // dG is spent: its buffer stages dC
         }
       }
-      TICK(6);
       epi_sync();
       if (!dead) {
         if (p.dx) copy_out<R, kP>(sHS, p.dx, tok0, Hs, T, t0);
         if (p.db) copy_out<R, kN>(sXw, p.db, tok0, Hs, T, t0);
         if (p.dc) copy_out<R, kN>(sDG, p.dc, tok0, Hs, T, t0);
       }
-      TICK(7);
       epi_sync();
       // every operand and table word of this tile has been read and the gradients have left their staging
       // buffers: the next tile's rows of B and C, its theta rows and its checkpoint may land
@@ -615,7 +652,6 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
           }
         }
       }
-      TICK(8);
       const float dD_tile = epi_sum(dD_part, s_red);  // also orders part_* and sDphi for what follows
       if (tid == 0) p.partD[(size_t)bh * ntiles + k] = dD_tile;
       // ---- 5. reverse cumulative sum of d phi over time -> d theta, and the dt term -----------------
@@ -676,7 +712,6 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
         epi_sync();
       }
       epi_signal(BAR_TAIL2, kPairCount, dead);  // dG's buffer is idle until the next band epilogue: x and dy may land
-      TICK(9);
       // ---- 6. per-token scalars of the tile ---------------------------------------------------------
       if (tid < LT) {
         const int l = tid;
@@ -738,35 +773,53 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
         if (lane == 0) p.partA[(size_t)bh * ntiles + k] = pa;
       }
       // this tile's scalars are spent: the look-ahead warp may overwrite their set
-      if (k >= 2) epi_signal(BAR_FREE, kPairCount, dead);
+      if (it + 2 < total) epi_signal(BAR_FREE, kPairCount, dead);
       epi_sync();
-      TICK(10);
-    }
-    // ---- gradient of the seed state -----------------------------------------------------------------
-    {
-      float first = 0.0f;
-      if (p.h0) {
-        const size_t i0 = tok_at(0);
-        const float l0 = p.disc == 0 ? 1.0f : (p.disc == 1 ? 0.5f : bf(p.lam, i0));
-        first = (1.0f - l0) * bf(p.dt, i0);
       }
-      float ip = 0.0f;
-      tc_fence_after();
+      {
+        // ---- the item's first tile is done: the gradient of the seed state, or the hand-over to the
+        //      segment before this one ------------------------------------------------------------------
+        const bool hand_over = seg > 0;
+        float first = 0.0f;
+        if (!hand_over && p.h0) {
+          const size_t i0 = tok_at(0);
+          const float l0 = p.disc == 0 ? 1.0f : (p.disc == 1 ? 0.5f : bf(p.lam, i0));
+          first = (1.0f - l0) * bf(p.dt, i0);
+        }
+        float ip = 0.0f;
+        if (!dead) {
+          tc_fence_after();
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int p0 = 32 * ch + 16 * cc;
-        float v[16];
-        tmem_ld16(tmem_addr(tm, quad * 32, TM_DH + p0), v);
+          for (int cc = 0; cc < 2; ++cc) {
+            const int p0 = 32 * ch + 16 * cc;
+            float v[16];
+            tmem_ld16(tmem_addr(tm, quad * 32, TM_DH + p0), v);
+            if (hand_over) {
+              float* dst = p.seg_state + ((size_t)bh * nseg + seg) * kP * kN;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const size_t o = ((size_t)bh * kP + p0 + j) * kN + row;
-          if (p.dh0) p.dh0[o] = v[j];
-          if (p.dlu0) p.dlu0[o] = first * v[j];
-          if (p.lu0) ip += v[j] * p.lu0[o];
+              for (int j = 0; j < 16; ++j) __stcg(dst + (size_t)(p0 + j) * kN + row, v[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const size_t o = ((size_t)bh * kP + p0 + j) * kN + row;
+                if (p.dh0) p.dh0[o] = v[j];
+                if (p.dlu0) p.dlu0[o] = first * v[j];
+                if (p.lu0) ip += v[j] * p.lu0[o];
+              }
+            }
+          }
+        }
+        if (hand_over) {
+          if (tid < kNH) __stcg(p.seg_angle + ((size_t)bh * nseg + seg) * kNH + tid, s_dcar[tid]);
+          __threadfence();
+          epi_sync();
+          // raised even by a CTA that gave up, so that nobody waits in vain: the error flag tells the host
+          if (tid == 0) raise_handover(p.seg_flag + (size_t)bh * nseg + seg);
+        } else {
+          const float tot = epi_sum(ip, s_red);
+          if (tid == 0) p.ip0[bh] = tot;
         }
       }
-      const float tot = epi_sum(ip, s_red);
-      if (tid == 0) p.ip0[bh] = tot;
     }
     if (dead && lane == 0 && p.err) raise_flag(p.err);
   }
@@ -777,23 +830,14 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
 
 template <int R>
 cudaError_t launch_r(cudaStream_t st, const TcBwdParams& p, bool rot) {
-  auto kern = rot ? tc_bwd_kernel<R, true> : tc_bwd_kernel<R, false>;
+  auto kern = p.nseg > 1 ? (rot ? tc_bwd_kernel<R, true, true> : tc_bwd_kernel<R, false, true>) : (rot ? tc_bwd_kernel<R, true, false> : tc_bwd_kernel<R, false, false>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return e;
-  kern<<<p.B * p.H, kCtaThreads, kSmemBytes, st>>>(p);
+  kern<<<p.grid, kCtaThreads, kSmemBytes, st>>>(p);
   return cudaGetLastError();
 }
 
 }  // namespace
-
-#ifdef M3_TC_TIMING
-extern "C" void m3_debug_timing_bwd(long long* out, int reset) {
-  long long z[32] = {0};
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, g_tcb_timing, sizeof(z));
-  if (reset) cudaMemcpyToSymbol(g_tcb_timing, z, sizeof(z));
-}
-#endif
 
 cudaError_t tc_backward(cudaStream_t st, const TcBwdParams& p, bool rot) {
   if (p.use_tma && p.R == 1 && !rot) return tc_backward_direct(st, p);

@@ -34,25 +34,14 @@ struct FwdSmem {
   // two sets of per-token scalars, the angle pass's exchange space ([4][64] sums, [64] running angle),
   // then mbarriers and the TMEM slot
   static constexpr uint32_t off_q = off_sc + 2 * kNumScal * kScal * 4;
-  static constexpr uint32_t bytes = off_q + (4 * kNH + kNH) * 4 + 64;
+  static constexpr uint32_t bytes = off_q + (4 * kNH + kNH) * 4 + 64;   // bars, TMEM slot, hand-over outcome
   static_assert(bytes <= 232448, "forward shared memory exceeds the 227 KB a CTA can have");
 };
 constexpr uint32_t TM_G = 0, TM_Y = 128, TM_H = 192, TM_COLS = 256;
 
-// Profiling build (-DM3_TC_TIMING): cycles per phase of CTA 0, accumulated per role, read back with
-// m3_debug_timing.  Compiled out otherwise.
-#ifdef M3_TC_TIMING
-__device__ long long g_tc_timing[32];
-#define TICK_INIT long long tick_ = clock64()
-#define TICK(i) do { if (blockIdx.x == 0 && lane == 0) { long long c_ = clock64(); g_tc_timing[i] += c_ - tick_; tick_ = c_; } } while (0)
-#else
-#define TICK_INIT do { } while (0)
-#define TICK(i) do { } while (0)
-#endif
-
-template <int R, bool ROT>
+template <int R, bool ROT, bool SPLIT>
 __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_constant__ TcFwdParams p) {
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem[];
   using SM = FwdSmem<R>;
   constexpr int LT = kRows / R;  // time steps per tile
   uint8_t *sC = smem + OFF_C, *sB = smem + OFF_B, *sX = smem + OFF_X, *sXw = smem + OFF_XW, *sH = smem + OFF_H;
@@ -69,17 +58,27 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
   // [0], [1]: tensor-core phases; [2]: arrival of a tile's raw rows of B and C; [3]: of its theta rows
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_carry + kNH);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  int* s_ok = reinterpret_cast<int*>(tmem_slot + 1);  // outcome of a hand-over wait, for the epilogue warps
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
   const int T = p.T, H = p.H;
-  // A head that walks right to left sees scan position s at time T-1-s: its rows are reached
-  // with a negative token stride, everything else (tiles, scalars, checkpoints) is in scan order.
-  const bool rev = h >= H - p.rev;
-  const int Hs = rev ? -H : H;
-  auto tok_at = [&](int s) { return ((size_t)b * T + (rev ? T - 1 - s : s)) * H + h; };
   const int ntiles = (T + LT - 1) / LT;
   const uint32_t wait_limit = p.wait_limit;
+  // Every role walks the same sequence of tiles: the tiles of this CTA's items, one item after the other,
+  // as two nested loops, so that what belongs to the item (stripe, head, direction) is invariant where the
+  // tiles are walked; g counts the tiles this CTA has gone through and picks barrier phases and scalar sets.
+  // A head that walks right to left sees scan position s at time T-1-s: its rows are reached with a
+  // negative token stride, everything else (tiles, scalars, checkpoints) is in scan order.
+  // SPLIT: stripes cut in time, a grid of at most one CTA per SM that works through its items.  Otherwise
+  // one CTA per stripe, whose single item is known without a decode and whose loops run once.
+  const int nseg = SPLIT ? p.nseg : 1;
+  const int BH = p.B * H, nitems = BH * nseg;
+  auto item_of = [&](int item) {
+    if (SPLIT) return decode_item(item, BH, H, ntiles, nseg, p.tps, 0);
+    ItemInfo r;
+    r.bh = item; r.b = item / H; r.h = item - r.b * H; r.seg = 0; r.k_lo = 0; r.k_hi = ntiles;
+    return r;
+  };
 
   if (tid == 0) {
     mbar_init(&bars[0], 1);
@@ -97,68 +96,64 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
   if (warp == kCopyWarp) {
     regs_for_helpers();
     // --------------------------------------------------------------------------------------------
-    // Copy warp: the raw rows of tile k + 1 are requested as soon as tile k is staged (staging buffers
-    // and angle table spent), one request per lane; theta rows land at the start of the table's buffer.
+    // Copy warp: the raw rows of a tile - the next item's first one included - are requested as soon as
+    // the tile before it is staged (staging buffers and angle table spent), one request per lane; theta
+    // rows land at the start of the table's buffer.
     // --------------------------------------------------------------------------------------------
-#ifdef M3_TC_TIMING
-    long long acc_issue = 0, acc_land = 0;
-#endif
-    auto request_rows = [&](int kk) {
-      if (lane == 0) {
-        mbar_expect_tx(&bars[2], 2u * SM::kRaw);
-        if (ROT) mbar_expect_tx(&bars[3], SM::kTheta);
-      }
-      __syncwarp();
-#ifdef M3_TC_TIMING
-      long long c0_ = clock64();
-#endif
-      int l0 = request_raw_tile<R>(0, rawB, &p.tm_b, &bars[2], kN, b, h, T, kk * LT, rev);
-      l0 += request_raw_tile<R>(l0, rawC, &p.tm_c, &bars[2], kN, b, h, T, kk * LT, rev);
-      if (ROT && lane == l0) tma_load_rows(sTab, &p.tm_th, &bars[3], 0, h, rev ? T - kk * LT - LT : kk * LT, b);
-      __syncwarp();
-#ifdef M3_TC_TIMING
-      long long c1_ = clock64();
-      acc_issue += c1_ - c0_;
-      mbar_wait(&bars[2], kk & 1);
-      acc_land += clock64() - c1_;
-#endif
-    };
-    request_rows(0);
-    int requested = 1;
+    int g = 0, requested = 0;
     bool copies_ok = true;
-    for (int k = 0; k < ntiles; ++k) {
-      bar_sync(BAR_OPS, kEpiThreads + 64);
-      if (k + 1 < ntiles && copies_ok) {
-        // tile k's rows have landed unless the epilogue warps gave up on them: a barrier is armed
-        // again only once its current phase is complete
-        copies_ok = warp_all(mbar_wait(&bars[2], k & 1) && (!ROT || mbar_wait(&bars[3], k & 1)));
+    for (int item = blockIdx.x; SPLIT ? item < nitems : item == (int)blockIdx.x; item += SPLIT ? (int)gridDim.x : 1) {
+      const ItemInfo it = item_of(item);
+      const int b = it.b, h = it.h;
+      const bool rev = h >= H - p.rev;
+      for (int k = it.k_lo; k < it.k_hi; ++k, ++g) {
+        if (g > 0) {
+          bar_sync(BAR_OPS, kEpiThreads + 64);  // the tile before this one is staged
+          // its rows have landed unless the epilogue warps gave up on them: a barrier is armed again only
+          // once its current phase is complete
+          if (copies_ok) copies_ok = warp_all(mbar_wait(&bars[2], (g - 1) & 1) && (!ROT || mbar_wait(&bars[3], (g - 1) & 1)));
+        }
         if (copies_ok) {
-          request_rows(k + 1);
-          requested = k + 2;
+          if (lane == 0) {
+            mbar_expect_tx(&bars[2], 2u * SM::kRaw);
+            if (ROT) mbar_expect_tx(&bars[3], SM::kTheta);
+          }
+          __syncwarp();
+          int l0 = request_raw_tile<R>(0, rawB, &p.tm_b, &bars[2], kN, b, h, T, k * LT, rev);
+          l0 += request_raw_tile<R>(l0, rawC, &p.tm_c, &bars[2], kN, b, h, T, k * LT, rev);
+          if (ROT && lane == l0) tma_load_rows(sTab, &p.tm_th, &bars[3], 0, h, rev ? T - k * LT - LT : k * LT, b);
+          __syncwarp();
+          ++requested;
         }
       }
     }
+    if (g > 0) bar_sync(BAR_OPS, kEpiThreads + 64);  // the last tile
     // no copy of this CTA may be in flight when it lets go of its shared memory
-    mbar_wait(&bars[2], (requested - 1) & 1);
-    if (ROT) mbar_wait(&bars[3], (requested - 1) & 1);
-#ifdef M3_TC_TIMING
-    if (blockIdx.x == 0 && lane == 0) { g_tc_timing[12] += acc_issue; g_tc_timing[13] += acc_land; }
-#endif
+    if (requested > 0) {
+      mbar_wait(&bars[2], (requested - 1) & 1);
+      if (ROT) mbar_wait(&bars[3], (requested - 1) & 1);
+    }
   } else if (warp == kScalarWarp) {
     regs_for_helpers();
     // --------------------------------------------------------------------------------------------
-    // Look-ahead warp: the scalars of tile j go into set j & 1 as soon as the epilogue warps have let
-    // go of it (BAR_FREE), and are announced on BAR_AHEAD; dt and lambda of tile j + 1 are requested
-    // right away and wait in registers.
+    // Look-ahead warp: the scalars of the g-th tile go into set g & 1 as soon as the epilogue warps have
+    // let go of it (BAR_FREE), and are announced on BAR_AHEAD; dt and lambda of the item's next tile are
+    // requested right away and wait in registers.
     // --------------------------------------------------------------------------------------------
-    const float A = -expf(p.a_log[h]);
     ScalarLoads<R> ld;
-    lookahead_load<R>(ld, p.dt, p.lam, p.disc, b, h, H, T, 0, rev);
-    for (int j = 0; j < ntiles; ++j) {
-      if (j > 0) bar_sync(BAR_FREE, kPairCount);
-      lookahead_scalars<R>(scal_set(j & 1), ld, A, T, j * LT);
-      bar_arrive(bar_ahead(j), kPairCount);
-      if (j + 1 < ntiles) lookahead_load<R>(ld, p.dt, p.lam, p.disc, b, h, H, T, (j + 1) * LT, rev);
+    int g = 0;
+    for (int item = blockIdx.x; SPLIT ? item < nitems : item == (int)blockIdx.x; item += SPLIT ? (int)gridDim.x : 1) {
+      const ItemInfo it = item_of(item);
+      const int b = it.b, h = it.h;
+      const bool rev = h >= H - p.rev;
+      const float A = -expf(p.a_log[h]);
+      lookahead_load<R>(ld, p.dt, p.lam, p.disc, b, h, H, T, it.k_lo * LT, rev);
+      for (int k = it.k_lo; k < it.k_hi; ++k, ++g) {
+        if (g > 0) bar_sync(BAR_FREE, kPairCount);
+        lookahead_scalars<R>(scal_set(g & 1), ld, A, T, k * LT);
+        bar_arrive(bar_ahead(g), kPairCount);
+        if (k + 1 < it.k_hi) lookahead_load<R>(ld, p.dt, p.lam, p.disc, b, h, H, T, (k + 1) * LT, rev);
+      }
     }
   } else if (warp > kIssuerWarp) {
     regs_for_helpers();  // the idle warp of the helpers' group
@@ -167,10 +162,11 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
     // --------------------------------------------------------------------------------------------
     // Issuer: both groups of products of every tile, and the state checkpoint.
     // --------------------------------------------------------------------------------------------
-    TICK_INIT;
-    for (int k = 0; k < ntiles; ++k) {
-      bar_sync(BAR_OPS, kEpiThreads + 64);  // operands of tile k staged
-      TICK(16);
+    int done = 0;
+    for (int item = blockIdx.x; SPLIT ? item < nitems : item == (int)blockIdx.x; item += SPLIT ? (int)gridDim.x : 1) {
+      const ItemInfo it = item_of(item);
+      for (int k = it.k_lo; k < it.k_hi; ++k, ++done) {
+      bar_sync(BAR_OPS, kEpiThreads + 64);  // operands of the tile staged
       if (lane == 0) {
         tc_fence_after();
         const Operand aC = k_major(smem_u32(sC), kN);
@@ -180,14 +176,12 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
         if (p.ckpt_h) {
           // the bf16 state entering this tile, for the backward pass: one contiguous 16 KB bulk copy out of
           // the state's operand copy, which is next written after the second group of products
-          bulk_store(p.ckpt_h + ((size_t)bh * ntiles + k) * kN * kP, sH, kN * kP * 2);
+          bulk_store(p.ckpt_h + ((size_t)it.bh * ntiles + k) * kN * kP, sH, kN * kP * 2);
           bulk_commit();
         }
       }
       __syncwarp();
-      TICK(17);
       bar_sync(BAR_MID, kPairCount);  // M = G o band staged; decays applied
-      TICK(19);
       if (lane == 0) {
         if (p.ckpt_h) bulk_wait_read();  // the checkpoint has left the state's bf16 copy
         tc_fence_after();
@@ -196,75 +190,104 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
         umma_commit(&bars[1]);
       }
       __syncwarp();
-      TICK(20);
+      }
     }
     // Nothing of this CTA may be in flight when it lets go of its shared memory and TMEM.
-    mbar_wait(&bars[0], (ntiles - 1) & 1);
-    mbar_wait(&bars[1], (ntiles - 1) & 1);
+    if (done > 0) {
+      mbar_wait(&bars[0], (done - 1) & 1);
+      mbar_wait(&bars[1], (done - 1) & 1);
+    }
     if (lane == 0) bulk_wait_all();
   } else {
     regs_for_epilogue();
     // --------------------------------------------------------------------------------------------
     // Epilogue warps.
     // --------------------------------------------------------------------------------------------
-    const float dsk = p.d_skip ? p.d_skip[h] : 0.0f;
     const int quad = warp & 3, ch = warp >> 2;
     const int row = quad * 32 + lane;
-    // ---- seed state: H^T[n][p] in TMEM and its bf16 copy [p][n] in shared memory
-    {
-      float first = 0.0f;
-      if (p.h0) {
-        const size_t i0 = tok_at(0);
-        const float l0 = p.disc == 0 ? 1.0f : (p.disc == 1 ? 0.5f : bf(p.lam, i0));
-        first = (1.0f - l0) * bf(p.dt, i0);
-      }
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int p0 = 32 * ch + 16 * cc;
-        float v[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float s = 0.0f;
-          if (p.h0) {
-            const size_t o = ((size_t)bh * kP + (p0 + j)) * kN + row;
-            s = p.h0[o] + first * p.lu0[o];
-          }
-          v[j] = s;
-          *reinterpret_cast<__nv_bfloat16*>(sH + tile_off(p0 + j, row, kN)) = __float2bfloat16_rn(s);
-        }
-        tmem_st16(tmem_addr(tm, quad * 32, TM_H + p0), v);
-      }
-      tmem_wait_st();
-    }
-    if (ROT && tid < kNH) s_carry[tid] = p.angle0 ? p.angle0[(size_t)bh * kNH + tid] : 0.0f;
     bool dead = false;  // a bounded wait of this warp gave up: it keeps the barriers going, nothing else
-    RawPX<R> raw_x;     // x of the next tile travels in registers
-    issue_px<R>(raw_x, p.x, tok_at(0), Hs, T, 0);
-    // The angle table of tile j from its theta rows and its scalars (which this call waits for).
-    auto angle_table = [&](int j) {
-      bar_sync(bar_ahead(j), kPairCount);  // scalars of tile j
+    // The angle table of tile kk of stripe sbh, the gg-th tile of this CTA, from its theta rows and its
+    // scalars (which this call waits for).
+    auto angle_table = [&](int gg, int sbh, int kk, bool srev) {
+      bar_sync(bar_ahead(gg), kPairCount);  // scalars of the tile
       if (ROT) {
-        if (!dead) dead = !warp_all(mbar_wait(&bars[3], j & 1, wait_limit));
+        if (!dead) dead = !warp_all(mbar_wait(&bars[3], gg & 1, wait_limit));
         if (!dead)
-          epi_angle_table<R>(sTab, s_q, s_carry, s_carry, scal_set(j & 1).dt, T, j * LT, rev,
-                             p.ckpt_angle ? p.ckpt_angle + ((size_t)bh * ntiles + j) * kNH : nullptr,
-                             p.angle_out ? p.angle_out + (size_t)bh * kNH : nullptr);
+          epi_angle_table<R>(sTab, s_q, s_carry, s_carry, scal_set(gg & 1).dt, T, kk * LT, srev,
+                             p.ckpt_angle ? p.ckpt_angle + ((size_t)sbh * ntiles + kk) * kNH : nullptr,
+                             p.angle_out ? p.angle_out + (size_t)sbh * kNH : nullptr);
         else
           epi_sync();  // the pass's own barrier
       }
     };
-    angle_table(0);
-    if (ntiles > 1) epi_signal(BAR_FREE, kPairCount, dead);  // set 1 has never been used
-    epi_sync();
-    TICK_INIT;
-    for (int k = 0; k < ntiles; ++k) {
+    RawPX<R> raw_x;     // x of the next tile travels in registers
+    int total = 0;      // tiles this CTA goes through in all
+    for (int item = blockIdx.x; SPLIT ? item < nitems : item == (int)blockIdx.x; item += SPLIT ? (int)gridDim.x : 1) {
+      const ItemInfo it = item_of(item);
+      total += it.k_hi - it.k_lo;
+    }
+    int g = 0;
+    for (int item = blockIdx.x; SPLIT ? item < nitems : item == (int)blockIdx.x; item += SPLIT ? (int)gridDim.x : 1) {
+      const ItemInfo it = item_of(item);
+      const int bh = it.bh, b = it.b, h = it.h, seg = it.seg, k_lo = it.k_lo, k_hi = it.k_hi;
+      const bool rev = h >= H - p.rev;
+      const int Hs = rev ? -H : H;
+      // token-head index (row of a [B, T, H, ...] tensor) of scan position 0; position s is s * Hs rows further
+      const size_t tok_base = ((size_t)b * T + (rev ? T - 1 : 0)) * H + h;
+      auto tok_at = [&](int s) { return tok_base + (size_t)((ptrdiff_t)s * Hs); };
+      const float dsk = p.d_skip ? p.d_skip[h] : 0.0f;
+      const bool hand_over = seg + 1 < nseg;
+      // ---- the item's first tile: the state and the running angle start from the caller's (first segment)
+      //      or from what the previous segment handed over (bounded wait for its flag); the tile's angle
+      //      table, which every later tile has ready from its predecessor's step 3 ----------------------------
+      {
+        issue_px<R>(raw_x, p.x, tok_at(k_lo * LT), Hs, T, k_lo * LT);
+        if (seg > 0) {
+          if (tid == 0) *s_ok = wait_flag(p.seg_flag + (size_t)bh * nseg + seg - 1, wait_limit << 4) ? 1 : 0;
+          epi_sync();
+          if (!*s_ok) dead = true;
+        }
+        if (ROT && tid < kNH)
+          s_carry[tid] = seg > 0 ? __ldcg(p.seg_angle + ((size_t)bh * nseg + seg - 1) * kNH + tid)
+                                 : (p.angle0 ? p.angle0[(size_t)bh * kNH + tid] : 0.0f);
+        epi_sync();
+        angle_table(g, bh, k_lo, rev);
+        if (g == 0 && total > 1) epi_signal(BAR_FREE, kPairCount, dead);  // set 1 has never been used
+        epi_sync();
+        const float* src = seg > 0 ? p.seg_state + ((size_t)bh * nseg + seg - 1) * kP * kN
+                                   : (p.h0 ? p.h0 + (size_t)bh * kP * kN : nullptr);
+        float first = 0.0f;
+        if (seg == 0 && p.h0) {
+          const size_t i0 = tok_at(0);
+          const float l0 = p.disc == 0 ? 1.0f : (p.disc == 1 ? 0.5f : bf(p.lam, i0));
+          first = (1.0f - l0) * bf(p.dt, i0);
+        }
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int p0 = 32 * ch + 16 * cc;
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float s_ = 0.0f;
+            if (src) {
+              const size_t o = (size_t)(p0 + j) * kN + row;
+              s_ = __ldcg(src + o);
+              if (seg == 0) s_ += first * p.lu0[(size_t)bh * kP * kN + o];
+            }
+            v[j] = s_;
+            *reinterpret_cast<__nv_bfloat16*>(sH + tile_off(p0 + j, row, kN)) = __float2bfloat16_rn(s_);
+          }
+          tmem_st16(tmem_addr(tm, quad * 32, TM_H + p0), v);
+        }
+        tmem_wait_st();
+      }
+      for (int k = k_lo; k < k_hi; ++k, ++g) {
       const int t0 = k * LT;
-      const TileScalars ts = scal_set(k & 1);
+      const TileScalars ts = scal_set(g & 1);
       float *s_ac = ts.ac, *s_eac = ts.eac;
       const size_t tok0 = tok_at(t0);  // token-head index of l = 0 (stride Hs per step)
       // ---- 1. stage the operands ---------------------------------------------------------------
-      if (!dead) dead = !warp_all(mbar_wait(&bars[2], k & 1, wait_limit));
-      if (warp == 7) TICK(1);
+      if (!dead) dead = !warp_all(mbar_wait(&bars[2], g & 1, wait_limit));
       if (!dead) {
         convert_bc<R, ROT>(rawB, rawC, sB, sC, sTab, rev);
         commit_px<R>(raw_x, sX, sXw, ts.sw);
@@ -272,11 +295,9 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
       fence_async_smem();
       tc_fence_before();
       epi_signal(BAR_OPS, kEpiThreads + 64, dead);
-      if (warp == 7) TICK(2);
-      if (!dead && k + 1 < ntiles) issue_px<R>(raw_x, p.x, tok0 + (size_t)LT * Hs, Hs, T, t0 + LT);
+      if (!dead && k + 1 < k_hi) issue_px<R>(raw_x, p.x, tok0 + (size_t)LT * Hs, Hs, T, t0 + LT);
       // ---- 2. band, decays ---------------------------------------------------------------------
-      if (!dead) dead = !warp_all(mbar_wait(&bars[0], k & 1, wait_limit));
-      if (warp == 7) TICK(3);
+      if (!dead) dead = !warp_all(mbar_wait(&bars[0], g & 1, wait_limit));
       if (!dead) {
         tc_fence_after();
         const int l = row / R;
@@ -356,13 +377,12 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
       fence_async_smem();
       tc_fence_before();
       epi_signal(BAR_MID, kPairCount, dead);
-      if (warp == 7) TICK(4);
-      // ---- 3. the next tile's angle table, while the second group of products runs -------------------
-      if (k + 1 < ntiles) angle_table(k + 1);
-      if (warp == 7) TICK(0);
+      // ---- 3. the next tile's angle table, while the second group of products runs (a tile that opens an
+      //         item builds its own: its predecessor, which may be this very item, must have handed over) ---
+      if (k + 1 < k_hi) angle_table(g + 1, bh, k + 1, rev);
       // ---- 4. outputs ----------------------------------------------------------------------------
-      if (!dead) dead = !warp_all(mbar_wait(&bars[1], k & 1, wait_limit));
-      if (warp == 7) TICK(5);
+      const bool hands = hand_over && k + 1 == k_hi;
+      if (!dead) dead = !warp_all(mbar_wait(&bars[1], g & 1, wait_limit));
       if (!dead) {
         tc_fence_after();
         float yv[2][16], hv[2][16];
@@ -400,31 +420,39 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
 #pragma unroll
             for (int j = 0; j < 16; ++j) p.h_out[((size_t)bh * kP + p0 + j) * kN + row] = hv[cc][j];
           }
+          if (hands) {  // the state leaving this segment, for whichever CTA runs the next one
+            float* dst = p.seg_state + ((size_t)bh * nseg + seg) * kP * kN;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) __stcg(dst + (size_t)(p0 + j) * kN + row, hv[cc][j]);
+          }
         }
         if (k == ntiles - 1 && p.lu_out) {
           // last_u = sum_r x_{T-1}^(r) (x) B^_{T-1}^(r), from the staged operands (scan.rs:621-638)
           const int ll = T - 1 - t0;
           for (int e = tid; e < kP * kN; e += kEpiThreads) {
-            const int pp = e / kN, n = e % kN;
-            float s = 0.0f;
+            const int pp = e / kN, nn = e % kN;
+            float s_ = 0.0f;
 #pragma unroll
             for (int rr = 0; rr < R; ++rr) {
               const float xv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sX + tile_off(ll * R + rr, pp, kP)));
-              const float bv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sB + tile_off(ll * R + rr, n, kN)));
-              s += xv * bv;
+              const float bv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sB + tile_off(ll * R + rr, nn, kN)));
+              s_ += xv * bv;
             }
-            p.lu_out[(size_t)bh * kP * kN + e] = s;
+            p.lu_out[(size_t)bh * kP * kN + e] = s_;
           }
         }
       }
-      if (warp == 7) TICK(6);
-      // this tile's scalars are spent: the look-ahead warp may overwrite their set with tile k + 2's
-      if (k + 2 < ntiles) epi_signal(BAR_FREE, kPairCount, dead);
+      // this tile's scalars are spent: the look-ahead warp may overwrite their set with those of the tile after next
+      if (g + 2 < total) epi_signal(BAR_FREE, kPairCount, dead);
+      if (hands) {
+        if (ROT && tid < kNH) __stcg(p.seg_angle + ((size_t)bh * nseg + seg) * kNH + tid, s_carry[tid]);
+        __threadfence();
+      }
       epi_sync();
-      if (warp == 7) TICK(7);
       if (!dead) copy_out<R, kP>(sXw, p.y, tok0, Hs, T, t0);
+      if (hands && tid == 0) raise_handover(p.seg_flag + (size_t)bh * nseg + seg);  // even if this CTA gave up: nobody waits in vain
       epi_sync();
-      if (warp == 7) TICK(8);
+      }
     }
     if (dead && lane == 0 && p.err) raise_flag(p.err);
   }
@@ -435,24 +463,37 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
 
 template <int R>
 cudaError_t launch_r(cudaStream_t st, const TcFwdParams& p, bool rot) {
-  auto kern = rot ? tc_fwd_kernel<R, true> : tc_fwd_kernel<R, false>;
+  auto kern = p.nseg > 1 ? (rot ? tc_fwd_kernel<R, true, true> : tc_fwd_kernel<R, false, true>) : (rot ? tc_fwd_kernel<R, true, false> : tc_fwd_kernel<R, false, false>);
   constexpr uint32_t bytes = FwdSmem<R>::bytes;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
   if (e != cudaSuccess) return e;
-  kern<<<p.B * p.H, kCtaThreads, bytes, st>>>(p);
+  kern<<<p.grid, kCtaThreads, bytes, st>>>(p);
   return cudaGetLastError();
 }
 
 }  // namespace
 
-#ifdef M3_TC_TIMING
-extern "C" void m3_debug_timing(long long* out, int reset) {
-  long long z[32] = {0};
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, g_tc_timing, sizeof(z));
-  if (reset) cudaMemcpyToSymbol(g_tc_timing, z, sizeof(z));
+void tc_segment_plan(int BH, int tiles, bool allow_split, int* nseg, int* tps, int* grid, size_t* scratch_bytes) {
+  static const int sms = [] {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;
+    return n;
+  }();
+  int want = 1;
+  // Segments of one stripe run one after the other, so cutting adds no parallelism: it only evens out the
+  // last round when there are more stripes than SMs.
+  while (allow_split && BH > sms && (long long)BH * want < 6LL * sms && tiles / (want * 2) >= 4) want *= 2;
+  const int per = (tiles + want - 1) / want;
+  const int n = (tiles + per - 1) / per;
+  *nseg = n;
+  *tps = per;
+  // whole stripes: one CTA each, handed out by the hardware; cut stripes: one CTA per SM at most, each
+  // working through its items in order
+  const long long items = (long long)BH * n;
+  *grid = n == 1 ? BH : (int)(items < sms ? items : sms);
+  if (scratch_bytes)
+    *scratch_bytes = n > 1 ? (size_t)BH * n * ((size_t)kP * kN * 4 + kNH * 4 + 4) : 0;
 }
-#endif
 
 cudaError_t tc_forward(cudaStream_t st, const TcFwdParams& p, bool rot) {
   if (p.use_tma && p.R == 1 && !rot) return tc_forward_direct(st, p);

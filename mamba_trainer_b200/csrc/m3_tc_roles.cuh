@@ -64,6 +64,47 @@ __device__ __forceinline__ void epi_signal(int id, int count, bool dead) {
 __device__ __forceinline__ void regs_for_epilogue() { asm volatile("setmaxnreg.inc.sync.aligned.u32 232;"); }
 __device__ __forceinline__ void regs_for_helpers() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
 
+// ---------------------------------------------------------------------------------------
+// Work distribution.  A stripe (one batch row x head) is cut in time into `nseg` segments of `tps` tiles;
+// an item is one segment of one stripe, numbered segment-major (all first segments, then all second ones
+// ...; the backward pass starts from the last segment), and CTA c works through the items c, c + grid,
+// c + 2 grid ... in that order.  A segment takes the state its predecessor left in global memory (fp32
+// state, running angle; in the backward pass the state's gradient and the running sum of d phi) once that
+// predecessor has raised its flag.  Items are handed out in dependency order and every CTA takes its own
+// in increasing order, so the item a CTA waits for was always started before the one that waits; the wait
+// is bounded all the same.  With one segment per stripe nothing is handed over at all.
+// ---------------------------------------------------------------------------------------
+// What an item number stands for.  Kept out of line: it runs once per item and role and divides twice
+// (the kernels' code size is what their instruction fetch pays for).
+struct ItemInfo {
+  int bh, b, h, seg, k_lo, k_hi;
+};
+static __device__ __noinline__ ItemInfo decode_item(int item, int BH, int H, int ntiles, int nseg, int tps, int backward) {
+  ItemInfo r;
+  const int s = item / BH;
+  r.seg = backward ? nseg - 1 - s : s;
+  r.bh = item - s * BH;
+  r.b = r.bh / H;
+  r.h = r.bh - r.b * H;
+  r.k_lo = r.seg * tps;
+  r.k_hi = min(ntiles, r.k_lo + tps);
+  return r;
+}
+
+// One thread's bounded wait for a hand-over flag (with back-off: the producer is another CTA).
+__device__ __forceinline__ bool wait_flag(const int* flag, uint32_t limit) {
+  for (uint32_t it = 1; it < limit; ++it) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v) return true;
+    __nanosleep(it < 64 ? 100 : 1000);
+  }
+  return false;
+}
+__device__ __forceinline__ void raise_handover(int* flag) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(1) : "memory");
+}
+
 // true if every lane's wait succeeded (tcgen05.ld is warp-collective, so a warp gives up as one)
 __device__ __forceinline__ bool warp_all(bool ok) { return __all_sync(0xffffffffu, ok); }
 

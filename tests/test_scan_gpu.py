@@ -405,6 +405,38 @@ def test_tensor_core_backward(rank, rot, seq, state, disc):
     compare_all(t, w.chunk, check_bf16, True, ds, discretization=disc, path=2)
 
 
+@pytest.mark.parametrize("rank,rot,seq,rev", [(2, True, 1000, 1), (1, True, 1100, 0), (4, False, 520, 0), (2, False, 1000, 32)])
+def test_time_segments_leave_results_unchanged(rank, rot, seq, rev):
+    """With more stripes than SMs the kernels cut every stripe into time segments, possibly run by different
+    CTAs, which hand the fp32 state (backward: its gradient) and the running angle over in global memory.
+    The arithmetic and its order are those of whole stripes, so the results are identical: 160 stripes in one
+    call (cut) against the same rows in calls of 64 and 96 stripes (never cut)."""
+    w = tc_workload(rank, rot, seq, batch=5, heads=32)
+    t = synthetic.make_inputs(w, seed=seq + rank, with_state=True)
+    g = torch.Generator().manual_seed(seq)
+    ds = {"h": torch.randn(w.batch, w.heads, 64, 128, generator=g) * 0.1,
+          "last_u": torch.randn(w.batch, w.heads, 64, 128, generator=g) * 0.1,
+          "angle": torch.randn(w.batch, w.heads, 64, generator=g) * 0.1 if rot else None}
+    y, st, gr = fused_run(t, w.chunk, True, True, ds, path=2, reverse_heads=rev)
+    per_head = ("a_log", "d_skip")
+    sums = {}
+    for lo, hi in ((0, 2), (2, 5)):
+        tp = {k: (v if (v is None or k in per_head) else v[lo:hi]) for k, v in t.items()}
+        dp = {k: (v if v is None else v[lo:hi]) for k, v in ds.items()}
+        yp, sp, gp = fused_run(tp, w.chunk, True, True, dp, path=2, reverse_heads=rev)
+        assert torch.equal(y[lo:hi], yp), "y"
+        assert torch.equal(st.h[lo:hi], sp.h) and torch.equal(st.last_u[lo:hi], sp.last_u), "state"
+        if rot:
+            assert torch.equal(st.angle[lo:hi], sp.angle), "angle"
+        for n, v in gp.items():
+            if n in per_head:
+                sums[n] = sums.get(n, 0) + v.double()
+            else:
+                assert torch.equal(gr[n][lo:hi], v), n
+    for n, v in sums.items():
+        assert torch.allclose(gr[n].double(), v, rtol=1e-4, atol=1e-4), n
+
+
 # ---- bidirectional mixer: the last heads walk right to left (models/mamba3.rs:352-370, :548-556) -----
 
 @pytest.mark.parametrize("B,T,H,P,N,R,L,rot,state,rev", [
