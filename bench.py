@@ -128,10 +128,11 @@ def cpu_sample_shape(w):
     carries over), short enough that a forward + backward takes seconds.  Small workloads run whole."""
     if w.tokens * w.heads * w.rank * w.rank <= 8 * 2048 * 12:
         return w, "the whole workload"
-    heads = min(w.heads, 8)
-    seq = min(w.seq, 2048)
-    sw = w.scaled(batch=1, heads=heads, seq=seq)
-    note = f"batch 1 x seq {seq} x {heads} of {w.heads} heads, scaled by batch x heads"
+    heads = min(w.heads, 16)
+    seq = min(w.seq, 4096)
+    batch = min(w.batch, 2)
+    sw = w.scaled(batch=batch, heads=heads, seq=seq)
+    note = f"batch {batch} x seq {seq} x {heads} of {w.heads} heads, scaled by batch x heads"
     if seq < w.seq:
         note += (f"; the sequence is cut from {w.seq} to {seq}, which flatters the CPU: the reference's inter-chunk "
                  "pass costs O(chunks^2) per sequence")
@@ -305,6 +306,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", type=int, default=0, help="0 auto, 1 generic, 2 tensor-core")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's global batch (profiling of a small case)")
+    ap.add_argument("--seq", type=int, default=0, help="override the workload's sequence length (profiling of a small case)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--mixer-core", action="store_true", help="add the secondary mixer-core figure")
@@ -315,13 +317,19 @@ def main():
     gw = global_workload(args.config)
     if args.batch:
         gw = gw.scaled(batch=args.batch)
+    if args.seq:
+        gw = gw.scaled(seq=args.seq)
     if args.impl == "reference":
         run_reference(args, gw, rank)
         return
 
     from mamba_trainer_b200.ssm import Context
+    from mamba_trainer_b200.host_pipeline import bind_host_thread_near
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # one process per GPU: keep this one, and the pinned staging buffers it will allocate, on the GPU's side
+    # of the box (matters for the end-to-end leg once several ranks copy at the same time)
+    numa = bind_host_thread_near(dev)
     dist = None
     if world > 1:
         import torch.distributed as dist_
@@ -469,6 +477,27 @@ def main():
             for out in flying:
                 pipe.wait(out)
 
+        # the two PCIe directions on their own (1 GiB each way, every rank at the same time): what the
+        # end-to-end figure is made of
+        def copy_rate(dst, src):
+            barrier()
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dst.copy_(src, non_blocking=True)
+            torch.cuda.synchronize()
+            c0.record()
+            for _ in range(3):
+                dst.copy_(src, non_blocking=True)
+            c1.record()
+            torch.cuda.synchronize()
+            r = torch.tensor([3 * src.numel() / (c0.elapsed_time(c1) * 1e-3) / 1e9], device=dev)
+            if dist is not None:
+                dist.all_reduce(r, op=dist.ReduceOp.MIN)
+            return float(r)
+        probe_h = torch.empty(1 << 30, dtype=torch.uint8).pin_memory()
+        probe_d = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+        h2d_gbs, d2h_gbs = copy_rate(probe_d, probe_h), copy_rate(probe_h, probe_d)
+        del probe_h, probe_d
+
         e2e_steps(2)
         barrier()
         e_steps = max(3, min(args.steps, 6))
@@ -482,7 +511,9 @@ def main():
             dist.all_reduce(ems, op=dist.ReduceOp.MAX)
         e2e_value = world * eb * w.seq / (float(ems) / e_steps * 1e-3) / 1e6
         e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "sequences_per_step_per_gpu": eb, "steps": e_steps}
+               "sequences_per_step_per_gpu": eb, "steps": e_steps,
+               "pcie_gbs_per_gpu": {"h2d": h2d_gbs, "d2h": d2h_gbs, "note": "slowest rank, all ranks copying at once"},
+               "host_numa": numa}
 
     if rank == 0:
         peak, peak_kind = measured_peaks()

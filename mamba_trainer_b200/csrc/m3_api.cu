@@ -177,6 +177,10 @@ int tc_backward_call(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* i
       cudaFreeAsync(base, ctx->stream);
       return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family needs 16-byte aligned b, c, x, dy and theta");
     }
+    // the gradients asked for leave by bulk tensor stores where they can; by plain stores otherwise
+    p.out_maps = ((!p.dx || m3::tc_make_row_map(&p.tm_dx, p.dx, d.B, d.T, d.H, 64 * d.R, steps, true)) &&
+                  (!p.db || m3::tc_make_row_map(&p.tm_db, p.db, d.B, d.T, d.H, 128 * d.R, steps, true)) &&
+                  (!p.dc || m3::tc_make_row_map(&p.tm_dc, p.dc, d.B, d.T, d.H, 128 * d.R, steps, true))) ? 1 : 0;
   }
   char* seg = nullptr;
   cudaError_t e = plan_segments(ctx, p, tiles, !p.use_tma, &seg);
@@ -397,6 +401,8 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
         return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family needs 16-byte aligned b and c");
       if (d.rot && !m3::tc_make_row_map(&p.tm_th, p.theta, d.B, d.T, d.H, 64, steps, false))
         return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family needs a 16-byte aligned theta");
+      // y leaves by bulk tensor stores where it can (a 16-byte aligned tensor); by plain stores otherwise
+      p.out_maps = m3::tc_make_row_map(&p.tm_y, p.y, d.B, d.T, d.H, 64 * d.R, steps, true) ? 1 : 0;
     }
     char* base = nullptr;
     size_t bytes = 0;

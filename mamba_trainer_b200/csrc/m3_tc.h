@@ -37,6 +37,8 @@ bool tc_make_row_map(CUtensorMap* map, const void* base, int B, int T, int H, in
 struct TcFwdParams {
   alignas(64) CUtensorMap tm_b, tm_c, tm_x;   // tile maps of the direct form when use_tma, else row maps of b and c
   alignas(64) CUtensorMap tm_th;              // row map of theta (rotational dynamics, role-split kernel)
+  alignas(64) CUtensorMap tm_y;               // row map of y: its tiles leave by bulk tensor stores when out_maps
+  int out_maps;
   int use_tma;        // rank 1, real dynamics, T % 8 == 0, no right-to-left heads
   const __nv_bfloat16 *x, *b, *c, *dt, *lam, *theta;
   const float *a_log, *d_skip, *h0, *lu0, *angle0;
@@ -66,6 +68,8 @@ cudaError_t tc_forward_direct(cudaStream_t st, const TcFwdParams& p);
 struct TcBwdParams {
   alignas(64) CUtensorMap tm_b, tm_c;   // tile maps of the direct form when use_tma, else row maps of b and c
   alignas(64) CUtensorMap tm_x, tm_dy, tm_th;  // row maps of x, dy and theta (role-split kernel)
+  alignas(64) CUtensorMap tm_dx, tm_db, tm_dc; // row maps of the gradients asked for: their tiles leave by bulk tensor stores when out_maps
+  int out_maps;
   int use_tma;
   const __nv_bfloat16 *x, *b, *c, *dt, *lam, *theta, *dy;
   const float *a_log, *d_skip, *h0, *lu0;

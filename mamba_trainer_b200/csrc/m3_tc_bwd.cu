@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
   uint8_t *sC = smem + OFF_C, *sB = smem + OFF_B, *sX = smem + OFF_X, *sXw = smem + OFF_XW, *sDY = smem + OFF_DY,
           *sDYe = smem + OFF_DYE, *sM = smem + OFF_M, *sDG = smem + OFF_DG, *sHS = smem + OFF_HS;
   float* sTab = reinterpret_cast<float*>(smem + OFF_M);    // theta rows, then the angle table, until M is written
-  float* sDphi = reinterpret_cast<float*>(smem + OFF_DG);  // alive after phase B
+  float* sDphi = reinterpret_cast<float*>(smem + OFF_X);   // d phi of the tile, once X~ and dY~ are spent (up to 32 KB)
   // dG's buffer is free from the copy-out of dC to the next band epilogue: the raw rows of x and dy land there
   uint8_t *rawX = smem + OFF_DG, *rawDY = smem + OFF_DG + RT::bytes(kP);
   float* sc = reinterpret_cast<float*>(smem + OFF_SC);
@@ -116,14 +116,17 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
     // --------------------------------------------------------------------------------------------
     // bars[2] counts two arrivals per tile: the rows of B, C and theta, then those of x and dy
     constexpr uint32_t kBcBytes = 2u * RT::bytes(kN) + (ROT ? (uint32_t)LT * kNH * 2u : 0u), kXdyBytes = 2u * RT::bytes(kP);
-    auto request_bc = [&](int b, int h, bool rev, int bh, int kk) {
+    auto request_bc = [&](int b, int h, bool rev, int kk) {
       if (lane == 0) mbar_expect_tx(&bars[2], kBcBytes);
       __syncwarp();
       const int t0 = kk * LT;
       int l0 = request_raw_tile<R>(0, sC, &p.tm_c, &bars[2], kN, b, h, T, t0, rev);
       l0 += request_raw_tile<R>(l0, sB, &p.tm_b, &bars[2], kN, b, h, T, t0, rev);
       if (ROT && lane == l0) tma_load_rows(sTab, &p.tm_th, &bars[2], 0, h, rev ? T - t0 - LT : t0, b);
-      if (lane == 31) {
+      __syncwarp();
+    };
+    auto request_ckpt = [&](int bh, int kk) {
+      if (lane == 0) {
         mbar_expect_tx(&bars[3], kN * kP * 2);
         bulk_load(sHS, p.ckpt_h + ((size_t)bh * ntiles + kk) * kN * kP, kN * kP * 2, &bars[3]);
       }
@@ -137,7 +140,20 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
       request_raw_tile<R>(l0, rawDY, &p.tm_dy, &bars[2], kP, b, h, T, t0, rev);
       __syncwarp();
     };
+    // The staged gradients of a finished tile leave by bulk tensor stores, one box per lane: d x from the
+    // checkpoint's buffer, d B from that of the scaled copies, d C from dG's.
+    auto store_tile = [&](int b, int h, bool rev, int kk) {
+      const int t0 = kk * LT;
+      if (!tile_leaves_by_map<R>(p.out_maps, rev, T, t0)) return;
+      int l0 = 0;
+      if (p.dx) l0 += store_out_tile<R>(l0, sHS, &p.tm_dx, kP, b, h, T, t0, rev);
+      if (p.db) l0 += store_out_tile<R>(l0, sXw, &p.tm_db, kN, b, h, T, t0, rev);
+      if (p.dc) l0 += store_out_tile<R>(l0, sDG, &p.tm_dc, kN, b, h, T, t0, rev);
+      bulk_commit();
+    };
     int it = 0, requested = 0;
+    int pb = 0, ph = 0, pk = 0;  // the tile before the current one
+    bool prev = false;
     bool copies_ok = true;
     for (int item = blockIdx.x; SPLIT ? item < nitems : item == (int)blockIdx.x; item += SPLIT ? (int)gridDim.x : 1) {
       const ItemInfo im = item_of(item);
@@ -145,26 +161,29 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
       const bool rev = h >= H - p.rev;
       for (int k = im.k_hi - 1; k >= im.k_lo; --k, ++it) {
         if (it > 0) {
-          // the tile before this one: its gradients have left their staging buffers, so operands, angle table
-          // and checkpoint are spent
+          // the tile before this one: every operand and table word has been read and its gradients are staged
           bar_sync(BAR_TAIL, kPairCount);
+          store_tile(pb, ph, prev, pk);
           // its copies have landed unless the epilogue warps gave up on them: a barrier is armed again only
           // once its current phase is complete
           if (copies_ok) copies_ok = warp_all(mbar_wait(&bars[2], (it - 1) & 1) && mbar_wait(&bars[3], (it - 1) & 1));
         }
-        if (copies_ok) request_bc(b, h, rev, im.bh, k);
-        if (it > 0) bar_sync(BAR_TAIL2, kPairCount);  // its reverse scan of d phi is done with dG's buffer
+        if (copies_ok) request_bc(b, h, rev, k);  // into the operand buffers and the table's: no staged gradient there
+        if (it > 0) bulk_wait_read();             // the stores have read the staging buffers, which now take:
         if (copies_ok) {
-          request_xdy(b, h, rev, k);
+          request_ckpt(im.bh, k);                 // the checkpoint, where d x was staged
+          request_xdy(b, h, rev, k);              // x and dy, where d C was staged (d B's buffer is the epilogue's)
           ++requested;
         }
+        pb = b; ph = h; prev = rev; pk = k;
       }
     }
     if (it > 0) {  // the last tile
       bar_sync(BAR_TAIL, kPairCount);
-      bar_sync(BAR_TAIL2, kPairCount);
+      store_tile(pb, ph, prev, pk);
     }
     // no copy of this CTA may be in flight when it lets go of its shared memory
+    bulk_wait_all();
     if (requested > 0) {
       mbar_wait(&bars[2], (requested - 1) & 1);
       mbar_wait(&bars[3], (requested - 1) & 1);
@@ -551,7 +570,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
                 for (int jj = 0; jj < 16; ++jj) acc[cc][jj] += add[jj];
               }
             }
-            stage_store16<kP>(sHS, row, p0, acc[cc]);  // dS is spent: its buffer stages dx
+            stage_out16<R>(sHS, row, p0, acc[cc], rev);  // dS is spent: its buffer stages dx
           }
           part_q[ch * 128 + row] = qp2.x + qp2.y;
           dD_part = dD2.x + dD2.y;
@@ -612,7 +631,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
               }
             }
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) stage_store16<kN>(stg, row, gcol(q4), g[q4]);
+            for (int q4 = 0; q4 < 4; ++q4) stage_out16<R>(stg, row, gcol(q4), g[q4], rev);
           };
           finish(gq, sB, sXw, true);     // sigma_w X~ and exp(acum) dY~ are spent: 32 KB to stage dB
 #pragma unroll
@@ -623,19 +642,22 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
           finish(gq, sC, sDG, false);    // dG is spent: its buffer stages dC
         }
       }
+      fence_async_smem();  // the staged gradients, for the stores that read them
       epi_sync();
-      if (!dead) {
-        if (p.dx) copy_out<R, kP>(sHS, p.dx, tok0, Hs, T, t0);
-        if (p.db) copy_out<R, kN>(sXw, p.db, tok0, Hs, T, t0);
-        if (p.dc) copy_out<R, kN>(sDG, p.dc, tok0, Hs, T, t0);
+      if (!tile_leaves_by_map<R>(p.out_maps, rev, T, t0)) {
+        if (!dead) {
+          if (p.dx) copy_out_rows<R>(sHS, p.dx, kP, tok0, Hs, T, t0, rev);
+          if (p.db) copy_out_rows<R>(sXw, p.db, kN, tok0, Hs, T, t0, rev);
+          if (p.dc) copy_out_rows<R>(sDG, p.dc, kN, tok0, Hs, T, t0, rev);
+        }
+        epi_sync();
       }
-      epi_sync();
-      // every operand and table word of this tile has been read and the gradients have left their staging
-      // buffers: the next tile's rows of B and C, its theta rows and its checkpoint may land
+      // every operand and table word of this tile has been read and its gradients are staged (or gone): the
+      // copy warp sends them off and lets the next tile's rows, theta rows and checkpoint land
       epi_signal(BAR_TAIL, kPairCount, dead);
       if (ROT) {
-        // d phi of a time step sums its R rows (adjacent lanes); it then overwrites dG's buffer,
-        // which the phase-B products have finished reading.
+        // d phi of a time step sums its R rows (adjacent lanes); it then takes the buffers of X~ and dY~,
+        // which the phase-B products and the epilogue have finished reading.
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           float v = dphi[j];
@@ -711,7 +733,6 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
         }
         epi_sync();
       }
-      epi_signal(BAR_TAIL2, kPairCount, dead);  // dG's buffer is idle until the next band epilogue: x and dy may land
       // ---- 6. per-token scalars of the tile ---------------------------------------------------------
       if (tid < LT) {
         const int l = tid;

@@ -132,6 +132,15 @@ __device__ __forceinline__ void tma_load_rows(void* dst, const void* tensor_map,
       : "memory");
 }
 
+// The reverse direction: one box of a row map leaves shared memory (laid out as tma_load_rows would have
+// landed it) for the tensor; rows past the tensor's end are dropped.  `t` must not be negative.  The copy
+// joins the issuing thread's current bulk group (bulk_commit / bulk_wait_read / bulk_wait_all).
+__device__ __forceinline__ void tma_store_rows(const void* tensor_map, const void* src, int col, int h, int t, int b) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(tensor_map),
+               "r"(smem_u32(src)), "r"(col), "r"(h), "r"(t), "r"(b)
+               : "memory");
+}
+
 // A contiguous block (16-byte aligned, a multiple of 16 bytes) of this GPU's memory into shared memory.
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),

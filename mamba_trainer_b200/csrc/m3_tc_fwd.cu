@@ -288,10 +288,12 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
       const size_t tok0 = tok_at(t0);  // token-head index of l = 0 (stride Hs per step)
       // ---- 1. stage the operands ---------------------------------------------------------------
       if (!dead) dead = !warp_all(mbar_wait(&bars[2], g & 1, wait_limit));
-      if (!dead) {
-        convert_bc<R, ROT>(rawB, rawC, sB, sC, sTab, rev);
-        commit_px<R>(raw_x, sX, sXw, ts.sw);
+      if (!dead) convert_bc<R, ROT>(rawB, rawC, sB, sC, sTab, rev);
+      if (g > 0) {  // sigma_w X~ goes where the previous tile's y was staged: its stores must have read it
+        if (warp == 0) bulk_wait_read();
+        epi_sync();
       }
+      if (!dead) commit_px<R>(raw_x, sX, sXw, ts.sw);
       fence_async_smem();
       tc_fence_before();
       epi_signal(BAR_OPS, kEpiThreads + 64, dead);
@@ -411,7 +413,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
               }
             }
           }
-          stage_store16<kP>(sXw, row, p0, v);  // sigma_w X~ is spent: its buffer stages y
+          stage_out16<R>(sXw, row, p0, v, rev);  // sigma_w X~ is spent: its buffer stages y
           // refresh the bf16 copy of the state (lane = n = row, columns = p)
 #pragma unroll
           for (int j = 0; j < 16; ++j)
@@ -448,12 +450,21 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
         if (ROT && tid < kNH) __stcg(p.seg_angle + ((size_t)bh * nseg + seg) * kNH + tid, s_carry[tid]);
         __threadfence();
       }
+      fence_async_smem();  // the staged rows of y, for the stores that read them
       epi_sync();
-      if (!dead) copy_out<R, kP>(sXw, p.y, tok0, Hs, T, t0);
+      if (tile_leaves_by_map<R>(p.out_maps, rev, T, t0)) {
+        if (warp == 0 && !dead) {
+          store_out_tile<R>(0, sXw, &p.tm_y, kP, b, h, T, t0, rev);
+          bulk_commit();
+        }
+      } else {
+        if (!dead) copy_out_rows<R>(sXw, p.y, kP, tok0, Hs, T, t0, rev);
+        epi_sync();
+      }
       if (hands && tid == 0) raise_handover(p.seg_flag + (size_t)bh * nseg + seg);  // even if this CTA gave up: nobody waits in vain
-      epi_sync();
       }
     }
+    if (warp == 0) bulk_wait_all();  // the last tiles' stores
     if (dead && lane == 0 && p.err) raise_flag(p.err);
   }
   tc_fence_before();

@@ -39,7 +39,6 @@ enum : int {
   BAR_FREE = 5,   // 288: a set of scalars is free again (epilogue warps arrive; look-ahead warp syncs)
   BAR_TAIL = 6,   // 288: a tile's gradients are staged, its operands spent (epilogue warps arrive; copy warp syncs)
   BAR_OPS0 = 9,   // 288: the x / dy operands of a tile are staged, ahead of B and C (epilogue warps arrive; issuer syncs)
-  BAR_TAIL2 = 8,  // 288: the gradients have left their staging buffers (epilogue warps arrive; copy warp syncs)
 };
 
 
@@ -270,6 +269,89 @@ __device__ __forceinline__ int request_raw_tile(int lane0, uint8_t* dst, const v
   if (pn >= 0 && pn < (int)RT::panels(cols))
     tma_load_rows(dst + (uint32_t)pn * RT::kPanelBytes, map, bar, pn * 64, h, t, b);
   return (int)RT::panels(cols);
+}
+
+// ---------------------------------------------------------------------------------------
+// Results on their way out.  A thread owns a folded row (l, r) of an accumulator tile; the caller's tensor
+// wants rows [step][col * R + r].  The tile is staged in shared memory exactly as a bulk tensor copy of a
+// row map would have landed it (the layout of RawTile), and leaves by bulk tensor stores, one box per 64
+// elements of a row, issued side by side by the lanes of one warp: no thread carries the bytes.  The ranks
+// of a step sit in neighbouring lanes, so the interleave is an exchange of registers (rank 2), not a pass
+// over shared memory.  A tile whose box would start before the tensor (the ragged last tile of a head that
+// walks right to left) leaves by plain 16-byte stores instead.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_shared16(uint8_t* dst, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  *reinterpret_cast<uint4*>(dst) = make_uint4(a, b, c, d);
+}
+// 16 consecutive columns [col0, col0 + 16) of folded row `row` (col0 a multiple of 16).  Whole warps only.
+template <int R>
+__device__ __forceinline__ void stage_out16(uint8_t* stg, int row, int col0, const float (&v)[16], bool rev) {
+  using RT = RawTile<R>;
+  const int l = row / R;
+  if constexpr (R == 4) {  // no exchange for rank 4: element by element
+    const int r = row % R;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const uint32_t e = (uint32_t)(col0 + j) * R + r;
+      *reinterpret_cast<__nv_bfloat16*>(stg + RT::piece(l, e & ~7u, rev) + (e & 7u) * 2u) = __float2bfloat16_rn(v[j]);
+    }
+  } else {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+    if constexpr (R == 1) {
+      st_shared16(stg + RT::piece(l, (uint32_t)col0, rev), w[0], w[1], w[2], w[3]);
+      st_shared16(stg + RT::piece(l, (uint32_t)col0 + 8u, rev), w[4], w[5], w[6], w[7]);
+    } else {
+      // lanes (2i, 2i + 1) hold ranks 0 and 1 of one step: the even lane takes columns [col0, col0 + 8) of
+      // both ranks, the odd one [col0 + 8, col0 + 16)
+      const bool odd = row & 1;
+      uint32_t mine[4], theirs[4], o[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        mine[i] = odd ? w[4 + i] : w[i];
+        theirs[i] = __shfl_xor_sync(0xffffffffu, odd ? w[i] : w[4 + i], 1);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const uint32_t r0 = odd ? theirs[k >> 1] : mine[k >> 1], r1 = odd ? mine[k >> 1] : theirs[k >> 1];
+        o[k] = __byte_perm(r0, r1, (k & 1) ? 0x7632 : 0x5410);
+      }
+      const uint32_t e0 = (uint32_t)(col0 + (odd ? 8 : 0)) * 2u;
+      st_shared16(stg + RT::piece(l, e0, rev), o[0], o[1], o[2], o[3]);
+      st_shared16(stg + RT::piece(l, e0 + 8u, rev), o[4], o[5], o[6], o[7]);
+    }
+  }
+}
+// May the tile at scan step t0 leave by bulk tensor stores?
+template <int R>
+__device__ __forceinline__ bool tile_leaves_by_map(int has_maps, bool rev, int T, int t0) {
+  return has_maps && !(rev && T - t0 - kRows / R < 0);
+}
+// The stores of one staged tile of one tensor (`cols` columns per rank), by the lanes [lane0, lane0 + panels)
+// of a warp.  The caller commits and waits for the group.  Returns the number of lanes used.
+template <int R>
+__device__ __forceinline__ int store_out_tile(int lane0, const uint8_t* src, const void* map, int cols, int b, int h, int T,
+                                              int t0, bool rev) {
+  using RT = RawTile<R>;
+  const int pn = (int)(threadIdx.x & 31) - lane0;
+  if (pn >= 0 && pn < (int)RT::panels(cols))
+    tma_store_rows(map, src + (uint32_t)pn * RT::kPanelBytes, pn * 64, h, rev ? T - t0 - RT::LT : t0, b);
+  return (int)RT::panels(cols);
+}
+// The same tile by plain stores of the 256 epilogue threads: g[(tok0 + l * Hs) * cols * R + e], steps
+// t0 + l < T only.
+template <int R>
+__device__ __forceinline__ void copy_out_rows(const uint8_t* stg, __nv_bfloat16* g, int cols, size_t tok0, int Hs, int T, int t0,
+                                             bool rev) {
+  constexpr int LT = kRows / R;
+  const int E = cols * R, per_row = E / 8;
+  for (int it = threadIdx.x; it < LT * per_row; it += kEpiThreads) {
+    const int l = it / per_row, c = it - l * per_row;
+    if (t0 + l >= T) continue;
+    const uint4 q = *reinterpret_cast<const uint4*>(stg + RawTile<R>::piece(l, (uint32_t)c * 8u, rev));
+    *reinterpret_cast<uint4*>(g + (tok0 + (size_t)((ptrdiff_t)l * Hs)) * E + (size_t)c * 8) = q;
+  }
 }
 
 // R consecutive 16-byte pieces of a staged row, starting at element e, as 4 R words.

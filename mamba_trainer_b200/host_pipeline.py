@@ -24,6 +24,36 @@ _PER_TOKEN = ("x", "b", "c", "dt", "lam", "theta", "dy")
 _PER_HEAD = ("a_log", "d_skip")
 
 
+def bind_host_thread_near(device) -> Optional[dict]:
+    """Pin the calling process to the CPUs next to `device` (its PCIe root's NUMA node, as sysfs reports
+    it), so that the page-locked buffers it allocates afterwards - a pinned page lives on the node of the
+    thread that first touches it - sit on the memory controller the GPU's copies reach without crossing the
+    socket interconnect.  With one process per GPU and none of them bound, every rank's staging buffers can
+    land on one node and all host-to-device traffic of the box then shares that node's bandwidth.
+    Returns {"node", "cpus"} or None where the platform gives no answer (no sysfs entry, node -1, or an
+    empty intersection with the CPUs this process may use); nothing is changed in that case."""
+    import os
+    try:
+        props = torch.cuda.get_device_properties(torch.device(device))
+        addr = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        base = "/sys/bus/pci/devices/" + addr
+        node = int(open(base + "/numa_node").read().strip())
+        cpulist = open(base + "/local_cpulist").read().strip()
+    except (OSError, ValueError, AttributeError):
+        return None
+    if node < 0 or not cpulist:
+        return None
+    cpus = set()
+    for part in cpulist.split(","):
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    cpus &= os.sched_getaffinity(0)
+    if not cpus:
+        return None
+    os.sched_setaffinity(0, cpus)
+    return {"node": node, "cpus": len(cpus)}
+
+
 def _hp(t: Optional[torch.Tensor]):
     return C.c_void_p(t.data_ptr()) if t is not None else None
 
