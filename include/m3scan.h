@@ -300,7 +300,8 @@ typedef struct {
 int m3_conv_forward(m3_ctx *ctx, const m3_conv_desc *desc, void *y, void *new_history);
 /* The adjoint; it recomputes the pre-activation from x, so the forward saves nothing.
  * dx has x's strides; dweight [K, channels], dbias [channels] (float) and dhistory
- * (like history) may each be NULL.  The parameter gradients are summed in a fixed order. */
+ * (like history) may each be NULL.  The parameter gradients are summed in a fixed order;
+ * dbias of a convolution without a bias is written as zeros. */
 int m3_conv_backward(m3_ctx *ctx, const m3_conv_desc *desc, const void *dy, void *dx,
                      float *dweight, float *dbias, void *dhistory);
 

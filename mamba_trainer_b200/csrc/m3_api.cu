@@ -165,8 +165,7 @@ int tc_backward_call(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* i
   p.err = ctx->dev_err;
   p.B = d.B; p.T = d.T; p.H = d.H; p.R = d.R; p.disc = d.disc; p.rev = d.rev;
   p.wait_limit = ctx->wait_limit ? ctx->wait_limit : (1u << 18);
-  static const bool tma_off = getenv("M3_TC_NO_TMA") != nullptr;
-  p.use_tma = (!tma_off && d.R == 1 && !d.rot && d.rev == 0 && d.T % 8 == 0 && !(reinterpret_cast<uintptr_t>(p.ckpt_h) & 15) &&
+  p.use_tma = (d.R == 1 && !d.rot && d.rev == 0 && d.T % 8 == 0 && !(reinterpret_cast<uintptr_t>(p.ckpt_h) & 15) &&
                m3::tc_make_tile_map(&p.tm_b, p.b, d.B, d.T, d.H, 128) && m3::tc_make_tile_map(&p.tm_c, p.c, d.B, d.T, d.H, 128)) ? 1 : 0;
   if (!p.use_tma) {
     if (!m3::tc_make_row_map(&p.tm_b, p.b, d.B, d.T, d.H, 128 * d.R, steps, true) ||
@@ -389,8 +388,7 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
     p.wait_limit = ctx->wait_limit ? ctx->wait_limit : (1u << 18);
     // Rank 1 with real dynamics needs no conversion of its rows: bulk tensor copies land them in
     // operand layout (every head left to right, T a multiple of 8, 16-byte aligned tensors).
-    static const bool tma_off = getenv("M3_TC_NO_TMA") != nullptr;
-    p.use_tma = (!tma_off && d.R == 1 && !d.rot && d.rev == 0 && d.T % 8 == 0 &&
+    p.use_tma = (d.R == 1 && !d.rot && d.rev == 0 && d.T % 8 == 0 &&
                  m3::tc_make_tile_map(&p.tm_b, p.b, d.B, d.T, d.H, 128) && m3::tc_make_tile_map(&p.tm_c, p.c, d.B, d.T, d.H, 128) &&
                  m3::tc_make_tile_map(&p.tm_x, p.x, d.B, d.T, d.H, 64)) ? 1 : 0;
     if (!p.use_tma) {

@@ -494,6 +494,11 @@ int m3_conv_backward(m3_ctx* ctx, const m3_conv_desc* c, const void* dy, void* d
     const size_t n = (size_t)(d.K + 1) * d.C;  // a block's partial: K taps of C channels, then the bias
     if (dweight) e = m3::column_sums(ctx->stream, part, nblk, n, d.K * d.C, dweight);
     if (e == cudaSuccess && dbias && c->bias) e = m3::column_sums(ctx->stream, part + (size_t)d.K * d.C, nblk, n, d.C, dbias);
+  }
+  // a convolution without a bias has no bias gradient: the buffer, if one was passed, reads zero (as it
+  // does for an empty sequence) rather than whatever it held
+  if (e == cudaSuccess && dbias && !c->bias) e = cudaMemsetAsync(dbias, 0, (size_t)d.C * sizeof(float), ctx->stream);
+  if (e == cudaSuccess && want_par) {
     ctx->launches += (dweight ? 1 : 0) + ((dbias && c->bias) ? 1 : 0);
   }
   cudaError_t e2 = part ? cudaFreeAsync(part, ctx->stream) : cudaSuccess;

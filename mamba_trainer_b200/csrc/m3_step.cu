@@ -60,7 +60,12 @@ __global__ void __launch_bounds__(256) k_step(m3_step_desc d, m3_step_out o) {
   float* hout = o.h + (size_t)bh * P * N;
   float* uout = o.last_u + (size_t)bh * P * N;
   T* y = static_cast<T*>(o.y) + (size_t)bh * P * R;
-  if ((N & 3) == 0) {  // 128-bit path: each lane owns 4 consecutive state columns per pass
+  // 128-bit path: each lane owns 4 consecutive state columns per pass; it needs rows of whole float4s
+  // and 16-byte aligned state tensors (a caller may hand over an offset view), else the scalar loop
+  const bool vec4 = (N & 3) == 0 &&
+                    !((reinterpret_cast<uintptr_t>(d.h) | reinterpret_cast<uintptr_t>(d.last_u) |
+                       reinterpret_cast<uintptr_t>(o.h) | reinterpret_cast<uintptr_t>(o.last_u)) & 15);
+  if (vec4) {
     for (int p = warp; p < P; p += 8) {
       float acc[kStepMaxRank];
 #pragma unroll

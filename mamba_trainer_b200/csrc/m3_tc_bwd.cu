@@ -1,8 +1,8 @@
 // Tensor-core backward of the Mamba-3 SSD scan (sm_100a: tcgen05 MMA, TMEM accumulators, bulk copies).
 //
-// The hand-written adjoint of the folded scan, one CTA per (batch, head) stripe walking its
-// 128-row tiles in REVERSE with the gradient of the state, dH^T [d_state x head_dim] fp32,
-// resident in TMEM.  The reference derives this pass from its tape (rules in
+// The hand-written adjoint of the folded scan: a CTA walks the 128-row tiles of a (batch, head) stripe -
+// or of a time segment of one - in REVERSE with the gradient of the state, dH^T [d_state x head_dim]
+// fp32, resident in TMEM.  The reference derives this pass from its tape (rules in
 // src/autograd/ops.rs:204-264, :1066-1139, kernels src/tensor/ops/fused.rs:627-672,
 // :2080-2138, :2513-2549); here it is two MMA phases per tile:
 //   A:  G = C^ B^^T,  dM = dY~ X~^T,  T1 = dY~ H_k
@@ -14,10 +14,12 @@
 // Warp roles (m3_tc_roles.cuh): the issuer warp issues both phases, the look-ahead warp computes the next
 // tile's per-token scalars, the copy warp requests the next tile's raw rows of B, C, x, dy and theta (bulk
 // tensor copies) and its state checkpoint (a plain bulk copy) as soon as this tile has let go of the
-// buffers.  Shared memory has no room for staging beside the operands (a tile's operands alone take
-// 208 KB), so the rows of B and C land IN their operand buffers and are converted in place - every epilogue
-// warp reads its share into registers, one barrier, then the rotated / de-interleaved operands overwrite
-// them - and those of x and dy land in dG's buffer, which is idle between two band epilogues.
+// buffers, and sends this tile's staged gradients d x, d B, d C off by bulk tensor stores.  Shared memory
+// has no room for staging beside the operands (a tile's operands alone take 208 KB), so the rows of B and C
+// land IN their operand buffers and are converted in place - every epilogue warp reads its share into
+// registers, one barrier, then the rotated / de-interleaved operands overwrite them - those of x and dy
+// land in dG's buffer, which is idle between two band epilogues, and the gradients are staged in buffers
+// the tile has finished with (d x over dS, d B over the scaled copies, d C over dG).
 // The (cos, sin) table of the tile's angles is computed once, used for the rotation, and kept in 64
 // TMEM columns for the un-rotation of the gradients (its shared-memory buffer becomes M in between).
 // Rank 1 with real dynamics has a second form (m3_tc_bwd_direct.cu).

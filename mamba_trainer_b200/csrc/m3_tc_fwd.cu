@@ -1,21 +1,23 @@
 // Tensor-core forward of the Mamba-3 SSD scan (sm_100a: tcgen05 MMA, TMEM accumulators, bulk copies).
 //
-// One CTA walks one (batch, head) stripe in 128-row tiles (128 / R time steps, rows
-// rho = (t, r)), with the fp32 state resident in TMEM as H^T [d_state x head_dim], so the
-// forward pass moves no chunk-state traffic beyond the per-tile checkpoint the backward
-// pass asks for.  Per tile:
-//   copy    raw rows of B and C land in a staging buffer by bulk tensor copies (one box per tensor and
-//           256 columns), requested a tile ahead by the issuer warp
-//   ahead   per-token scalars and the (cos, sin) table of the wrapped cumulative angle, computed a
-//           tile ahead by the look-ahead warps                          (scan.rs:491-522, fused.rs:588-619)
+// A CTA walks (batch, head) stripes in 128-row tiles (128 / R time steps, rows rho = (t, r)), with the
+// fp32 state resident in TMEM as H^T [d_state x head_dim], so the forward pass moves no chunk-state
+// traffic beyond the per-tile checkpoint the backward pass asks for.  Per tile:
+//   copy    raw rows of B, C (and theta) land in staging buffers by bulk tensor copies of row maps (one box
+//           per 64 elements of a row, 128-byte swizzle), requested a tile ahead by the copy warp
+//   ahead   per-token scalars by the look-ahead warp a tile ahead; the (cos, sin) table of the wrapped
+//           cumulative angle by the epilogue warps, while the previous tile's second group of products
+//           runs                                                        (scan.rs:491-522, fused.rs:588-619)
 //   stage   C^, B^ (rotated by -phi, ranks de-interleaved), X~, sigma_w X~ as bf16 operands
-//   MMA     Yoff = C^ H^T-contraction,  G = C^ B^^T                      (scan.rs:199, :256-261)
+//   MMA     Yoff = C^ H^T-contraction,  G = C^ B^^T   (issuer warp)      (scan.rs:199, :256-261)
 //   regs    M = G o band -> operand; Yoff *= exp(acum); H *= exp(cd)     (fused.rs:2044-2070)
 //   MMA     Y += M X~ ;  H^T += B^^T (sigma_w X~)                        (scan.rs:202-216)
-//   store   y = Y + D x ; refresh the bf16 copy of H for the next tile
+//   store   y = Y + D x staged in the row map's layout and sent off by bulk tensor stores; the bf16 copy
+//           of H refreshed for the next tile
 // bf16 operands, fp32 accumulation and state; shapes: head_dim 64, d_state 128, R in {1,2,4}.
-// Warp roles and barriers: m3_tc_roles.cuh.  Rank 1 with real dynamics has a second form
-// (m3_tc_fwd_direct.cu) whose rows need no conversion and land in operand layout by bulk TENSOR copies.
+// Warp roles, barriers and the distribution of stripes (or time segments of stripes) over CTAs:
+// m3_tc_roles.cuh.  Rank 1 with real dynamics has a second form (m3_tc_fwd_direct.cu) whose rows need no
+// conversion and land in operand layout by bulk TENSOR copies.
 #include "m3_tc.h"
 #include "m3_tc_roles.cuh"
 

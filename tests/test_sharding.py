@@ -1,5 +1,7 @@
-"""Sharding over ranks: host logic on CPU, world_size 2 over gloo.  Each rank runs the oracle on
-its shard; gathered outputs and reduced per-head gradients must equal the unsharded result."""
+"""Sharding over ranks (mamba_trainer_b200/sharding.py): the batch-then-heads plan, the per-shard count of
+reversed heads, and - as two gloo ranks on CPU - the path bench.py takes at N > 1: each rank runs its shard
+(here through the oracle, the GPU box runs the kernels), per-token outputs are gathered, per-head gradients
+reduced, and both must equal the unsharded result."""
 import os
 import socket
 
@@ -24,6 +26,38 @@ def test_plan_covers_everything_once():
         sharding.shard_plan(2, 3, 4, 0)      # 3 heads do not split over 2 ranks per sequence
     with pytest.raises(ValueError):
         sharding.shard_plan(2, 4, 2, 2)
+
+
+def test_reversed_heads_follow_their_shard():
+    """A bidirectional scan reverses the last `reverse_heads` heads (models/mamba3.rs:352-370).  When the
+    heads of a sequence are split over ranks, each shard reverses exactly those of its heads that lie in
+    that tail: summed over the shards of a sequence that is the whole tail, and the oracle on the shard
+    with its own count reproduces the unsharded result."""
+    for batch, heads, world, rev in [(2, 8, 8, 4), (1, 4, 4, 1), (8, 12, 2, 6), (2, 8, 8, 8), (2, 8, 8, 0)]:
+        per_row = {}
+        for r in range(world):
+            s = sharding.shard_plan(batch, heads, world, r)
+            n = sharding.shard_reverse_heads(heads, rev, s)
+            assert 0 <= n <= s.n_heads
+            # the shard's reversed heads are its last n, and they are global heads >= heads - rev
+            assert all(h >= heads - rev for h in range(s.heads.stop - n, s.heads.stop))
+            assert all(h < heads - rev for h in range(s.heads.start, s.heads.stop - n))
+            for b in range(s.batch.start, s.batch.stop):
+                per_row[b] = per_row.get(b, 0) + n
+        assert all(v == rev for v in per_row.values()), (batch, heads, world, rev)
+    # numerically: 2 sequences x 4 heads over 4 ranks (two heads per rank), the last 3 heads reversed
+    from oracle.m3_oracle import mamba3_scan_bidirectional
+    w = synthetic.Workload("bidir_shard", 2, 24, 4, 4, 8, 8, 2, torch.float32, Discretization.LearnedTrapezoid, True, "scaled")
+    t = synthetic.make_inputs(w, seed=5)
+    full, _ = mamba3_scan_bidirectional(t["x"], t["b"], t["c"], t["dt"], t["a_log"], t["lam"], t["theta"], t["d_skip"],
+                                         None, w.chunk, False, reverse_heads=3)
+    for r in range(4):
+        s = sharding.shard_plan(2, 4, 4, r)
+        ts = sharding.shard_inputs(t, s)
+        part, _ = mamba3_scan_bidirectional(ts["x"], ts["b"], ts["c"], ts["dt"], ts["a_log"], ts["lam"], ts["theta"],
+                                             ts["d_skip"], None, w.chunk, False,
+                                             reverse_heads=sharding.shard_reverse_heads(4, 3, s))
+        assert torch.equal(part, full[s.batch, :, s.heads]), r
 
 
 def _free_port():
