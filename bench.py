@@ -32,7 +32,20 @@ from mamba_trainer_b200 import sharding, synthetic  # noqa: E402
 # proportional to the token-heads a launch processes).  None where no capture was taken.
 NCU_TRAFFIC_BYTES_PER_TOKEN_HEAD = {
     "cfg1_siso_trapezoid_bf16": 267403520 / (8 * 2048 * 12),
+    # profiles/tc_fwd_bwd_kernels_cfg4.md: batch 4 x seq 4096 (whole stripes) and batch 8 x seq 4096 (stripes cut
+    # into time segments, which adds the hand-over of the state between segments)
+    "cfg4_mimo2_scaling_bf16": {"whole": 1724142135 / (4 * 4096 * 32), "split": 3560648568 / (8 * 4096 * 32)},
 }
+
+
+def traffic_per_token_head(w, sms: int):
+    """The captured DRAM traffic per (token, head) of the instantiation this shard runs: the library cuts
+    stripes in time when there are more stripes than SMs but fewer than six per SM (tc_segment_plan)."""
+    v = NCU_TRAFFIC_BYTES_PER_TOKEN_HEAD.get(w.name)
+    if isinstance(v, dict):
+        stripes = w.batch * w.heads
+        return v["split"] if sms < stripes < 6 * sms else v["whole"]
+    return v
 
 METRIC = "mamba3_ssd_scan_fwd_bwd_throughput"
 UNIT = "Mtokens/s"
@@ -527,7 +540,7 @@ def main():
         achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
         whole = alg_bytes / (ms_step * 1e-3) / 1e9
         flops = w.flops_per_token_head() * th
-        per_th = NCU_TRAFFIC_BYTES_PER_TOKEN_HEAD.get(w.name)
+        per_th = traffic_per_token_head(w, torch.cuda.get_device_properties(dev).multi_processor_count)
         cfg = workload_config(gw, world, args.config)
         cfg["batch_per_gpu"] = w.batch
         if fallback_note:
