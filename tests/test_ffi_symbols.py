@@ -67,3 +67,23 @@ def test_scratch_size_query_needs_no_gpu():
     fwd = lib.m3_scan_scratch_bytes(ctypes.byref(d), 0)
     both = lib.m3_scan_scratch_bytes(ctypes.byref(d), 1)
     assert 0 < fwd < both
+
+
+def test_rust_sys_source_covers_the_header():
+    """include/m3scan-sys/src/lib.rs (uncompiled here: the image has no Rust toolchain) declares every function
+    of the header and nothing else, and lists every structure's fields in the header's order."""
+    rs = (ROOT / "include" / "m3scan-sys" / "src" / "lib.rs").read_text()
+    assert set(re.findall(r"pub fn (m3_[a-z0-9_]+)\s*\(", rs)) == declared_symbols()
+    header = re.sub(r"/\*.*?\*/", "", (ROOT / "include" / "m3scan.h").read_text(), flags=re.S)
+    for body, name in re.findall(r"typedef struct \{(.*?)\}\s*(m3_[a-z_]+);", header, flags=re.S):
+        c_fields = []
+        for decl in body.split(";"):
+            decl = decl.strip()
+            if not decl:
+                continue
+            for part in decl.split(","):
+                c_fields.append(re.sub(r"\[\d+\]", "", part.strip().split()[-1].lstrip("*")))
+        m = re.search(r"pub struct %s \{(.*?)\n\}" % name, rs, flags=re.S)
+        assert m, name
+        rs_fields = re.findall(r"pub ([a-z_0-9]+):", re.sub(r"//.*", "", m.group(1)))
+        assert rs_fields == c_fields, name
