@@ -29,18 +29,15 @@ constexpr uint32_t TM_G = 0, TM_DM = 128, TM_T1 = 256, TM_DH = 384, TM_COLS = 51
 constexpr uint32_t TM_DB = 0, TM_DX = 128, TM_U = 192;
 
 
-// TMA: rank 1 with real dynamics; C^, B^, X~ and dY~ are the raw rows, landed in operand layout by bulk
-// tensor copies that are requested as soon as the previous tile has read its own, the checkpoint
-// by a plain bulk copy.
-template <int R, bool ROT, bool TMA>
-__global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ TcBwdParams p) {
+// Rank 1 with real dynamics: C^ and B^ are the raw rows, landed in operand layout by bulk tensor copies that
+// are requested as soon as the previous tile has read its own, the checkpoint by a plain bulk copy; x and
+// dy come through registers.
+__global__ void __launch_bounds__(256, 1) tc_bwd_direct_kernel(const __grid_constant__ TcBwdParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  static_assert(!TMA || (R == 1 && !ROT), "the TMA-fed variant serves rank 1 with real dynamics");
+  constexpr int R = 1;  // rank 1 with real dynamics is the only shape this form serves
   constexpr int LT = kRows / R;
   uint8_t *sC = smem + OFF_C, *sB = smem + OFF_B, *sX = smem + OFF_X, *sXw = smem + OFF_XW, *sDY = smem + OFF_DY,
           *sDYe = smem + OFF_DYE, *sM = smem + OFF_M, *sDG = smem + OFF_DG, *sHS = smem + OFF_HS;
-  float* sPhi = reinterpret_cast<float*>(smem + OFF_M);    // alive while staging and again after phase B
-  float* sDphi = reinterpret_cast<float*>(smem + OFF_DG);  // alive after phase B
   float* sc = reinterpret_cast<float*>(smem + OFF_SC);
   // Two sets of per-token scalars: the next tile's are computed while this tile's phase-B products run.
   auto scal_set = [&](int i) {
@@ -76,7 +73,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
   const float dsk = p.d_skip ? p.d_skip[h] : 0.0f;
   const int quad = warp & 3, ch = warp >> 2;
   const int row = quad * 32 + lane;
-  const int rl = row / R, rr = row % R;  // time step within the tile and rank of this thread's row
+  const int rl = row / R;  // time step within the tile of this thread's row
 
   if (tid == 0) {
     mbar_init(&bars[0], 1);
@@ -107,7 +104,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
   bool failed = false;
   float nx_dt, nx_lam;  // dt / lambda of the next tile to process, loaded one tile ahead
   load_dt_lam<R>(nx_dt, nx_lam, p.dt, p.lam, p.disc, b, h, H, T, (ntiles - 1) * LT, rev);
-  // TMA-fed variant: one thread asks for a tile's rows / its checkpoint.
+  // One thread asks for a tile's rows / its checkpoint.
   auto request_cb = [&](int kk) {
     const int tg = (b * T + kk * LT) / 8;  // token group of the tile's first row (T % 8 == 0)
     mbar_expect_tx(&bars[4], 2 * kRows * kN * 2);
@@ -125,86 +122,50 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
   prepare_scalars(ntiles - 1, 0);
   int ckpt_requested = 0, cb_requested = 0;  // the same in every thread
   bool early_cb = false;
-  if (TMA) {
-    if (tid == 0) {
-      request_cb(ntiles - 1);
-      request_ckpt(ntiles - 1);
-    }
-    ckpt_requested = cb_requested = 1;
+  if (tid == 0) {
+    request_cb(ntiles - 1);
+    request_ckpt(ntiles - 1);
   }
+  ckpt_requested = cb_requested = 1;
   for (int k = ntiles - 1, it = 0; k >= 0; --k, ++it) {
     const int t0 = k * LT;
     const size_t tok0 = tok_at(t0);
     const bool last_tile = (k == ntiles - 1);
     const int l_end = T - 1 - t0;  // row of the final token when last_tile
     // ---- 1. every global load of the tile in flight, then scalars and angles ---------------------
-    RawBC<R, ROT> raw_bc;
     RawPX<R> raw_x, raw_dy;
-    RawTheta<R> raw_th;
-    uint4 raw_h[4];
-    if (!TMA) {
-      issue_bc<R, ROT>(raw_bc, p.b, p.c, tok0, Hs, T, t0);
-      issue_px<R>(raw_x, p.x, tok0, Hs, T, t0);
-      issue_px<R>(raw_dy, p.dy, tok0, Hs, T, t0);
-      if (ROT) issue_theta<R>(raw_th, p.theta, tok0, Hs, T, t0);
-      const uint4* src = reinterpret_cast<const uint4*>(p.ckpt_h + ((size_t)bh * ntiles + k) * kN * kP);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) raw_h[i] = __ldg(src + tid + 256 * i);
-    } else {
-      // x and dy come through registers even here: a bulk tensor copy moves these tiles in 16-byte
-      // pieces, and the copy engine's piece rate, not memory, then sets when the tile can start.  The
-      // rows were asked into L2 one tile ago, and the scaled copies are made from the same registers.
-      issue_px<R>(raw_x, p.x, tok0, Hs, T, t0);
-      issue_px<R>(raw_dy, p.dy, tok0, Hs, T, t0);
-    }
+    // x and dy come through registers even here: a bulk tensor copy moves these tiles in 16-byte
+    // pieces, and the copy engine's piece rate, not memory, then sets when the tile can start.  The
+    // rows were asked into L2 one tile ago, and the scaled copies are made from the same registers.
+    issue_px<R>(raw_x, p.x, tok0, Hs, T, t0);
+    issue_px<R>(raw_dy, p.dy, tok0, Hs, T, t0);
     const TileScalars ts = scal_set(it & 1);  // filled during the previous tile's phase-B wait (or the prologue)
-    if (ROT) {
-      if (tid < kNH) s_carry[tid] = p.ckpt_angle[((size_t)bh * ntiles + k) * kNH + tid];
-      commit_theta<R>(raw_th, sPhi);
-      __syncthreads();
-      tile_angles_smem<R>(sPhi, s_q, s_carry, ts.dt, T, t0, nullptr);
-    }
     __syncthreads();
     // ---- 2-3. operands ------------------------------------------------------------------------------
-    if (TMA) {
-      {
-        const bool ok = mbar_wait(&bars[4], it & 1) && mbar_wait(&bars[3], it & 1);
-        if (__syncthreads_or(!ok)) { failed = true; break; }
-      }
-      const int nv = T - t0;  // rows of this tile that exist; the box ran on into the next sequence
-      if (nv < kRows) {
-        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-        for (int q = tid; q < kRows * (kN / 8); q += 256) {
-          const int r = q / (kN / 8), g8 = q % (kN / 8);
-          if (r >= nv) {
-            *reinterpret_cast<uint4*>(sC + tile_off(r, 8 * g8, kN)) = z;
-            *reinterpret_cast<uint4*>(sB + tile_off(r, 8 * g8, kN)) = z;
-          }
+    {
+      const bool ok = mbar_wait(&bars[4], it & 1) && mbar_wait(&bars[3], it & 1);
+      if (__syncthreads_or(!ok)) { failed = true; break; }
+    }
+    const int nv = T - t0;  // rows of this tile that exist; the box ran on into the next sequence
+    if (nv < kRows) {
+      const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+      for (int q = tid; q < kRows * (kN / 8); q += 256) {
+        const int r = q / (kN / 8), g8 = q % (kN / 8);
+        if (r >= nv) {
+          *reinterpret_cast<uint4*>(sC + tile_off(r, 8 * g8, kN)) = z;
+          *reinterpret_cast<uint4*>(sB + tile_off(r, 8 * g8, kN)) = z;
         }
       }
-      commit_px<R>(raw_x, sX, sXw, ts.sw);      // with the scaled copies sigma_w X~ and exp(acum) dY~
-      commit_px<R>(raw_dy, sDY, sDYe, ts.eac);
-      if (k > 0) {  // the next tile's x (threads 0-127) and dy rows, one 128-byte line each, into L2
-        const __nv_bfloat16* g = (tid < 128) ? p.x : p.dy;
-        prefetch_l2(g + (tok0 - (size_t)LT * Hs + (size_t)(tid & 127) * Hs) * kP);
-      }
-    } else {
-      commit_bc<R, ROT>(raw_bc, sB, sC, sPhi);
-      commit_px<R>(raw_x, sX, sXw, ts.sw);
-      commit_px<R>(raw_dy, sDY, sDYe, ts.eac);
-      // H_k, the bf16 state entering the tile, already in operand layout [p][n]
-      uint4* dst = reinterpret_cast<uint4*>(sHS);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) dst[tid + 256 * i] = raw_h[i];
+    }
+    commit_px<R>(raw_x, sX, sXw, ts.sw);      // with the scaled copies sigma_w X~ and exp(acum) dY~
+    commit_px<R>(raw_dy, sDY, sDYe, ts.eac);
+    if (k > 0) {  // the next tile's x (threads 0-127) and dy rows, one 128-byte line each, into L2
+      const __nv_bfloat16* g = (tid < 128) ? p.x : p.dy;
+      prefetch_l2(g + (tok0 - (size_t)LT * Hs + (size_t)(tid & 127) * Hs) * kP);
     }
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
-#ifndef M3_NO_L2_PREFETCH
-    if (!TMA && k > 0)  // warm L2 with the tile after this one (behind this tile's own loads)
-      prefetch_tile_l2<R, ROT>(p.b, p.c, p.x, p.dy, p.theta, p.ckpt_h + ((size_t)bh * ntiles + k - 1) * kN * kP,
-                               tok0 - (size_t)LT * Hs, Hs, T, t0 - LT);
-#endif
     // ---- 4. MMA phase A ------------------------------------------------------------------------
     if (tid == 0) {
       tc_fence_after();
@@ -215,7 +176,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
     }
     // Without a rotation nothing reuses dG's buffer before the next band epilogue, so the 32 KB of dC
     // staged there by the previous tile leave now, while every warp would only wait for the products.
-    if (!ROT && it > 0 && p.dc) copy_out<R, kN>(sDG, p.dc, tok0 + (size_t)LT * Hs, Hs, T, t0 + LT);
+    if (it > 0 && p.dc) copy_out<R, kN>(sDG, p.dc, tok0 + (size_t)LT * Hs, Hs, T, t0 + LT);
     {
       const bool ok = mbar_wait(&bars[0], it & 1);
       if (__syncthreads_or(!ok)) { failed = true; break; }
@@ -381,15 +342,13 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
       gemm_issue(tm + TM_DH, mn_major(aC, kN), mn_major(smem_u32(sDYe), kP), make_idesc(64, 1, 1), kRows, true);
       umma_commit(&bars[1]);
     }
-    RawTheta<R> th2;  // the tile's theta rows again (step 7), asked for now so that they arrive behind the products
-    if (ROT) issue_theta<R>(th2, p.theta, tok0, Hs, T, t0);
     if (k > 0) prepare_scalars(k - 1, (it + 1) & 1);  // while the five products run
     {
       const bool ok = mbar_wait(&bars[1], it & 1);
       if (__syncthreads_or(!ok)) { failed = true; break; }
     }
     tc_fence_after();
-    if (TMA && k > 0) {
+    if (k > 0) {
       // C^ and B^ of this tile have been read for the last time (only the gradient through last_u of the
       // final token looks at B^ again): their successors can start to arrive now.
       early_cb = !(last_tile && p.dlu);
@@ -399,18 +358,9 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
       }
     }
     // ---- 7. epilogue B -------------------------------------------------------------------------
-    if (ROT) {  // the angles again (their buffer held M in between)
-      commit_theta<R>(th2, sPhi);
-      __syncthreads();
-      tile_angles_smem<R, true>(sPhi, s_q, s_carry, ts.dt, T, t0, nullptr);  // (cos, sin) table this time
-      __syncthreads();
-    }
-    const int t = t0 + rl;
-    const bool live = t < T;
     const bool at_end = last_tile && rl == l_end;
-    // Column blocks of this thread in a [128 x 128] gradient tile: with rotation the pairs
-    // (m, m + 64) must sit in one thread, so it takes [32ch, 32ch+32) and [64+32ch, 64+32ch+32).
-    auto gcol = [&](int q4) { return ROT ? ((q4 >> 1) * kNH + 32 * ch + 16 * (q4 & 1)) : (64 * ch + 16 * q4); };
+    // Column blocks of this thread in a [128 x 128] gradient tile.
+    auto gcol = [&](int q4) { return 64 * ch + 16 * q4; };
     float acc[2][16], u[2][16], gq[4][16];
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {
@@ -466,9 +416,6 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
       dD_part = dD2.x + dD2.y;
     }
     {  // dB^ (TM_DB, operand sB, out db) then dC^ (TM_T1, operand sC, out dc)
-      float dphi[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) dphi[j] = 0.0f;
       float gc[4][16];
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) tmem_ld16_issue(tmem_addr(tm, quad * 32, TM_T1 + gcol(q4)), gc[q4]);  // in flight during dB^
@@ -489,28 +436,6 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
                 for (int jj = 0; jj < 16; ++jj) g[a4][jj] += (a4 == q4 && jj == j) ? s_ : 0.0f;
             }
         }
-        if (ROT) {
-#pragma unroll
-          for (int mc = 0; mc < 2; ++mc) {
-            const int m0 = 32 * ch + 16 * mc;
-            float (&g1)[16] = g[mc];
-            float (&g2)[16] = g[2 + mc];
-            float o1[16], o2[16];
-            load_chunk(sop, tile_off(row, m0, kN), *reinterpret_cast<float(*)[8]>(&o1[0]));
-            load_chunk(sop, tile_off(row, m0 + 8, kN), *reinterpret_cast<float(*)[8]>(&o1[8]));
-            load_chunk(sop, tile_off(row, kNH + m0, kN), *reinterpret_cast<float(*)[8]>(&o2[0]));
-            load_chunk(sop, tile_off(row, kNH + m0 + 8, kN), *reinterpret_cast<float(*)[8]>(&o2[8]));
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              dphi[16 * mc + j] += g1[j] * o2[j] - g2[j] * o1[j];
-              const uint32_t cw = __float_as_uint(sPhi[phi_idx(rl, m0 + j)]);
-              const float2 csn = __half22float2(*reinterpret_cast<const __half2*>(&cw));
-              const float cs = csn.x, sn = csn.y;
-              const float u1 = g1[j] * cs - g2[j] * sn, u2 = g1[j] * sn + g2[j] * cs;
-              g1[j] = u1; g2[j] = u2;
-            }
-          }
-        }
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) stage_store16<kN>(stg, row, gcol(q4), g[q4]);
       };
@@ -519,9 +444,9 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) tmem_ld_fence(gc[q4]);
       finish(gc, sC, sDG, false);    // dG is spent: its buffer stages dC
-      if (TMA) fence_async_smem();  // this tile's reads of its rows, before bulk copies replace them
+      fence_async_smem();  // this tile's reads of its rows, before bulk copies replace them
       __syncthreads();
-      if (TMA && k > 0) {  // the next tile's rows arrive during the copy-out and the per-token scalars
+      if (k > 0) {  // the next tile's rows arrive during the copy-out and the per-token scalars
         if (tid == 0) {
           if (!early_cb) request_cb(k - 1);
         }
@@ -529,92 +454,17 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
       }
       if (p.dx) copy_out<R, kP>(sHS, p.dx, tok0, Hs, T, t0);
       if (p.db) copy_out<R, kN>(sXw, p.db, tok0, Hs, T, t0);
-      if (p.dc && (ROT || k == 0)) copy_out<R, kN>(sDG, p.dc, tok0, Hs, T, t0);
-      if (TMA) fence_async_smem();  // dx was staged where the next checkpoint lands
+      if (p.dc && k == 0) copy_out<R, kN>(sDG, p.dc, tok0, Hs, T, t0);
+      fence_async_smem();  // dx was staged where the next checkpoint lands
       __syncthreads();
-      if (TMA && k > 0) {
+      if (k > 0) {
         if (tid == 0) request_ckpt(k - 1);
         ++ckpt_requested;
       }
-      if (ROT) {
-        // d phi of a time step sums its R rows (adjacent lanes); it then overwrites dG's buffer,
-        // which the phase-B products have finished reading.
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float v = dphi[j];
-#pragma unroll
-          for (int o = 1; o < R; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-          dphi[j] = v;
-        }
-        if (rr == 0) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float v = live ? dphi[j] : 0.0f;
-            if (at_end && p.dangle) v += p.dangle[(size_t)bh * kNH + 32 * ch + j];
-            sDphi[phi_idx(rl, 32 * ch + j)] = v;
-          }
-        }
-      }
     }
-    const float dD_tile = cta_sum(dD_part, s_red);  // also orders part_* and sDphi for what follows
+    const float dD_tile = cta_sum(dD_part, s_red);  // also orders part_* for what follows
     if (tid == 0) p.partD[(size_t)bh * ntiles + k] = dD_tile;
     // ---- 8. reverse cumulative sum of d phi over time -> d theta, and the dt term -----------------
-    if (ROT) {
-      constexpr int LQ = LT / 4, NV = 4 / R;  // NV: (time step, 8-plane group) items per thread
-      const int q = tid >> 6, m = tid & 63;
-      uint4 thq[NV];  // theta of this thread's items of the vector pass below, requested early
-#pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const int it = tid + 256 * i, l = it >> 3, mg = it & 7;
-        thq[i] = (t0 + l < T) ? __ldg(reinterpret_cast<const uint4*>(p.theta + (tok0 + (size_t)l * Hs) * kNH + mg * 8))
-                              : make_uint4(0u, 0u, 0u, 0u);
-      }
-      float run = 0.0f;
-#pragma unroll
-      for (int i = LQ - 1; i >= 0; --i) {
-        const int l = q * LQ + i;
-        run += sDphi[phi_idx(l, m)];
-        sDphi[phi_idx(l, m)] = run;
-      }
-      s_q[q * 64 + m] = run;
-      __syncthreads();
-      float off = s_dcar[m];
-      for (int qq = 3; qq > q; --qq) off += s_q[qq * 64 + m];
-#pragma unroll
-      for (int i = 0; i < LQ; ++i) sDphi[phi_idx(q * LQ + i, m)] += off;  // d step: sum of d phi from here on
-      const float total = off + s_q[0 * 64 + m];  // for q == 0: carry + all four quarters
-      __syncthreads();
-      if (q == 0) {
-        s_dcar[m] = total;
-        if (k == 0 && p.dangle0) p.dangle0[(size_t)bh * kNH + m] = total;
-      }
-      // vector pass: d theta = d step * dt (16-byte stores) and the rotation's share of d dt
-#pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const int it = tid + 256 * i, l = it >> 3, mg = it & 7;
-        const float4 d0 = *reinterpret_cast<const float4*>(&sDphi[phi_idx(l, mg * 8)]);
-        const float4 d1 = *reinterpret_cast<const float4*>(&sDphi[phi_idx(l, mg * 8 + 4)]);
-        const float ds[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
-        const uint32_t tw[4] = {thq[i].x, thq[i].y, thq[i].z, thq[i].w};
-        const float dtl = ts.dt[l];
-        float prod = 0.0f, o[8];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          prod += ds[2 * j] * bf16_lo(tw[j]) + ds[2 * j + 1] * bf16_hi(tw[j]);
-          o[2 * j] = ds[2 * j] * dtl;
-          o[2 * j + 1] = ds[2 * j + 1] * dtl;
-        }
-        if (t0 + l < T && p.dtheta) {
-          uint4 qv;
-          qv.x = pack_bf16(o[0], o[1]); qv.y = pack_bf16(o[2], o[3]); qv.z = pack_bf16(o[4], o[5]); qv.w = pack_bf16(o[6], o[7]);
-          *reinterpret_cast<uint4*>(p.dtheta + (tok0 + (size_t)l * Hs) * kNH + mg * 8) = qv;
-        }
-#pragma unroll
-        for (int o_ = 1; o_ < 8; o_ <<= 1) prod += __shfl_xor_sync(0xffffffffu, prod, o_);
-        if (mg == 0) part_rot[l] = prod;
-      }
-      __syncthreads();
-    }
     // ---- 9. per-token scalars of the tile ---------------------------------------------------------
     if (tid < LT) {
       const int l = tid;
@@ -638,7 +488,6 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
       const size_t o = (size_t)bh * Tp + t0 + l;
       p.dw[o] = col + sg * q;
       p.dg[o] = dgv;
-      if (ROT) p.ddt_rot[o] = part_rot[l];
     }
     __syncthreads();
     if (warp == 0) {  // reverse inclusive scan of d acum (+ the chunk-decay terms on the last step)
@@ -705,7 +554,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
     if (tid == 0) p.ip0[bh] = tot;
   }
   if (failed && tid == 0 && p.err) raise_flag(p.err);
-  if (TMA && failed) {
+  if (failed) {
     // A wait gave up: bulk copies already requested still target this CTA's shared memory.  Give the
     // latest request of each kind one more bounded wait before the CTA lets go of it.
     if (cb_requested > 0) mbar_wait(&bars[4], (cb_requested - 1) & 1);
@@ -717,7 +566,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_kernel(const __grid_constant__ 
 }
 
 cudaError_t launch_tma(cudaStream_t st, const TcBwdParams& p) {
-  auto kern = tc_bwd_kernel<1, false, true>;
+  auto kern = tc_bwd_direct_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return e;
   kern<<<p.B * p.H, 256, kSmemBytes, st>>>(p);
