@@ -242,7 +242,7 @@ __device__ __forceinline__ void table_cos_sin(const float* tab, int l, int m0, f
 // Raw rows of a tile as the caller stores them, [step][col * R + r], landed by bulk tensor copies of a
 // row map (tc_make_row_map): panels of [LT][<= 256 elements], one per 256 columns.  Heads that walk right
 // to left receive the tile's time range in memory order, so scan step l sits in row LT - 1 - l.
-// Work items are the (step, 16-byte group) pairs of commit_bc.
+// Work items are (step, 16-byte group) pairs (convert_coords).
 // ---------------------------------------------------------------------------------------
 template <int R>
 struct RawTile {

@@ -17,57 +17,11 @@ __device__ __forceinline__ float wrap2pi(float v) { return v - rintf(v * kInvTwo
 __device__ __forceinline__ float expc(float d) { return __expf(fmaxf(d, -60.0f)); }
 __device__ __forceinline__ float inside(float d) { return (d > -60.0f && d < 0.0f) ? 1.0f : 0.0f; }
 
-// sin and cos of an angle already wrapped into [-pi, pi], as polynomials in x^2 on the FMA pipe
-// (max error 3e-7): the special-function unit is the scarcest resource of these kernels.
-__device__ __forceinline__ void sincos_poly(float x, float* sn, float* cs) {
-  const float z = x * x;
-  float s = -2.069813466e-08f;
-  s = fmaf(s, z, 2.708831159e-06f);
-  s = fmaf(s, z, -1.981763099e-04f);
-  s = fmaf(s, z, 8.332791503e-03f);
-  s = fmaf(s, z, -1.666662111e-01f);
-  s = fmaf(s, z, 9.999999378e-01f);
-  float c = 1.724509175e-09f;
-  c = fmaf(c, z, -2.707903082e-07f);
-  c = fmaf(c, z, 2.476988356e-05f);
-  c = fmaf(c, z, -1.388780360e-03f);
-  c = fmaf(c, z, 4.166648922e-02f);
-  c = fmaf(c, z, -4.999998910e-01f);
-  c = fmaf(c, z, 9.999999891e-01f);
-  *sn = x * s;
-  *cs = c;
-}
-
 // Index of angle (l, m) in a [LT][64] float buffer whose 16-byte chunks are XOR-swizzled by
 // l & 7: threads that own different rows read the same plane group without bank conflicts.
 __device__ __forceinline__ int phi_idx(int l, int m) { return l * kNH + ((((m >> 2) ^ (l & 7)) << 2) | (m & 3)); }
 
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
-
-// Ask L2 for every input row of tile `t0` (and a 16 KB checkpoint), one 128-byte line per thread
-// and tensor: the real loads of that tile, a whole tile period later, then hit L2.
-template <int R, bool ROT>
-__device__ __forceinline__ void prefetch_tile_l2(const __nv_bfloat16* gb, const __nv_bfloat16* gc, const __nv_bfloat16* gx,
-                                                 const __nv_bfloat16* gdy, const __nv_bfloat16* gth, const void* ckpt,
-                                                 size_t tok0, int H, int T, int t0) {
-  constexpr int LT = kRows / R;
-  const int tid = threadIdx.x;
-  {  // B and C: LT rows of 256 R bytes = 2R lines each -> exactly 256 lines per tensor
-    const int l = tid / (2 * R), j = tid % (2 * R);
-    if (t0 + l < T) {
-      const size_t off = (tok0 + (size_t)l * H) * kN * R + (size_t)j * 64;
-      prefetch_l2(gb + off);
-      prefetch_l2(gc + off);
-    }
-  }
-  {  // x (threads 0..127) and dy (threads 128..255): LT rows of R lines
-    const int u = tid & 127, l = u / R, j = u % R;
-    const __nv_bfloat16* g = (tid < 128) ? gx : gdy;
-    if (g && t0 + l < T) prefetch_l2(g + (tok0 + (size_t)l * H) * kP * R + (size_t)j * 64);
-  }
-  if (ROT && tid < LT && t0 + tid < T) prefetch_l2(gth + (tok0 + (size_t)tid * H) * kNH);
-  if (ckpt && tid >= 128) prefetch_l2(static_cast<const char*>(ckpt) + (size_t)(tid - 128) * 128);
-}
 
 template <int R>
 __device__ __forceinline__ void load_row_group(const __nv_bfloat16* src, bool live, uint32_t (&raw)[4 * R]) {
@@ -115,12 +69,6 @@ __device__ __forceinline__ float row_factor(float ac_l, float ac_e) {
   return __expf(fminf(fmaxf(ac_l - ac_e, -87.0f), 80.0f));
 }
 
-// The per-tile scalars are the work of warps 1-7: warp 0 holds the thread that issues the tensor-core
-// products, and that thread is held up by the tensor pipe for as long as the products run, so it must
-// not be needed at a barrier meanwhile.  Warps 1-7 meet at named barrier 1 (224 threads); every one
-// of their threads must reach each of its uses.
-__device__ __forceinline__ void scalar_warps_sync() { asm volatile("bar.sync 1, 224;" ::: "memory"); }
-
 // dt and lambda of step t0 + i in thread 32 + i (i <= LT: one step of look-ahead), as registers, so
 // the loads of the NEXT tile can be in flight while the current one computes.
 template <int R>
@@ -136,6 +84,12 @@ __device__ __forceinline__ void load_dt_lam(float& vdt, float& vl, const __nv_bf
     vl = disc == 0 ? 1.0f : (disc == 1 ? 0.5f : bf(lam, i));
   }
 }
+
+// In the direct kernels the per-tile scalars are the work of warps 1-7: warp 0 holds the thread that issues
+// the tensor-core products, and that thread is held up by the tensor pipe for as long as the products run, so
+// it must not be needed at a barrier meanwhile.  Warps 1-7 meet at named barrier 1 (224 threads); every one
+// of their threads must reach each of its uses.
+__device__ __forceinline__ void scalar_warps_sync() { asm volatile("bar.sync 1, 224;" ::: "memory"); }
 
 // g, w (shifted add), a = dt A, its inclusive cumulative sum ac, sw = exp(cd - ac) w,
 // eac = exp(ac) and the column factors cf, from the (dt, lambda) registers of load_dt_lam.
@@ -213,70 +167,6 @@ struct RawBC {
   uint32_t v[NIT][2][NP][4 * R];
 };
 
-template <int R, bool ROT>
-__device__ __forceinline__ void issue_bc(RawBC<R, ROT>& raw, const __nv_bfloat16* gb, const __nv_bfloat16* gc,
-                                         size_t tok0, int H, int T, int t0) {
-  using RB = RawBC<R, ROT>;
-#pragma unroll
-  for (int i = 0; i < RB::NIT; ++i) {
-    int l, grp;
-    item_coords<RB::GB>(i, l, grp);
-    const bool live = t0 + l < T;
-    const size_t base = (tok0 + (size_t)l * H) * kN * R + (size_t)grp * 8 * R;
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {
-      const __nv_bfloat16* src = which ? gc : gb;
-#pragma unroll
-      for (int part = 0; part < RB::NP; ++part)
-        load_row_group<R>(src + base + (size_t)part * kNH * R, live, raw.v[i][which][part]);
-    }
-  }
-}
-
-template <int R, bool ROT>
-__device__ __forceinline__ void commit_bc(const RawBC<R, ROT>& raw, uint8_t* sB, uint8_t* sC, const float* sPhi) {
-  using RB = RawBC<R, ROT>;
-#pragma unroll
-  for (int i = 0; i < RB::NIT; ++i) {
-    int l, grp;
-    item_coords<RB::GB>(i, l, grp);
-    const int n0 = grp * 8;
-    if (ROT) {
-      float cs[8], sn[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) sincos_poly(sPhi[phi_idx(l, n0 + j)], &sn[j], &cs[j]);
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        uint8_t* dst = which ? sC : sB;
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-          float o1[8], o2[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float v1 = elem(raw.v[i][which][0], j * R + r), v2 = elem(raw.v[i][which][RB::NP - 1], j * R + r);
-            o1[j] = v1 * cs[j] + v2 * sn[j];
-            o2[j] = v2 * cs[j] - v1 * sn[j];
-          }
-          store_chunk(dst, tile_off(l * R + r, n0, kN), o1);
-          store_chunk(dst, tile_off(l * R + r, n0 + kNH, kN), o2);
-        }
-      }
-    } else {
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        uint8_t* dst = which ? sC : sB;
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-          float o[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = elem(raw.v[i][which][0], j * R + r);
-          store_chunk(dst, tile_off(l * R + r, n0, kN), o);
-        }
-      }
-    }
-  }
-}
-
 template <int R>
 struct RawPX {
   static constexpr int NIT = 4 / R;
@@ -309,70 +199,6 @@ __device__ __forceinline__ void commit_px(const RawPX<R>& raw, uint8_t* s_plain,
       store_chunk(s_scaled, tile_off(l * R + r, grp * 8, kP), ow);
     }
   }
-}
-
-// theta of a tile: [LT][64] bf16, 16-byte chunks spread over the CTA.
-template <int R>
-struct RawTheta {
-  static constexpr int NIT = 4 / R;
-  uint4 v[NIT];
-};
-
-template <int R>
-__device__ __forceinline__ void issue_theta(RawTheta<R>& raw, const __nv_bfloat16* theta, size_t tok0, int H, int T, int t0) {
-#pragma unroll
-  for (int i = 0; i < RawTheta<R>::NIT; ++i) {
-    const int c = threadIdx.x + 256 * i, l = c >> 3, c8 = c & 7;
-    raw.v[i] = (t0 + l < T) ? __ldg(reinterpret_cast<const uint4*>(theta + (tok0 + (size_t)l * H) * kNH + c8 * 8))
-                            : make_uint4(0u, 0u, 0u, 0u);
-  }
-}
-
-// Store the raw theta rows at the start of the angle buffer (row pitch 128 bytes).
-template <int R>
-__device__ __forceinline__ void commit_theta(const RawTheta<R>& raw, float* sPhi) {
-  uint4* dst = reinterpret_cast<uint4*>(sPhi);
-#pragma unroll
-  for (int i = 0; i < RawTheta<R>::NIT; ++i) dst[threadIdx.x + 256 * i] = raw.v[i];
-}
-
-// As tile_angles, but theta comes from the raw rows commit_theta left in the angle buffer
-// (they are consumed before any angle is written: one __syncthreads separates the passes).
-// With TABLE the buffer receives half2(cos phi, sin phi) words instead of the angles, for readers
-// that need the rotation many times per angle.
-template <int R, bool TABLE = false>
-__device__ __forceinline__ float tile_angles_smem(float* sPhi, float* s_q, const float* carry, const float* s_dt,
-                                                  int T, int t0, float* angle_out_bh) {
-  constexpr int LT = kRows / R, LQ = LT / 4;
-  const __nv_bfloat16* raw = reinterpret_cast<const __nv_bfloat16*>(sPhi);
-  const int tid = threadIdx.x, q = tid >> 6, m = tid & 63;
-  float loc[LQ];
-  float run = 0.0f;
-#pragma unroll
-  for (int i = 0; i < LQ; ++i) {
-    const int l = q * LQ + i;
-    run += s_dt[l] * __bfloat162float(raw[l * kNH + m]);
-    loc[i] = run;
-  }
-  s_q[q * 64 + m] = run;
-  __syncthreads();
-  float off = carry[m];
-  for (int qq = 0; qq < q; ++qq) off += s_q[qq * 64 + m];
-#pragma unroll
-  for (int i = 0; i < LQ; ++i) {
-    const int l = q * LQ + i;
-    const float wv = wrap2pi(loc[i] + off);
-    if (TABLE) {
-      float sn, cs;
-      sincos_poly(wv, &sn, &cs);
-      const __half2 h2 = __floats2half2_rn(cs, sn);
-      sPhi[phi_idx(l, m)] = __uint_as_float(*reinterpret_cast<const uint32_t*>(&h2));
-    } else {
-      sPhi[phi_idx(l, m)] = wv;
-    }
-    if (angle_out_bh && t0 + l == T - 1) angle_out_bh[m] = wv;
-  }
-  return wrap2pi(off + s_q[3 * 64 + m]);
 }
 
 // Per-source scalars of the 16 columns [c0, c0 + 16) of a band chunk: 16 / R distinct time steps.
