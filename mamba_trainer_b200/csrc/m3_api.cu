@@ -3,6 +3,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
 
 #include "m3_internal.h"
@@ -110,6 +111,52 @@ int make_dims(m3_ctx* ctx, const m3_scan_desc& s, m3::Dims* out) {
 
 namespace {
 
+// Launches whose CTAs wait on one another (stripes cut into segments) must not share the GPU with another such
+// launch: each could hold SMs the other's unscheduled CTAs are waited for on, and both would sit out their
+// bounded waits.  Within this process they are therefore chained across streams: a launch waits for the event
+// the previous one of the device recorded behind itself.  (They fill every SM anyway, so nothing is lost; launches
+// that wait on nobody - whole stripes, other libraries' kernels - finish on their own and need no such care.)
+// Streams under capture are left alone: a captured graph replays alone on its stream.
+struct SplitChain {
+  std::mutex mu;
+  cudaEvent_t ev[64] = {};
+  bool recorded[64] = {};
+};
+SplitChain& split_chain() {
+  static SplitChain c;
+  return c;
+}
+cudaError_t split_chain_enter(m3_ctx* ctx) {
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(ctx->stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return cudaSuccess;
+  }
+  const int dev = ctx->device;
+  if (dev < 0 || dev >= 64) return cudaSuccess;
+  SplitChain& c = split_chain();
+  std::lock_guard<std::mutex> lock(c.mu);
+  return c.recorded[dev] ? cudaStreamWaitEvent(ctx->stream, c.ev[dev], 0) : cudaSuccess;
+}
+void split_chain_leave(m3_ctx* ctx) {
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(ctx->stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return;
+  }
+  const int dev = ctx->device;
+  if (dev < 0 || dev >= 64) return;
+  SplitChain& c = split_chain();
+  std::lock_guard<std::mutex> lock(c.mu);
+  if (!c.ev[dev] && cudaEventCreateWithFlags(&c.ev[dev], cudaEventDisableTiming) != cudaSuccess) {
+    c.ev[dev] = nullptr;
+    cudaGetLastError();
+    return;
+  }
+  if (cudaEventRecord(c.ev[dev], ctx->stream) == cudaSuccess) c.recorded[dev] = true;
+  else cudaGetLastError();
+}
+
 // Time segments of the stripes for one launch of the role-split kernels: the plan, and - when a stripe is
 // cut - the hand-over scratch (state, angle, flags; the flags zeroed on the stream).  `*scratch` is null
 // when nothing is handed over; the caller frees it on the stream after the launch.
@@ -125,7 +172,9 @@ cudaError_t plan_segments(m3_ctx* ctx, Params& p, int tiles, bool allow_split, c
   p.seg_state = reinterpret_cast<float*>(*scratch);
   p.seg_angle = p.seg_state + items * 64 * 128;
   p.seg_flag = reinterpret_cast<int*>(p.seg_angle + items * 64);
-  return cudaMemsetAsync(p.seg_flag, 0, items * sizeof(int), ctx->stream);
+  e = cudaMemsetAsync(p.seg_flag, 0, items * sizeof(int), ctx->stream);
+  if (e == cudaSuccess) e = split_chain_enter(ctx);
+  return e;
 }
 
 // Backward of a forward that ran the tensor-core family: one stripe kernel, then the shared
@@ -184,7 +233,10 @@ int tc_backward_call(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* i
   char* seg = nullptr;
   cudaError_t e = plan_segments(ctx, p, tiles, !p.use_tma, &seg);
   if (e == cudaSuccess) e = m3::tc_backward(ctx->stream, p, d.rot != 0);
-  if (seg) cudaFreeAsync(seg, ctx->stream);
+  if (seg) {
+    split_chain_leave(ctx);
+    cudaFreeAsync(seg, ctx->stream);
+  }
   if (e == cudaSuccess) {
     ctx->launches += 1;
     void* ddt = want(M3_GRAD_DT, g->ddt) ? g->ddt : nullptr;
@@ -416,7 +468,10 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
     char* seg = nullptr;
     cudaError_t te = plan_segments(ctx, p, m3::tc_tiles(d.T, d.R), !p.use_tma && !ctx->no_scratch, &seg);
     if (te == cudaSuccess) te = m3::tc_forward(ctx->stream, p, d.rot != 0);
-    if (seg) cudaFreeAsync(seg, ctx->stream);
+    if (seg) {
+      split_chain_leave(ctx);
+      cudaFreeAsync(seg, ctx->stream);
+    }
     if (te != cudaSuccess) {
       if (base) cudaFreeAsync(base, ctx->stream);
       return cuda_fail(ctx, te, "tensor-core forward");

@@ -447,6 +447,34 @@ def test_time_segments_leave_results_unchanged(rank, rot, seq, rev):
         assert torch.allclose(gr[n].double(), v, rtol=1e-4, atol=1e-4), n
 
 
+def test_cut_stripe_launches_on_two_streams_do_not_wait_on_each_other():
+    """Two launches whose CTAs wait on one another must not share the GPU (each could hold SMs the other's
+    unscheduled CTAs are waited for on): the library chains them across streams.  Two cut-stripe scans
+    enqueued back to back on two streams finish without a wait giving up and equal the same scans run alone."""
+    from mamba_trainer_b200.ssm.scan import Context
+    w = tc_workload(2, True, 2000, batch=5, heads=32)
+    ts = [synthetic.make_inputs(w, seed=s_, device="cuda") for s_ in (11, 12)]
+
+    def run(t):
+        inp = ScanInputs.new(t["x"], t["b"], t["c"], t["dt"], t["a_log"], t["lam"]).with_chunk_size(w.chunk)
+        inp = inp.with_theta(t["theta"]).with_skip(t["d_skip"]).with_state_output(False).with_path(2)
+        with torch.no_grad():
+            return mamba3_scan(inp).y
+
+    alone = [run(t) for t in ts]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    both = []
+    for _ in range(3):
+        for t, st in zip(ts, streams):
+            with torch.cuda.stream(st):
+                both.append(run(t))
+    torch.cuda.synchronize()
+    Context.for_device(torch.device("cuda")).sync()     # raises if a bounded wait gave up
+    for i, y in enumerate(both):
+        assert torch.equal(y, alone[i % 2]), i
+
+
 # ---- bidirectional mixer: the last heads walk right to left (models/mamba3.rs:352-370, :548-556) -----
 
 @pytest.mark.parametrize("B,T,H,P,N,R,L,rot,state,rev", [
