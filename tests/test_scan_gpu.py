@@ -299,14 +299,17 @@ def test_bf16_configs_full_size(idx):
 
 # ---- a bounded device-side wait that runs out (no fault, no hang: the kernels give up and say so) ----
 
-@pytest.mark.parametrize("idx,kw", [(4, dict(batch=1, heads=2, seq=700)), (1, dict(batch=1, heads=2, seq=512))])
+@pytest.mark.parametrize("idx,kw", [(4, dict(batch=1, heads=2, seq=700)), (1, dict(batch=1, heads=2, seq=512)),
+                                    (4, dict(batch=5, heads=32, seq=640))])
 def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable(idx, kw):
     """Every device-side wait of the tensor-core kernels has an iteration limit.  With the limit set to one
     poll (m3_ctx_set_wait_limit) the first wait of every CTA gives up before its products or copies have
     finished: the kernels must return by themselves, the condition must surface as DeviceTimeout - at
     Context.sync() and, for callers that never sync, on entry to the next scan call - and once the limit
     is back to its default the same context must compute correct results again.  Covers the role-split
-    kernels (rank 2, rotational) and the direct form (rank 1, real dynamics)."""
+    kernels (rank 2, rotational), the direct form (rank 1, real dynamics) and stripes cut into time segments
+    (160 stripes on 148 SMs: a CTA that gave up still raises its hand-over flag, and the wait for a
+    predecessor's flag is bounded like every other)."""
     from mamba_trainer_b200.error import DeviceTimeout
     from mamba_trainer_b200.ssm import Context
     w = synthetic.WORKLOADS[idx].scaled(**kw)
