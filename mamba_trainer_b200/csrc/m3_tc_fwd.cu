@@ -381,6 +381,9 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
       fence_async_smem();
       tc_fence_before();
       epi_signal(BAR_MID, kPairCount, dead);
+      // this tile's scalars are spent with the band: the look-ahead warp, whose code runs cold and slowly, may
+      // overwrite their set with those of the tile after next from here on
+      if (g + 2 < total) epi_signal(BAR_FREE, kPairCount, dead);
       // ---- 3. the next tile's angle table, while the second group of products runs (a tile that opens an
       //         item builds its own: its predecessor, which may be this very item, must have handed over) ---
       if (k + 1 < k_hi) angle_table(g + 1, bh, k + 1, rev);
@@ -446,8 +449,6 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
           }
         }
       }
-      // this tile's scalars are spent: the look-ahead warp may overwrite their set with those of the tile after next
-      if (g + 2 < total) epi_signal(BAR_FREE, kPairCount, dead);
       if (hands) {
         if (ROT && tid < kNH) __stcg(p.seg_angle + ((size_t)bh * nseg + seg) * kNH + tid, s_carry[tid]);
         __threadfence();
