@@ -238,7 +238,8 @@ def test_bf16_configs_full_size(idx):
     """The benchmark configurations at their full size (config 4: one GPU's shard of the 8-way run,
     batch 8).  The oracle cannot run them whole, so: (a) sampled (batch, head) stripes - each an
     independent recurrence - against the oracle in float64, values, final state and every per-token
-    gradient; (b) the backward pass is linear in dy: doubling dy doubles every gradient exactly;
+    gradient; (a') d a_log and d D of one head against the oracle summed over all of the head's stripes;
+    (b) the backward pass is linear in dy: doubling dy doubles every gradient exactly;
     (c) two windows with the state carried across equal one pass (tests/ssm.rs:238-310)."""
     w = synthetic.WORKLOADS[idx]
     if idx == 4:
@@ -284,6 +285,21 @@ def test_bf16_configs_full_size(idx):
             assert ref_metric(a_, e_) <= 2e-2, f"dtheta[{b_},{h_}]: reference metric {ref_metric(a_, e_):.3e}"
             assert norm_rel(a_, e_) <= max(2e-2, yard), \
                 f"dtheta[{b_},{h_}]: norm-relative error {norm_rel(a_, e_):.3e}, the reference's bf16 mode: {yard:.3e}"
+    # (a') the per-head parameter gradients of ONE head: d a_log and d D sum over every batch row and token
+    # of the head, so the oracle runs all B stripes of that head and its results are added up
+    h_ = H // 3
+    want = {"a_log": 0.0, "d_skip": 0.0}
+    for b_ in range(B):
+        cut = lambda v: v[b_:b_ + 1, :, h_:h_ + 1].detach().cpu()
+        st = {n: cut(t[n]) for n in ("x", "b", "c", "dt", "lam", "theta", "dy") if t.get(n) is not None}
+        st["a_log"], st["d_skip"] = t["a_log"][h_:h_ + 1].cpu(), t["d_skip"][h_:h_ + 1].cpu()
+        _, _, eg = oracle_run(st, w.chunk, False, torch.float64, True)
+        for n in want:
+            want[n] = want[n] + eg[n].double()
+    for n, e_ in want.items():
+        a_ = g[n][h_:h_ + 1].detach().double().cpu()
+        err = float((a_ - e_).abs() / e_.abs().clamp_min(1.0))
+        assert err <= 2e-2, f"d{n}[head {h_}]: {float(a_):.6g} against {float(e_):.6g} ({err:.3e})"
     # (b) linearity in dy (a factor of two is exact in every format involved)
     g2 = torch.autograd.grad(out.y, [leaf[n] for n in names], grad_outputs=t["dy"] * 2)
     for n, a_, b2 in zip(names, grads, g2):
