@@ -172,7 +172,11 @@ int m3_download(m3_ctx *ctx, void *dst_host, const void *src_device, size_t byte
  * `saved` may be NULL (inference, no rule is built: var.rs:174-180); otherwise it
  * receives a handle the caller frees with m3_saved_free after the last backward.
  * The saved context refers to the input buffers of `desc`: keep them alive and
- * unchanged until then (the reference's closure holds clones, var.rs:210-216). */
+ * unchanged until then (the reference's closure holds clones, var.rs:210-216).
+ * The tensor-core kernel family moves rows as 16-byte vectors: with M3_PATH_AUTO a call whose
+ * x, b, c, theta or y is not 16-byte aligned runs the generic family instead (M3_PATH_TENSOR
+ * refuses it), and the backward of a forward that ran the tensor-core family needs 16-byte
+ * aligned dy, dx, db, dc and dtheta (M3_ERR_UNSUPPORTED otherwise). */
 int m3_scan_forward(m3_ctx *ctx, const m3_scan_desc *desc, const m3_scan_out *out,
                     m3_saved **saved);
 

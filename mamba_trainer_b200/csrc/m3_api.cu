@@ -214,6 +214,11 @@ int tc_backward_call(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* i
   p.err = ctx->dev_err;
   p.B = d.B; p.T = d.T; p.H = d.H; p.R = d.R; p.disc = d.disc; p.rev = d.rev;
   p.wait_limit = ctx->wait_limit ? ctx->wait_limit : (1u << 18);
+  if (!m3::tc_aligned(p.dy) || !m3::tc_aligned(p.dx) || !m3::tc_aligned(p.db) || !m3::tc_aligned(p.dc) ||
+      !m3::tc_aligned(p.dtheta)) {
+    cudaFreeAsync(base, ctx->stream);
+    return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family needs 16-byte aligned dy and gradient buffers");
+  }
   p.use_tma = (d.R == 1 && !d.rot && d.rev == 0 && d.T % 8 == 0 && !(reinterpret_cast<uintptr_t>(p.ckpt_h) & 15) &&
                m3::tc_make_tile_map(&p.tm_b, p.b, d.B, d.T, d.H, 128) && m3::tc_make_tile_map(&p.tm_c, p.c, d.B, d.T, d.H, 128)) ? 1 : 0;
   if (!p.use_tma) {
@@ -422,7 +427,7 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
     return M3_OK;
   }
   if (!out->y) return fail(ctx, M3_ERR_NULL, "y is required");
-  const bool tc_ok = m3::tc_supported(*desc) && !d.raw;
+  const bool tc_ok = m3::tc_supported(*desc) && !d.raw && m3::tc_aligned(out->y);
   if (desc->path == M3_PATH_TENSOR && !tc_ok)
     return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family does not take this shape");
   if (tc_ok && desc->path != M3_PATH_GENERIC) {

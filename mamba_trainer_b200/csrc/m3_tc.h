@@ -10,9 +10,11 @@
 namespace m3 {
 
 // Shapes the family serves: bf16, head_dim 64, d_state 128, rank 1, 2 or 4.
+// 16-byte alignment: the kernels move rows as 16-byte vectors and bulk tensor copies.
+inline bool tc_aligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 inline bool tc_supported(const m3_scan_desc& s) {
   return s.dtype == M3_BF16 && s.head_dim == 64 && s.d_state == 128 && (s.rank == 1 || s.rank == 2 || s.rank == 4) &&
-         s.seq > 0;
+         s.seq > 0 && tc_aligned(s.x) && tc_aligned(s.b) && tc_aligned(s.c) && tc_aligned(s.theta);
 }
 // Time steps per 128-row tile and tiles per stripe.
 inline int tc_tile_steps(int rank) { return 128 / rank; }

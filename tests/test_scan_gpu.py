@@ -494,6 +494,31 @@ def test_cut_stripe_launches_on_two_streams_do_not_wait_on_each_other():
         assert torch.equal(y, alone[i % 2]), i
 
 
+def test_misaligned_rows_take_the_generic_family():
+    """The tensor-core kernels move rows as 16-byte vectors and bulk tensor copies.  An input that is not
+    16-byte aligned (a view that starts one element into its buffer) is served by the generic family when the
+    path is left to the library, and refused when the tensor-core family is asked for by name."""
+    from mamba_trainer_b200.error import UnsupportedError
+    w = tc_workload(2, True, 200)
+    t = synthetic.make_inputs(w, seed=9, device="cuda")
+    flat = torch.empty(t["x"].numel() + 8, dtype=t["x"].dtype, device="cuda")
+    off = flat[1:1 + t["x"].numel()].view(t["x"].shape)
+    off.copy_(t["x"])
+    assert off.data_ptr() % 16 != 0 and off.is_contiguous()
+
+    def run(path):
+        inp = ScanInputs.new(off, t["b"], t["c"], t["dt"], t["a_log"], t["lam"]).with_chunk_size(w.chunk)
+        inp = inp.with_theta(t["theta"]).with_skip(t["d_skip"]).with_state_output(False).with_path(path)
+        with torch.no_grad():
+            return mamba3_scan(inp).y
+
+    tc = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in t.items()}
+    ey, _, _ = oracle_run(tc, w.chunk, False, torch.float64, False)
+    check_bf16("y", run(0).cpu(), ey)
+    with pytest.raises(UnsupportedError):
+        run(2)
+
+
 # ---- bidirectional mixer: the last heads walk right to left (models/mamba3.rs:352-370, :548-556) -----
 
 @pytest.mark.parametrize("B,T,H,P,N,R,L,rot,state,rev", [
