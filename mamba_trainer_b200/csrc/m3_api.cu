@@ -18,6 +18,8 @@ struct m3_saved {
   m3::GenericWs gws;
   __nv_bfloat16* tc_ckpt_h = nullptr;  // tensor-core family: bf16 state entering each tile
   float* tc_ckpt_angle = nullptr;  // and the angle entering each tile
+  bool tc_direct = false;          // written by the direct form (state copy [p][n]) rather than the role-split
+                                   // kernels ([n][p]): the backward pass must be of the same form
   cudaStream_t stream = nullptr;   // the stream the forward ran on: the scratch is freed in its order
 };
 
@@ -219,8 +221,12 @@ int tc_backward_call(m3_ctx* ctx, const m3_saved* saved, const m3_scan_bwd_in* i
     cudaFreeAsync(base, ctx->stream);
     return fail(ctx, M3_ERR_UNSUPPORTED, "the tensor-core family needs 16-byte aligned dy and gradient buffers");
   }
-  p.use_tma = (d.R == 1 && !d.rot && d.rev == 0 && d.T % 8 == 0 && !(reinterpret_cast<uintptr_t>(p.ckpt_h) & 15) &&
+  p.use_tma = (saved->tc_direct && d.R == 1 && !d.rot && d.rev == 0 && d.T % 8 == 0 && !(reinterpret_cast<uintptr_t>(p.ckpt_h) & 15) &&
                m3::tc_make_tile_map(&p.tm_b, p.b, d.B, d.T, d.H, 128) && m3::tc_make_tile_map(&p.tm_c, p.c, d.B, d.T, d.H, 128)) ? 1 : 0;
+  if (saved->tc_direct && !p.use_tma) {
+    cudaFreeAsync(base, ctx->stream);
+    return fail(ctx, M3_ERR_UNSUPPORTED, "the forward pass ran the direct form; its backward pass cannot be set up");
+  }
   if (!p.use_tma) {
     if (!m3::tc_make_row_map(&p.tm_b, p.b, d.B, d.T, d.H, 128 * d.R, steps, true) ||
         !m3::tc_make_row_map(&p.tm_c, p.c, d.B, d.T, d.H, 128 * d.R, steps, true) ||
@@ -495,6 +501,7 @@ int m3_scan_forward(m3_ctx* ctx, const m3_scan_desc* desc, const m3_scan_out* ou
       sv->ws_bytes = bytes;
       sv->tc_ckpt_h = p.ckpt_h;
       sv->tc_ckpt_angle = p.ckpt_angle;
+      sv->tc_direct = p.use_tma != 0;
       sv->stream = ctx->stream;
       *saved = sv;
     }

@@ -231,7 +231,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
         if (!ckpt_ok && p.err) raise_flag(p.err);
         tc_fence_after();
         gemm_issue(tm + TM_DM, k_major(smem_u32(sDY), kP), k_major(smem_u32(sX), kP), make_idesc(128, 0, 0), kP, false);
-        gemm_issue(tm + TM_T1, k_major(smem_u32(sDY), kP), mn_major(smem_u32(sHS), kN), make_idesc(128, 0, 1), kP, false);
+        gemm_issue(tm + TM_T1, k_major(smem_u32(sDY), kP), k_major(smem_u32(sHS), kP), make_idesc(128, 0, 0), kP, false);
       }
       __syncwarp();
       bar_sync(BAR_OPS, kPairCount);  // C^ and B^ staged
@@ -246,8 +246,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
         tc_fence_after();
         const uint32_t aM = smem_u32(sM), aDG = smem_u32(sDG), aC = smem_u32(sC), aB = smem_u32(sB), aHS = smem_u32(sHS);
         gemm_issue(tm + TM_DX, mn_major(aM, kRows), mn_major(smem_u32(sDY), kP), make_idesc(64, 1, 1), kRows, false);
-        gemm_issue(tm + TM_U, k_major(aB, kN), k_major(aHS, kN), make_idesc(64, 0, 0), kN, false);
-        gemm_issue(tm + TM_DB, k_major(smem_u32(sXw), kP), mn_major(aHS, kN), make_idesc(128, 0, 1), kP, false);
+        gemm_issue(tm + TM_U, k_major(aB, kN), mn_major(aHS, kP), make_idesc(64, 0, 1), kN, false);
+        gemm_issue(tm + TM_DB, k_major(smem_u32(sXw), kP), k_major(aHS, kP), make_idesc(128, 0, 0), kP, false);
         // every product that reads dS is in this first group: the dx epilogue, which runs while the other
         // three products do, stages its result in dS's buffer
         umma_commit(&bars[1]);
@@ -491,16 +491,17 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
           tmem_st16(tmem_addr(tm, quad * 32, TM_T1 + n0), t1[cc]);
         }
         part_t1[ch * 128 + row] = dot2.x + dot2.y;
-        // state gradient: lanes are n, columns p
+        // state gradient: lanes are n, columns p; H_k and dS_k are kept [n][p], so a thread's 16 columns are
+        // two 16-byte pieces of its own row
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
           const int p0 = 32 * ch + 16 * cc;
+          float hk[16];
+          load_chunk(sHS, tile_off(row, p0, kP), *reinterpret_cast<float(*)[8]>(&hk[0]));
+          load_chunk(sHS, tile_off(row, p0 + 8, kP), *reinterpret_cast<float(*)[8]>(&hk[8]));
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            __nv_bfloat16* slot = reinterpret_cast<__nv_bfloat16*>(sHS + tile_off(p0 + j, row, kN));
-            dcd_part += dhv[cc][j] * __bfloat162float(*slot);  // <dH, H_k>
-            *slot = __float2bfloat16_rn(dhv[cc][j]);           // dS_k replaces H_k
-          }
+          for (int j = 0; j < 16; ++j) dcd_part += dhv[cc][j] * hk[j];  // <dH, H_k>
+          store_row16(sHS, row, p0, kP, dhv[cc]);                        // dS_k replaces H_k
 #pragma unroll
           for (int j = 0; j < 16; j += 2) {
             const float2 v = __fmul2_rn(make_float2(dhv[cc][j], dhv[cc][j + 1]), make_float2(ecd, ecd));

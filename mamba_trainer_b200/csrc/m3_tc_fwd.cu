@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
       if (lane == 0) {
         tc_fence_after();
         const Operand aC = k_major(smem_u32(sC), kN);
-        gemm_issue(tm + TM_Y, aC, k_major(smem_u32(sH), kN), make_idesc(64, 0, 0), kN, false);
+        gemm_issue(tm + TM_Y, aC, mn_major(smem_u32(sH), kP), make_idesc(64, 0, 1), kN, false);
         gemm_issue(tm + TM_G, aC, k_major(smem_u32(sB), kN), make_idesc(128, 0, 0), kN, false);
         umma_commit(&bars[0]);
         if (p.ckpt_h) {
@@ -277,8 +277,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
               if (seg == 0) s_ += first * p.lu0[(size_t)bh * kP * kN + o];
             }
             v[j] = s_;
-            *reinterpret_cast<__nv_bfloat16*>(sH + tile_off(p0 + j, row, kN)) = __float2bfloat16_rn(s_);
           }
+          store_row16(sH, row, p0, kP, v);
           tmem_st16(tmem_addr(tm, quad * 32, TM_H + p0), v);
         }
         tmem_wait_st();
@@ -419,10 +419,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
             }
           }
           stage_out16<R>(sXw, row, p0, v, rev);  // sigma_w X~ is spent: its buffer stages y
-          // refresh the bf16 copy of the state (lane = n = row, columns = p)
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            *reinterpret_cast<__nv_bfloat16*>(sH + tile_off(p0 + j, row, kN)) = __float2bfloat16_rn(hv[cc][j]);
+          // refresh the bf16 copy of the state: this thread's row n, 16 columns p at a time
+          store_row16(sH, row, p0, kP, hv[cc]);
           if (k == ntiles - 1 && p.h_out) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) p.h_out[((size_t)bh * kP + p0 + j) * kN + row] = hv[cc][j];

@@ -46,6 +46,14 @@ __device__ __forceinline__ void store_chunk(uint8_t* base, uint32_t off, const f
   q.x = pack_bf16(v[0], v[1]); q.y = pack_bf16(v[2], v[3]); q.z = pack_bf16(v[4], v[5]); q.w = pack_bf16(v[6], v[7]);
   *reinterpret_cast<uint4*>(base + off) = q;
 }
+// 16 consecutive columns of one row of an operand buffer [rows x cols] (col0 a multiple of 8)
+__device__ __forceinline__ void store_row16(uint8_t* base, int row, int col0, int cols, const float (&v)[16]) {
+  float lo[8], hi[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { lo[j] = v[j]; hi[j] = v[8 + j]; }
+  store_chunk(base, tile_off(row, col0, cols), lo);
+  store_chunk(base, tile_off(row, col0 + 8, cols), hi);
+}
 // 8 consecutive bf16 of an operand buffer as floats
 __device__ __forceinline__ void load_chunk(const uint8_t* base, uint32_t off, float (&v)[8]) {
   const uint4 q = *reinterpret_cast<const uint4*>(base + off);
