@@ -393,6 +393,7 @@ __device__ __forceinline__ void convert_bc(const uint8_t* rawB, const uint8_t* r
     int l, grp;
     convert_coords<RB::GB, R>(i, l, grp);
     const int n0 = grp * 8;
+    const int rot = rank_rotation<R>();  // the order of the ranks differs by lane: see rank_rotation
     float cs[8], sn[8];
     if (ROT) table_cos_sin(tab, l, n0, cs, sn);
 #pragma unroll
@@ -404,12 +405,13 @@ __device__ __forceinline__ void convert_bc(const uint8_t* rawB, const uint8_t* r
       for (int part = 0; part < RB::NP; ++part)
         load_raw_pieces<R>(src, l, (uint32_t)(n0 + part * kNH) * R, rev, v[part]);
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
+      for (int rr = 0; rr < R; ++rr) {
+        const int r = rr ^ rot;
         if (ROT) {
           float o1[8], o2[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const float v1 = elem(v[0], j * R + r), v2 = elem(v[RB::NP - 1], j * R + r);
+            const float v1 = elem_rank<R>(v[0], j, r), v2 = elem_rank<R>(v[RB::NP - 1], j, r);
             o1[j] = v1 * cs[j] + v2 * sn[j];
             o2[j] = v2 * cs[j] - v1 * sn[j];
           }
@@ -418,7 +420,7 @@ __device__ __forceinline__ void convert_bc(const uint8_t* rawB, const uint8_t* r
         } else {
           float o[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = elem(v[0], j * R + r);
+          for (int j = 0; j < 8; ++j) o[j] = elem_rank<R>(v[0], j, r);
           store_chunk(dst, tile_off(l * R + r, n0, kN), o);
         }
       }
@@ -447,11 +449,13 @@ __device__ __forceinline__ void store_px(const RawPX<R>& raw, uint8_t* s_plain, 
     int l, grp;
     convert_coords<2, R>(i, l, grp);
     const float sv = scale[l];
+    const int rot = rank_rotation<R>();
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
+    for (int rr = 0; rr < R; ++rr) {
+      const int r = rr ^ rot;
       float o[8], ow[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { o[j] = elem(raw.v[i], j * R + r); ow[j] = o[j] * sv; }
+      for (int j = 0; j < 8; ++j) { o[j] = elem_rank<R>(raw.v[i], j, r); ow[j] = o[j] * sv; }
       store_chunk(s_plain, tile_off(l * R + r, grp * 8, kP), o);
       store_chunk(s_scaled, tile_off(l * R + r, grp * 8, kP), ow);
     }
@@ -480,18 +484,20 @@ __device__ __forceinline__ void store_bc(const RawBC<R, ROT>& raw, uint8_t* sB, 
     int l, grp;
     convert_coords<RB::GB, R>(i, l, grp);
     const int n0 = grp * 8;
+    const int rot = rank_rotation<R>();  // the order of the ranks differs by lane: see rank_rotation
     float cs[8], sn[8];
     if (ROT) table_cos_sin(tab, l, n0, cs, sn);
 #pragma unroll
     for (int which = 0; which < 2; ++which) {
       uint8_t* dst = which ? sC : sB;
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
+      for (int rr = 0; rr < R; ++rr) {
+        const int r = rr ^ rot;
         if (ROT) {
           float o1[8], o2[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const float v1 = elem(raw.v[i][which][0], j * R + r), v2 = elem(raw.v[i][which][RB::NP - 1], j * R + r);
+            const float v1 = elem_rank<R>(raw.v[i][which][0], j, r), v2 = elem_rank<R>(raw.v[i][which][RB::NP - 1], j, r);
             o1[j] = v1 * cs[j] + v2 * sn[j];
             o2[j] = v2 * cs[j] - v1 * sn[j];
           }
@@ -500,7 +506,7 @@ __device__ __forceinline__ void store_bc(const RawBC<R, ROT>& raw, uint8_t* sB, 
         } else {
           float o[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = elem(raw.v[i][which][0], j * R + r);
+          for (int j = 0; j < 8; ++j) o[j] = elem_rank<R>(raw.v[i][which][0], j, r);
           store_chunk(dst, tile_off(l * R + r, n0, kN), o);
         }
       }

@@ -41,6 +41,31 @@ template <int NREG>
 __device__ __forceinline__ float elem(const uint32_t (&raw)[NREG], int i) {
   return (i & 1) ? bf16_hi(raw[i >> 1]) : bf16_lo(raw[i >> 1]);
 }
+// Operand stores and the banks.  An operand row is 16 bytes of an 8 x 8 core matrix (128 bytes = all 32
+// banks), so the bank group of a 16-byte store is its row & 7, whatever the column.  The conversion's work
+// items lie over a warp as 4 steps x 8 column groups, a quarter warp - the unit a 16-byte store is served in -
+// as 4 steps x 2 groups; step l holds rows l * R + r.  Were every lane to store rank r at the same time, a
+// quarter warp would touch 8 / (2 R) ... 4 distinct bank groups only (rank 2: two-way conflicts, rank 4:
+// four-way).  So the lanes go through the ranks in different orders, r = rr ^ rank_rotation(): for rank 2 the
+// lanes of odd column groups start with rank 1, for rank 4 the order also depends on the step, and the eight
+// rows of a quarter warp's store then fall into eight different bank groups.
+template <int R>
+__device__ __forceinline__ int rank_rotation() {
+  const int lane = threadIdx.x & 31;
+  return R == 2 ? ((lane >> 2) & 1) : (R == 4 ? ((((lane & 3) >> 1) << 1) | ((lane >> 2) & 1)) : 0);
+}
+// Element j of rank r of a rank-interleaved group of 8 R raw values (r may depend on the lane).
+template <int R, int NREG>
+__device__ __forceinline__ float elem_rank(const uint32_t (&raw)[NREG], int j, int r) {
+  if constexpr (R == 1) {
+    return elem(raw, j);
+  } else if constexpr (R == 2) {
+    return __uint_as_float(__byte_perm(raw[j], 0u, (r & 1) ? 0x3244u : 0x1044u));
+  } else {
+    const uint32_t w = (r & 2) ? raw[2 * j + 1] : raw[2 * j];
+    return __uint_as_float(__byte_perm(w, 0u, (r & 1) ? 0x3244u : 0x1044u));
+  }
+}
 __device__ __forceinline__ void store_chunk(uint8_t* base, uint32_t off, const float (&v)[8]) {
   uint4 q;
   q.x = pack_bf16(v[0], v[1]); q.y = pack_bf16(v[2], v[3]); q.z = pack_bf16(v[4], v[5]); q.w = pack_bf16(v[6], v[7]);
@@ -198,11 +223,13 @@ __device__ __forceinline__ void commit_px(const RawPX<R>& raw, uint8_t* s_plain,
     int l, grp;
     item_coords<2>(i, l, grp);
     const float sv = scale[l];
+    const int rot = rank_rotation<R>();
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
+    for (int rr = 0; rr < R; ++rr) {
+      const int r = rr ^ rot;
       float o[8], ow[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { o[j] = elem(raw.v[i], j * R + r); ow[j] = o[j] * sv; }
+      for (int j = 0; j < 8; ++j) { o[j] = elem_rank<R>(raw.v[i], j, r); ow[j] = o[j] * sv; }
       store_chunk(s_plain, tile_off(l * R + r, grp * 8, kP), o);
       store_chunk(s_scaled, tile_off(l * R + r, grp * 8, kP), ow);
     }
