@@ -573,8 +573,9 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
                 for (int jj = 0; jj < 16; ++jj) acc[cc][jj] += add[jj];
               }
             }
-            stage_out16<R>(sHS, row, p0, acc[cc], rev);  // dS is spent: its buffer stages dx
+            if constexpr (R != 2) stage_out16<R>(sHS, row, p0, acc[cc], rev);  // dS is spent: its buffer stages dx
           }
+          if constexpr (R == 2) stage_out32<R>(sHS, row, 32 * ch, acc[0], acc[1], rev);  // rank 2: both halves at once
           part_q[ch * 128 + row] = qp2.x + qp2.y;
           dD_part = dD2.x + dD2.y;
         }
@@ -633,8 +634,13 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
                 }
               }
             }
+            if constexpr (R == 2) {
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) stage_out16<R>(stg, row, gcol(q4), g[q4], rev);
+              for (int q4 = 0; q4 < 4; q4 += 2) stage_out32<R>(stg, row, gcol(q4), g[q4], g[q4 + 1], rev);
+            } else {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) stage_out16<R>(stg, row, gcol(q4), g[q4], rev);
+            }
           };
           finish(gq, sB, sXw, true);     // sigma_w X~ and exp(acum) dY~ are spent: 32 KB to stage dB
 #pragma unroll

@@ -418,7 +418,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
               }
             }
           }
-          stage_out16<R>(sXw, row, p0, v, rev);  // sigma_w X~ is spent: its buffer stages y
+          if constexpr (R != 2) stage_out16<R>(sXw, row, p0, v, rev);  // sigma_w X~ is spent: its buffer stages y
           // refresh the bf16 copy of the state: this thread's row n, 16 columns p at a time
           store_row16(sH, row, p0, kP, hv[cc]);
           if (k == ntiles - 1 && p.h_out) {
@@ -431,6 +431,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
             for (int j = 0; j < 16; ++j) __stcg(dst + (size_t)(p0 + j) * kN + row, hv[cc][j]);
           }
         }
+        if constexpr (R == 2) stage_out32<R>(sXw, row, 32 * ch, yv[0], yv[1], rev);  // rank 2: both halves at once
         if (k == ntiles - 1 && p.lu_out) {
           // last_u = sum_r x_{T-1}^(r) (x) B^_{T-1}^(r), from the staged operands (scan.rs:621-638)
           const int ll = T - 1 - t0;

@@ -325,6 +325,40 @@ __device__ __forceinline__ void stage_out16(uint8_t* stg, int row, int col0, con
     }
   }
 }
+// 32 consecutive columns [col0, col0 + 32) of folded row `row` (col0 a multiple of 32).  Whole warps only.
+// For rank 2 the two lanes of a step split the 32 columns between them - the even lane takes the first 16 of
+// both ranks, the odd lane the last 16 - so that a quarter warp (4 steps x 2 lanes) writes into both 64-byte
+// halves of its rows at once and its eight 16-byte stores fall into eight bank groups; with 16 columns at a
+// time (stage_out16) both lanes of a step write into the same half and every store is served twice.
+template <int R>
+__device__ __forceinline__ void stage_out32(uint8_t* stg, int row, int col0, const float (&va)[16], const float (&vb)[16],
+                                            bool rev) {
+  if constexpr (R != 2) {
+    stage_out16<R>(stg, row, col0, va, rev);
+    stage_out16<R>(stg, row, col0 + 16, vb, rev);
+  } else {
+    using RT = RawTile<R>;
+    const int l = row / R;
+    const bool odd = row & 1;
+    uint32_t wa[8], wb[8], other[8], o[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      wa[i] = pack_bf16(va[2 * i], va[2 * i + 1]);
+      wb[i] = pack_bf16(vb[2 * i], vb[2 * i + 1]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) other[i] = __shfl_xor_sync(0xffffffffu, odd ? wa[i] : wb[i], 1);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      // even lane: ranks (mine, theirs) of the first 16 columns; odd lane: (theirs, mine) of the last 16
+      const uint32_t r0 = odd ? other[k >> 1] : wa[k >> 1], r1 = odd ? wb[k >> 1] : other[k >> 1];
+      o[k] = __byte_perm(r0, r1, (k & 1) ? 0x7632 : 0x5410);
+    }
+    const uint32_t e0 = (uint32_t)(col0 + (odd ? 16 : 0)) * 2u;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) st_shared16(stg + RT::piece(l, e0 + 8u * q, rev), o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+  }
+}
 // May the tile at scan step t0 leave by bulk tensor stores?
 template <int R>
 __device__ __forceinline__ bool tile_leaves_by_map(int has_maps, bool rev, int T, int t0) {
