@@ -400,21 +400,27 @@ __device__ __forceinline__ void load_raw_pieces(const uint8_t* base, int l, uint
   }
 }
 
-// The work items of a tile's conversion: (time step l, 16-byte column group grp) pairs, 4 steps x 8
-// groups per warp as in item_coords, with the bits of the group index permuted so that the two groups a
+// The work items of a tile's conversion: (time step l, 16-byte column group grp) pairs.  Ranks 2 and 4: 4 steps
+// x 8 groups per warp as in item_coords, with the bits of the group index permuted so that the two groups a
 // quarter warp touches lie 4 / R apart: its eight lanes (4 steps x 2 groups) then read eight different
-// 16-byte columns of the swizzled staging rows (a group is R pieces wide; the swizzle XORs the column
-// with step & 7).
+// 16-byte columns of the swizzled staging rows (a group is R pieces wide; the swizzle XORs the column with
+// step & 7), and rank_rotation spreads their operand stores over the bank groups.  Rank 1 has no rank to
+// rotate, so its warp covers 8 steps x 4 groups instead: a quarter warp is eight consecutive steps of one
+// group - eight different rows & 7 for the operand stores, eight different swizzled columns for the reads.
 template <int GB, int R>
 __device__ __forceinline__ void convert_coords(int i, int& l, int& grp) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int w = warp + 8 * i;
   constexpr int GB8 = GB / 2;
   const int g3 = lane >> 2;
-  const int gp = R == 4 ? g3 : (R == 2 ? (((g3 & 1) << 1) | ((g3 >> 1) & 1) | (g3 & 4))
-                                       : (((g3 & 1) << 2) | (g3 & 2) | ((g3 >> 2) & 1)));
-  l = (w / GB8) * 4 + (lane & 3);
-  grp = (w % GB8) * 8 + gp;
+  if constexpr (R == 1) {
+    l = (w / (2 * GB8)) * 8 + (lane & 3) + 4 * (g3 & 1);
+    grp = (w % (2 * GB8)) * 4 + (g3 >> 1);
+  } else {
+    const int gp = R == 4 ? g3 : (((g3 & 1) << 1) | ((g3 >> 1) & 1) | (g3 & 4));
+    l = (w / GB8) * 4 + (lane & 3);
+    grp = (w % GB8) * 8 + gp;
+  }
 }
 
 // Staged raw rows -> rotated (by -phi, from the table), rank-de-interleaved bf16 operands B^, C^.
