@@ -18,8 +18,7 @@ struct m3_saved {
   m3::GenericWs gws;
   __nv_bfloat16* tc_ckpt_h = nullptr;  // tensor-core family: bf16 state entering each tile
   float* tc_ckpt_angle = nullptr;  // and the angle entering each tile
-  bool tc_direct = false;          // written by the direct form (state copy [p][n]) rather than the role-split
-                                   // kernels ([n][p]): the backward pass must be of the same form
+  bool tc_direct = false;          // the forward ran the direct form: so does the backward (same tile maps)
   cudaStream_t stream = nullptr;   // the stream the forward ran on: the scratch is freed in its order
 };
 

@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_direct_kernel(const __grid_cons
       tc_fence_after();
       gemm_issue(tm + TM_G, k_major(smem_u32(sC), kN), k_major(smem_u32(sB), kN), make_idesc(128, 0, 0), kN, false);
       gemm_issue(tm + TM_DM, k_major(smem_u32(sDY), kP), k_major(smem_u32(sX), kP), make_idesc(128, 0, 0), kP, false);
-      gemm_issue(tm + TM_T1, k_major(smem_u32(sDY), kP), mn_major(smem_u32(sHS), kN), make_idesc(128, 0, 1), kP, false);
+      gemm_issue(tm + TM_T1, k_major(smem_u32(sDY), kP), k_major(smem_u32(sHS), kP), make_idesc(128, 0, 0), kP, false);
       umma_commit(&bars[0]);
     }
     // Without a rotation nothing reuses dG's buffer before the next band epilogue, so the 32 KB of dC
@@ -307,16 +307,16 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_direct_kernel(const __grid_cons
         tmem_st16(tmem_addr(tm, quad * 32, TM_T1 + n0), t1[cc]);
       }
       part_t1[ch * 128 + row] = dot2.x + dot2.y;
-      // state gradient: lanes are n, columns p
+      // state gradient: lanes are n, columns p; H_k and dS_k are kept [n][p]
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int p0 = 32 * ch + 16 * cc;
+        float hk[16];
+        load_chunk(sHS, tile_off(row, p0, kP), *reinterpret_cast<float(*)[8]>(&hk[0]));
+        load_chunk(sHS, tile_off(row, p0 + 8, kP), *reinterpret_cast<float(*)[8]>(&hk[8]));
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          __nv_bfloat16* slot = reinterpret_cast<__nv_bfloat16*>(sHS + tile_off(p0 + j, row, kN));
-          dcd_part += dhv[cc][j] * __bfloat162float(*slot);  // <dH, H_k>
-          *slot = __float2bfloat16_rn(dhv[cc][j]);           // dS_k replaces H_k
-        }
+        for (int j = 0; j < 16; ++j) dcd_part += dhv[cc][j] * hk[j];  // <dH, H_k>
+        store_row16(sHS, row, p0, kP, dhv[cc]);                        // dS_k replaces H_k
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
           const float2 v = __fmul2_rn(make_float2(dhv[cc][j], dhv[cc][j + 1]), make_float2(ecd, ecd));
@@ -335,9 +335,9 @@ __global__ void __launch_bounds__(256, 1) tc_bwd_direct_kernel(const __grid_cons
       tc_fence_after();
       const uint32_t aM = smem_u32(sM), aDG = smem_u32(sDG), aC = smem_u32(sC), aB = smem_u32(sB), aHS = smem_u32(sHS);
       gemm_issue(tm + TM_DX, mn_major(aM, kRows), mn_major(smem_u32(sDY), kP), make_idesc(64, 1, 1), kRows, false);
-      gemm_issue(tm + TM_U, k_major(aB, kN), k_major(aHS, kN), make_idesc(64, 0, 0), kN, false);
+      gemm_issue(tm + TM_U, k_major(aB, kN), mn_major(aHS, kP), make_idesc(64, 0, 1), kN, false);
       gemm_issue(tm + TM_DB, mn_major(aDG, kRows), mn_major(aC, kN), make_idesc(128, 1, 1), kRows, false);
-      gemm_issue(tm + TM_DB, k_major(smem_u32(sXw), kP), mn_major(aHS, kN), make_idesc(128, 0, 1), kP, true);
+      gemm_issue(tm + TM_DB, k_major(smem_u32(sXw), kP), k_major(aHS, kP), make_idesc(128, 0, 0), kP, true);
       gemm_issue(tm + TM_T1, k_major(aDG, kRows), mn_major(aB, kN), make_idesc(128, 0, 1), kRows, true);
       gemm_issue(tm + TM_DH, mn_major(aC, kN), mn_major(smem_u32(sDYe), kP), make_idesc(64, 1, 1), kRows, true);
       umma_commit(&bars[1]);

@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_direct_kernel(const __grid_cons
   constexpr int R = 1, LT = kRows;
   uint8_t *sC, *sB, *sX;
   uint8_t* sXw = smem + TO_XW;
-  uint8_t* sH = smem + TO_H;    // bf16 H [p][n]
+  uint8_t* sH = smem + TO_H;    // bf16 H [n][p]: a thread's 16 columns are two 16-byte pieces of its row
   float* sc = reinterpret_cast<float*>(smem + TO_SC);
   // Two sets of per-token scalars: the next tile's are computed while this tile's products run.
   auto scal_set = [&](int i) {
@@ -83,8 +83,8 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_direct_kernel(const __grid_cons
           s = p.h0[o] + first * p.lu0[o];
         }
         v[j] = s;
-        *reinterpret_cast<__nv_bfloat16*>(sH + tile_off(p0 + j, row, kN)) = __float2bfloat16_rn(s);
       }
+      store_row16(sH, row, p0, kP, v);
       tmem_st16(tmem_addr(tm, quad * 32, TM_H + p0), v);
     }
     tmem_wait_st();
@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_direct_kernel(const __grid_cons
     if (tid == 0) {
       tc_fence_after();
       const Operand aC = k_major(smem_u32(sC), kN);
-      gemm_issue(tm + TM_Y, aC, k_major(smem_u32(sH), kN), make_idesc(64, 0, 0), kN, false);
+      gemm_issue(tm + TM_Y, aC, mn_major(smem_u32(sH), kP), make_idesc(64, 0, 1), kN, false);
       gemm_issue(tm + TM_G, aC, k_major(smem_u32(sB), kN), make_idesc(128, 0, 0), kN, false);
       umma_commit(&bars[0]);
     }
@@ -299,9 +299,7 @@ __global__ void __launch_bounds__(256, 1) tc_fwd_direct_kernel(const __grid_cons
           }
         }
         stage_store16<kP>(sXw, row, p0, v);  // sigma_w x is spent: its buffer stages y
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-          *reinterpret_cast<__nv_bfloat16*>(sH + tile_off(p0 + j, row, kN)) = __float2bfloat16_rn(hv[cc][j]);
+        store_row16(sH, row, p0, kP, hv[cc]);
         if (k == ntiles - 1 && p.h_out) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) p.h_out[((size_t)bh * kP + p0 + j) * kN + row] = hv[cc][j];
