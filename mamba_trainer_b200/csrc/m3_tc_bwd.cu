@@ -674,12 +674,16 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
           for (int o = 1; o < R; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
           dphi[j] = v;
         }
-        if (rr == 0) {
+        if (rr == 0) {  // four planes (16 bytes) at a time: the buffer's swizzle moves whole 16-byte pieces
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float v = live ? dphi[j] : 0.0f;
-            if (at_end && p.dangle) v += p.dangle[(size_t)bh * kNH + 32 * ch + j];
-            sDphi[phi_idx(rl, 32 * ch + j)] = v;
+          for (int j = 0; j < 32; j += 4) {
+            float v[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              v[c] = live ? dphi[j + c] : 0.0f;
+              if (at_end && p.dangle) v[c] += p.dangle[(size_t)bh * kNH + 32 * ch + j + c];
+            }
+            *reinterpret_cast<float4*>(&sDphi[phi_idx(rl, 32 * ch + j)]) = make_float4(v[0], v[1], v[2], v[3]);
           }
         }
       }
@@ -696,19 +700,18 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
           thq[i] = (t0 + l < T) ? __ldg(reinterpret_cast<const uint4*>(p.theta + (tok0 + (size_t)l * Hs) * kNH + mg * 8))
                                 : make_uint4(0u, 0u, 0u, 0u);
         }
-        float run = 0.0f;
+        float run = 0.0f, loc[LQ];  // the quarter's running sums wait in registers for the other quarters' totals
 #pragma unroll
         for (int i = LQ - 1; i >= 0; --i) {
-          const int l = q * LQ + i;
-          run += sDphi[phi_idx(l, m)];
-          sDphi[phi_idx(l, m)] = run;
+          run += sDphi[phi_idx(q * LQ + i, m)];
+          loc[i] = run;
         }
         s_q[q * 64 + m] = run;
         epi_sync();
         float off = s_dcar[m];
         for (int qq = 3; qq > q; --qq) off += s_q[qq * 64 + m];
 #pragma unroll
-        for (int i = 0; i < LQ; ++i) sDphi[phi_idx(q * LQ + i, m)] += off;  // d step: sum of d phi from here on
+        for (int i = 0; i < LQ; ++i) sDphi[phi_idx(q * LQ + i, m)] = loc[i] + off;  // d step: sum of d phi from here on
         const float total = off + s_q[0 * 64 + m];  // for q == 0: carry + all four quarters
         epi_sync();
         if (q == 0) {
