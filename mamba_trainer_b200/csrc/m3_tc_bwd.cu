@@ -674,7 +674,20 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
           for (int o = 1; o < R; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
           dphi[j] = v;
         }
-        if (rr == 0) {  // four planes (16 bytes) at a time: the buffer's swizzle moves whole 16-byte pieces
+        // Ranks 1 and 4 store four planes (16 bytes) at a time - the buffer's swizzle moves whole 16-byte pieces -
+        // and keep the scan's running sums in registers; on rank 2 both measured slower (backward + 1.8 % on the
+        // scaling workload: the kernel's timing follows its code layout more than its instruction count), so
+        // rank 2 keeps the plane-by-plane stores and the second pass over shared memory.
+        if constexpr (R == 2) {
+          if (rr == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float v = live ? dphi[j] : 0.0f;
+              if (at_end && p.dangle) v += p.dangle[(size_t)bh * kNH + 32 * ch + j];
+              sDphi[phi_idx(rl, 32 * ch + j)] = v;
+            }
+          }
+        } else if (rr == 0) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
             float v[4];
@@ -700,18 +713,22 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
           thq[i] = (t0 + l < T) ? __ldg(reinterpret_cast<const uint4*>(p.theta + (tok0 + (size_t)l * Hs) * kNH + mg * 8))
                                 : make_uint4(0u, 0u, 0u, 0u);
         }
-        float run = 0.0f, loc[LQ];  // the quarter's running sums wait in registers for the other quarters' totals
+        float run = 0.0f, loc[R == 2 ? 1 : LQ];  // (not rank 2:) the quarter's running sums wait in registers
 #pragma unroll
         for (int i = LQ - 1; i >= 0; --i) {
           run += sDphi[phi_idx(q * LQ + i, m)];
-          loc[i] = run;
+          if constexpr (R == 2) sDphi[phi_idx(q * LQ + i, m)] = run;
+          else loc[i] = run;
         }
         s_q[q * 64 + m] = run;
         epi_sync();
         float off = s_dcar[m];
         for (int qq = 3; qq > q; --qq) off += s_q[qq * 64 + m];
 #pragma unroll
-        for (int i = 0; i < LQ; ++i) sDphi[phi_idx(q * LQ + i, m)] = loc[i] + off;  // d step: sum of d phi from here on
+        for (int i = 0; i < LQ; ++i) {  // d step: sum of d phi from here on
+          if constexpr (R == 2) sDphi[phi_idx(q * LQ + i, m)] += off;
+          else sDphi[phi_idx(q * LQ + i, m)] = loc[i] + off;
+        }
         const float total = off + s_q[0 * 64 + m];  // for q == 0: carry + all four quarters
         epi_sync();
         if (q == 0) {
