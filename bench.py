@@ -34,7 +34,7 @@ NCU_TRAFFIC_BYTES_PER_TOKEN_HEAD = {
     "cfg1_siso_trapezoid_bf16": 267403520 / (8 * 2048 * 12),
     # profiles/tc_fwd_bwd_kernels_cfg4.md: batch 4 x seq 4096 (whole stripes) and batch 8 x seq 4096 (stripes cut
     # into time segments, which adds the hand-over of the state between segments)
-    "cfg4_mimo2_scaling_bf16": {"whole": 1722.7e6 / (4 * 4096 * 32), "split": 3560.2e6 / (8 * 4096 * 32)},
+    "cfg4_mimo2_scaling_bf16": {"whole": 1722.7e6 / (4 * 4096 * 32), "split": 3560.8e6 / (8 * 4096 * 32)},
 }
 
 
