@@ -26,7 +26,7 @@
 namespace m3tc {
 
 constexpr int kEpiThreads = 256, kCtaThreads = 384, kPairCount = kEpiThreads + 32;
-constexpr int kIssuerWarp = 8, kScalarWarp = 9, kCopyWarp = 10, kTailWarp = 11;
+constexpr int kIssuerWarp = 8, kScalarWarp = 9, kCopyWarp = 10;  // warp 11 idles
 
 // Named barriers (0 is __syncthreads).
 enum : int {
@@ -39,10 +39,7 @@ enum : int {
   BAR_FREE = 5,   // 288: a set of scalars is free again (epilogue warps arrive; look-ahead warp syncs)
   BAR_TAIL = 6,   // 288: a tile's gradients are staged, its operands spent (epilogue warps arrive; copy warp syncs)
   BAR_OPS0 = 9,   // 288: the x / dy operands of a tile are staged, ahead of B and C (epilogue warps arrive; issuer syncs)
-  BAR_TAILREADY = 8,   // 288: a backward tile's partial sums are complete (epilogue warps arrive; tail warp syncs)
-  BAR_TAILDONE = 10,   // 288: the tail warp has finished a tile's per-token scalars (it arrives; epilogue warps sync)
 };
-
 
 __device__ __forceinline__ void bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
