@@ -291,14 +291,15 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
       // ---- 1. stage the operands ---------------------------------------------------------------
       if (!dead) dead = !warp_all(mbar_wait(&bars[2], g & 1, wait_limit));
       if (!dead) convert_bc<R, ROT>(rawB, rawC, sB, sC, sTab, rev);
+      fence_async_smem();
+      tc_fence_before();
+      epi_signal(BAR_OPS, kEpiThreads + 64, dead);
+      // X~ and sigma_w X~ are operands of the second group only: they are staged while the first group runs
       if (g > 0) {  // sigma_w X~ goes where the previous tile's y was staged: its stores must have read it
         if (warp == 0) bulk_wait_read();
         epi_sync();
       }
       if (!dead) commit_px<R>(raw_x, sX, sXw, ts.sw);
-      fence_async_smem();
-      tc_fence_before();
-      epi_signal(BAR_OPS, kEpiThreads + 64, dead);
       if (!dead && k + 1 < k_hi) issue_px<R>(raw_x, p.x, tok0 + (size_t)LT * Hs, Hs, T, t0 + LT);
       // ---- 2. band, decays ---------------------------------------------------------------------
       if (!dead) dead = !warp_all(mbar_wait(&bars[0], g & 1, wait_limit));
