@@ -272,6 +272,22 @@ pub struct m3_gate_desc {
     pub z: *const c_void,
 }
 
+/// out = rms_norm(y) * weight * silu(z): the gate behind SsmConfig::post_gate_norm
+/// (src/models/mamba3.rs:475-484, src/nn/norm.rs:95-105).
+#[repr(C)]
+#[derive(Clone, Copy)]
+pub struct m3_gate_norm_desc {
+    pub batch: i32,
+    pub seq: i32,
+    pub channels: i32,
+    pub dtype: i32,
+    pub z_stride: i64,
+    pub y: *const c_void,
+    pub z: *const c_void,
+    pub weight: *const f32,
+    pub eps: f32,
+}
+
 extern "C" {
     pub fn m3_version() -> *const c_char;
 
@@ -329,4 +345,7 @@ extern "C" {
     pub fn m3_gate_forward(ctx: *mut m3_ctx, desc: *const m3_gate_desc, out: *mut c_void) -> c_int;
     pub fn m3_gate_backward(ctx: *mut m3_ctx, desc: *const m3_gate_desc, dout: *const c_void, dy: *mut c_void,
                             dz: *mut c_void) -> c_int;
+    pub fn m3_gate_norm_forward(ctx: *mut m3_ctx, desc: *const m3_gate_norm_desc, out: *mut c_void) -> c_int;
+    pub fn m3_gate_norm_backward(ctx: *mut m3_ctx, desc: *const m3_gate_norm_desc, dout: *const c_void, dy: *mut c_void,
+                                 dz: *mut c_void, dweight: *mut f32) -> c_int;
 }

@@ -357,6 +357,24 @@ typedef struct {
 int m3_gate_forward(m3_ctx *ctx, const m3_gate_desc *desc, void *out);
 int m3_gate_backward(m3_ctx *ctx, const m3_gate_desc *desc, const void *dout, void *dy, void *dz);
 
+/* The same gate behind the optional post-gate norm (SsmConfig::post_gate_norm, src/ssm/config.rs:113;
+ * Mamba3Mixer::finish, src/models/mamba3.rs:475-484; RmsNorm::apply, src/nn/norm.rs:95-105):
+ * out = y * rsqrt(mean over channels of y^2 + eps) * weight * silu(z), one launch.  weight is the norm's
+ * gain [channels] in float32, or NULL for a norm without gain.  The backward pass returns dy, dz (either may
+ * be NULL) and, when both weight and dweight are given, dweight [channels] (zeroed for seq == 0), summed over
+ * the rows in a fixed order.  channels is at most 8192 (M3_ERR_UNSUPPORTED beyond). */
+typedef struct {
+  int32_t batch, seq, channels;
+  int32_t dtype;
+  int64_t z_stride;
+  const void *y, *z;
+  const float *weight;
+  float eps;
+} m3_gate_norm_desc;
+int m3_gate_norm_forward(m3_ctx *ctx, const m3_gate_norm_desc *desc, void *out);
+int m3_gate_norm_backward(m3_ctx *ctx, const m3_gate_norm_desc *desc, const void *dout, void *dy, void *dz,
+                          float *dweight);
+
 /* Bytes of device scratch a forward with this descriptor allocates (kept until
  * m3_saved_free when `saved` is requested). */
 size_t m3_scan_scratch_bytes(const m3_scan_desc *desc, int for_backward);

@@ -79,6 +79,11 @@ class GateDesc(C.Structure):
         (n, C.c_void_p) for n in ("y", "z")]
 
 
+class GateNormDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("batch", "seq", "channels", "dtype")] + [("z_stride", C.c_int64)] + [
+        (n, C.c_void_p) for n in ("y", "z", "weight")] + [("eps", C.c_float)]
+
+
 class HostIn(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("x", "b", "c", "dt", "lambda_", "theta", "dy")]
 
@@ -116,6 +121,8 @@ SYMBOLS = {
     "m3_dt_lambda_backward": (C.c_int, [C.c_void_p, C.POINTER(ActDesc)] + [C.c_void_p] * 5),
     "m3_gate_forward": (C.c_int, [C.c_void_p, C.POINTER(GateDesc), C.c_void_p]),
     "m3_gate_backward": (C.c_int, [C.c_void_p, C.POINTER(GateDesc), C.c_void_p, C.c_void_p, C.c_void_p]),
+    "m3_gate_norm_forward": (C.c_int, [C.c_void_p, C.POINTER(GateNormDesc), C.c_void_p]),
+    "m3_gate_norm_backward": (C.c_int, [C.c_void_p, C.POINTER(GateNormDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "m3_host_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "m3_host_free": (C.c_int, [C.c_void_p]),
     "m3_host_pipe_create": (C.c_int, [C.c_void_p, C.POINTER(ScanDesc), C.c_int, C.POINTER(C.c_void_p)]),

@@ -4,6 +4,7 @@
 //                  permute to the scan's rank-last layout (:409-436)
 //   m3_dt_lambda_* dt = softplus(dt_raw + dt_bias), lambda = sigmoid(lambda_raw) (:440-446)
 //   m3_gate_*      y * silu(z) (:475-484, without post_gate_norm)
+//   m3_gate_norm_* rms_norm(y) * gain * silu(z) (:475-484 with post_gate_norm; src/nn/norm.rs:95-105)
 // All are HBM-bound streaming kernels; inputs may be column bands of a wider row (the input
 // projection / the convolution's output), outputs of the forward are dense.
 #include <cuda_bf16.h>
@@ -467,6 +468,95 @@ int bc_dims(m3_ctx* ctx, const m3_bc_desc* s, BcDims* d) {
   return M3_OK;
 }
 
+// ---- the gate behind a post-gate RMS norm: out = y * rsqrt(mean_c y^2 + eps) * gain * silu(z) -------
+// One block per token row, rows grid-strided; thread t owns channels t, t + kGnThreads, ... (coalesced),
+// so a block's per-channel sums for d gain stay in registers over all of its rows.
+constexpr int kGnThreads = 256, kGnMaxPer = 32;  // channels <= kGnThreads * kGnMaxPer
+
+__device__ __forceinline__ float gn_block_sum(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();  // the previous sum's readers are done with red
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kGnThreads / 32; ++i) t += red[i];  // the same order in every thread
+  return t;
+}
+
+template <class T>
+__global__ void __launch_bounds__(kGnThreads)
+k_gate_norm_fwd(size_t ntok, int Cn, long long zs, float eps, const T* __restrict__ y, const T* __restrict__ z,
+                const float* __restrict__ gain, T* __restrict__ out) {
+  __shared__ float red[kGnThreads / 32];
+  for (size_t bt = blockIdx.x; bt < ntok; bt += gridDim.x) {
+    float v[kGnMaxPer];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kGnMaxPer; ++j) {
+      const int c = threadIdx.x + j * kGnThreads;
+      v[j] = c < Cn ? ldf(y, bt * Cn + c) : 0.0f;
+      ss += v[j] * v[j];
+    }
+    const float r = rsqrtf(gn_block_sum(ss, red) / (float)Cn + eps);
+#pragma unroll
+    for (int j = 0; j < kGnMaxPer; ++j) {
+      const int c = threadIdx.x + j * kGnThreads;
+      if (c < Cn) stf(out, bt * Cn + c, v[j] * r * (gain ? gain[c] : 1.0f) * silu(ldf(z, bt * zs + c)));
+    }
+  }
+}
+
+// With n = y r gain and u = gain * dout * silu(z):  dy = r u - y r^3 mean_c(u y),  dz = dout n silu'(z),
+// d gain[c] = sum over rows of dout silu(z) y r  (per-block partial sums, added in a fixed order afterwards).
+template <class T>
+__global__ void __launch_bounds__(kGnThreads)
+k_gate_norm_bwd(size_t ntok, int Cn, long long zs, float eps, const T* __restrict__ y, const T* __restrict__ z,
+                const float* __restrict__ gain, const T* __restrict__ dout, T* __restrict__ dy, T* __restrict__ dz,
+                float* __restrict__ part) {
+  __shared__ float red[kGnThreads / 32];
+  float accg[kGnMaxPer];
+#pragma unroll
+  for (int j = 0; j < kGnMaxPer; ++j) accg[j] = 0.0f;
+  for (size_t bt = blockIdx.x; bt < ntok; bt += gridDim.x) {
+    float yv[kGnMaxPer], dn[kGnMaxPer], w[kGnMaxPer];
+    float ss = 0.0f, dot = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kGnMaxPer; ++j) {
+      const int c = threadIdx.x + j * kGnThreads;
+      yv[j] = dn[j] = w[j] = 0.0f;
+      if (c < Cn) {
+        const float g = gain ? gain[c] : 1.0f;
+        const float zv = ldf(z, bt * zs + c), gv = ldf(dout, bt * Cn + c);
+        yv[j] = ldf(y, bt * Cn + c);
+        dn[j] = gv * silu(zv);
+        w[j] = gv * silu_grad(zv) * g;
+        ss += yv[j] * yv[j];
+        dot += dn[j] * g * yv[j];
+      }
+    }
+    const float r = rsqrtf(gn_block_sum(ss, red) / (float)Cn + eps);
+    const float md = gn_block_sum(dot, red) / (float)Cn;
+#pragma unroll
+    for (int j = 0; j < kGnMaxPer; ++j) {
+      const int c = threadIdx.x + j * kGnThreads;
+      if (c < Cn) {
+        const float g = gain ? gain[c] : 1.0f;
+        if (dy) stf(dy, bt * Cn + c, r * (dn[j] * g - yv[j] * r * r * md));
+        if (dz) stf(dz, bt * zs + c, w[j] * yv[j] * r);
+        accg[j] += dn[j] * yv[j] * r;
+      }
+    }
+  }
+  if (part) {
+#pragma unroll
+    for (int j = 0; j < kGnMaxPer; ++j) {
+      const int c = threadIdx.x + j * kGnThreads;
+      if (c < Cn) part[(size_t)blockIdx.x * Cn + c] = accg[j];
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -712,6 +802,78 @@ int m3_gate_backward(m3_ctx* ctx, const m3_gate_desc* s, const void* dout, void*
   }
   M3_CUDA(ctx, cudaGetLastError());
   ctx->launches += 1;
+  return M3_OK;
+}
+
+static int gate_norm_check(m3_ctx* ctx, const m3_gate_norm_desc* s) {
+  if (!ctx || !s) return M3_ERR_NULL;
+  if (s->batch <= 0 || s->seq < 0 || s->channels <= 0) return m3::fail(ctx, M3_ERR_SHAPE, "gate: extents must be positive");
+  if (s->channels > kGnThreads * kGnMaxPer)
+    return m3::fail(ctx, M3_ERR_UNSUPPORTED, "post-gate norm over %d channels (at most %d)", s->channels, kGnThreads * kGnMaxPer);
+  if (s->dtype != M3_F32 && s->dtype != M3_BF16) return m3::fail(ctx, M3_ERR_UNSUPPORTED, "dtype %d", s->dtype);
+  if (!s->y || !s->z) return m3::fail(ctx, M3_ERR_NULL, "y and z are required");
+  if (s->z_stride && s->z_stride < s->channels) return m3::fail(ctx, M3_ERR_SHAPE, "z_stride below the channel count");
+  if (!(s->eps >= 0.0f)) return m3::fail(ctx, M3_ERR_CONFIG, "eps must not be negative");
+  return M3_OK;
+}
+
+int m3_gate_norm_forward(m3_ctx* ctx, const m3_gate_norm_desc* s, void* out) {
+  const int rc = gate_norm_check(ctx, s);
+  if (rc != M3_OK) return rc;
+  if (!out) return m3::fail(ctx, M3_ERR_NULL, "out is required");
+  if (s->seq == 0) return M3_OK;
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  const size_t ntok = (size_t)s->batch * s->seq;
+  const long long zs = s->z_stride ? s->z_stride : s->channels;
+  const unsigned grid = (unsigned)(ntok < 148u * 8u ? ntok : 148u * 8u);
+  if (s->dtype == M3_BF16) {
+    using T = __nv_bfloat16;
+    k_gate_norm_fwd<T><<<grid, kGnThreads, 0, ctx->stream>>>(ntok, s->channels, zs, s->eps, static_cast<const T*>(s->y),
+                                                              static_cast<const T*>(s->z), s->weight, static_cast<T*>(out));
+  } else {
+    k_gate_norm_fwd<float><<<grid, kGnThreads, 0, ctx->stream>>>(ntok, s->channels, zs, s->eps, static_cast<const float*>(s->y),
+                                                                  static_cast<const float*>(s->z), s->weight, static_cast<float*>(out));
+  }
+  M3_CUDA(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return M3_OK;
+}
+
+int m3_gate_norm_backward(m3_ctx* ctx, const m3_gate_norm_desc* s, const void* dout, void* dy, void* dz, float* dweight) {
+  const int rc = gate_norm_check(ctx, s);
+  if (rc != M3_OK) return rc;
+  if (!dout) return m3::fail(ctx, M3_ERR_NULL, "dout is required");
+  M3_CUDA(ctx, cudaSetDevice(ctx->device));
+  const bool want_w = dweight && s->weight;
+  if (s->seq == 0) {
+    if (want_w) M3_CUDA(ctx, cudaMemsetAsync(dweight, 0, s->channels * sizeof(float), ctx->stream));
+    return M3_OK;
+  }
+  const size_t ntok = (size_t)s->batch * s->seq;
+  const long long zs = s->z_stride ? s->z_stride : s->channels;
+  const unsigned grid = (unsigned)(ntok < 148u * 4u ? ntok : 148u * 4u);
+  float* part = nullptr;
+  if (want_w) M3_CUDA(ctx, m3::scratch_alloc(ctx, reinterpret_cast<void**>(&part), (size_t)grid * s->channels * sizeof(float), ctx->stream));
+  if (s->dtype == M3_BF16) {
+    using T = __nv_bfloat16;
+    k_gate_norm_bwd<T><<<grid, kGnThreads, 0, ctx->stream>>>(ntok, s->channels, zs, s->eps, static_cast<const T*>(s->y),
+                                                              static_cast<const T*>(s->z), s->weight, static_cast<const T*>(dout),
+                                                              static_cast<T*>(dy), static_cast<T*>(dz), part);
+  } else {
+    k_gate_norm_bwd<float><<<grid, kGnThreads, 0, ctx->stream>>>(ntok, s->channels, zs, s->eps, static_cast<const float*>(s->y),
+                                                                  static_cast<const float*>(s->z), s->weight,
+                                                                  static_cast<const float*>(dout), static_cast<float*>(dy),
+                                                                  static_cast<float*>(dz), part);
+  }
+  cudaError_t e = cudaGetLastError();
+  ctx->launches += 1;
+  if (e == cudaSuccess && want_w) {
+    e = m3::column_sums(ctx->stream, part, (int)grid, s->channels, s->channels, dweight);
+    ctx->launches += 1;
+  }
+  cudaError_t e2 = part ? cudaFreeAsync(part, ctx->stream) : cudaSuccess;
+  if (e != cudaSuccess) return m3::cuda_fail(ctx, e, "gate + norm backward");
+  if (e2 != cudaSuccess) return m3::cuda_fail(ctx, e2, "cudaFreeAsync");
   return M3_OK;
 }
 

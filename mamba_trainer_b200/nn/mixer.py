@@ -1,12 +1,12 @@
 """The stretch of the Mamba-3 mixer between its input and output projections, as seven launches.
 
 Mirrors Mamba3Mixer::project + mamba3_scan + finish of the reference (src/models/mamba3.rs:340-461,
-:475-484, :540-556; one direction or bidirectional, no post_gate_norm): the projection's output
+:475-484, :540-556; one direction or bidirectional, with or without post_gate_norm): the projection's output
 [batch, seq, width] is cut into z | x B C | dt | lambda | theta WITHOUT copies (the kernels read
 column bands of it and the backward pass writes the bands of one gradient buffer), then
 
     convolution + SiLU over x|B|C  ->  B/C bias + RMS norm + layout  ->  softplus / sigmoid
-    ->  scan  ->  y * silu(z)
+    ->  scan  ->  y * silu(z)        (rms_norm(y) * gain * silu(z) with post_gate_norm)
 
 Every step runs in libm3scan; the node's backward calls the matching adjoints in reverse order.
 """
@@ -79,7 +79,7 @@ class MixerCache:
 
 class _MixerCore(torch.autograd.Function):
     @staticmethod
-    def forward(fctx, o, proj, conv_w, conv_b, dt_bias, a_log, d_skip, b_bias, c_bias, norm_w):
+    def forward(fctx, o, proj, conv_w, conv_b, dt_bias, a_log, d_skip, b_bias, c_bias, norm_w, post_w):
         s: MixerShape = o["shape"]
         ctx = Context.for_device(proj.device)
         lib, hd = ctx.lib, ctx.handle
@@ -131,13 +131,18 @@ class _MixerCore(torch.autograd.Function):
         ctx.check(lib.m3_scan_forward(hd, C.byref(sdesc), C.byref(sout), C.byref(saved) if track else None))
         # 5. gate
         out = new(B, T, di)
-        gdesc = _ffi.GateDesc(batch=B, seq=T, channels=di, dtype=dt_code, z_stride=W, y=_p(y), z=_p(proj))
-        ctx.check(lib.m3_gate_forward(hd, C.byref(gdesc), _p(out)))
+        if o["post_norm"]:
+            gdesc = _ffi.GateNormDesc(batch=B, seq=T, channels=di, dtype=dt_code, z_stride=W, y=_p(y), z=_p(proj),
+                                      weight=_p(post_w), eps=float(o["eps"]))
+            ctx.check(lib.m3_gate_norm_forward(hd, C.byref(gdesc), _p(out)))
+        else:
+            gdesc = _ffi.GateDesc(batch=B, seq=T, channels=di, dtype=dt_code, z_stride=W, y=_p(y), z=_p(proj))
+            ctx.check(lib.m3_gate_forward(hd, C.byref(gdesc), _p(out)))
         if track:
             fctx.o, fctx.m3 = o, ctx
             fctx.saved = _Saved(ctx, saved)
             fctx.descs = (cdesc, bdesc, adesc, sdesc, gdesc)
-            fctx.keep = (proj, conv_w, conv_b, dt_bias, a_log, d_skip, b_bias, c_bias, norm_w, x, bcr, b, c, dt, lam, theta, y)
+            fctx.keep = (proj, conv_w, conv_b, dt_bias, a_log, d_skip, b_bias, c_bias, norm_w, x, bcr, b, c, dt, lam, theta, y, post_w)
         return out
 
     @staticmethod
@@ -147,7 +152,7 @@ class _MixerCore(torch.autograd.Function):
         lib, hd = ctx.lib, ctx.handle
         ctx.bind_current_stream()
         cdesc, bdesc, adesc, sdesc, gdesc = fctx.descs
-        proj, conv_w, conv_b, dt_bias, a_log, d_skip, b_bias, c_bias, norm_w, x, bcr, b, c, dt, lam, theta, y = fctx.keep
+        proj, conv_w, conv_b, dt_bias, a_log, d_skip, b_bias, c_bias, norm_w, x, bcr, b, c, dt, lam, theta, y, post_w = fctx.keep
         B, T, W = proj.shape
         H, P, N, R = s.heads, s.head_dim, s.d_state, s.rank
         di, bc = s.d_inner, s.bc_width
@@ -160,7 +165,12 @@ class _MixerCore(torch.autograd.Function):
         dout = dout.contiguous()
         # 5'. gate: dy (dense) and dz (band 0 of dproj)
         dy = new(B, T, H, P, R)
-        ctx.check(lib.m3_gate_backward(hd, C.byref(gdesc), _p(dout), _p(dy), _p(dproj)))
+        dpost = None
+        if o["post_norm"]:
+            dpost = f32(di) if post_w is not None else None
+            ctx.check(lib.m3_gate_norm_backward(hd, C.byref(gdesc), _p(dout), _p(dy), _p(dproj), _p(dpost)))
+        else:
+            ctx.check(lib.m3_gate_backward(hd, C.byref(gdesc), _p(dout), _p(dy), _p(dproj)))
         # 4'. scan
         dx, db, dc, ddt = new(B, T, H, P, R), new(B, T, H, N, R), new(B, T, H, N, R), new(B, T, H)
         dlam = new(B, T, H) if s.learned_lambda else None
@@ -193,7 +203,7 @@ class _MixerCore(torch.autograd.Function):
         dconv_b = f32(di + 2 * bc) if conv_b is not None else None
         cdesc.dy2 = _p(dbcr)
         ctx.check(lib.m3_conv_backward(hd, C.byref(cdesc), _p(dx), _p(dproj, off_x), _p(dconv_w), _p(dconv_b), None))
-        return (None, dproj, dconv_w, dconv_b, ddt_bias, da_log, dd_skip, db_bias, dc_bias, dnorm)
+        return (None, dproj, dconv_w, dconv_b, ddt_bias, da_log, dd_skip, db_bias, dc_bias, dnorm, dpost)
 
 
 class MixerCore(torch.nn.Module):
@@ -203,7 +213,7 @@ class MixerCore(torch.nn.Module):
     def __init__(self, shape: MixerShape, conv_kernel: int = 4, chunk: int = 64, conv_bias: bool = True,
                  bc_bias: bool = True, bc_norm: bool = True, norm_gain: bool = True, d_skip: bool = True,
                  eps: float = 1e-5, discretization: Optional[Discretization] = None, bidirectional: bool = False,
-                 device=None):
+                 post_gate_norm: bool = False, device=None):
         super().__init__()
         if shape.heads % shape.n_groups:
             raise ConfigError(f"heads {shape.heads} not a multiple of groups {shape.n_groups}")
@@ -211,6 +221,9 @@ class MixerCore(torch.nn.Module):
             raise ConfigError("rotational dynamics require an even d_state")
         if bidirectional and (shape.heads % 2 or shape.n_groups % 2):
             raise ConfigError("a bidirectional mixer needs even heads and groups")      # mamba3.rs:107-108
+        if bidirectional and post_gate_norm:                                            # mamba3.rs:175-179
+            raise ConfigError("post_gate_norm would normalise across both directions at once; use bc_norm with a "
+                              "bidirectional mixer")
         self.shape, self.chunk, self.eps, self.use_norm = shape, chunk, eps, bc_norm
         self.bidirectional = bidirectional
         self.disc = Discretization(discretization) if discretization is not None else (
@@ -227,6 +240,9 @@ class MixerCore(torch.nn.Module):
         self.b_bias = par(torch.zeros(H, N)) if bc_bias else None
         self.c_bias = par(torch.zeros(H, N)) if bc_bias else None
         self.norm_w = par(torch.ones(N)) if (bc_norm and norm_gain) else None
+        # RmsNormConfig::new(d_inner) (mamba3.rs:245-247): a gain of ones over the scan's flattened output
+        self.post_gate_norm = post_gate_norm
+        self.post_norm_w = par(torch.ones(shape.d_inner)) if post_gate_norm else None
 
     def empty_cache(self, batch: int, device, dtype=torch.float32) -> MixerCache:
         s = self.shape
@@ -292,8 +308,14 @@ class MixerCore(torch.nn.Module):
             y, ssm = res.y, res.state
         y = y.contiguous()
         out = new(B, T, di)
-        gdesc = _ffi.GateDesc(batch=B, seq=T, channels=di, dtype=code, z_stride=W, y=_p(y), z=_p(proj))
-        ctx.check(lib.m3_gate_forward(hd, C.byref(gdesc), _p(out)))
+        if self.post_gate_norm:
+            post_w = f(self.post_norm_w)
+            gdesc = _ffi.GateNormDesc(batch=B, seq=T, channels=di, dtype=code, z_stride=W, y=_p(y), z=_p(proj),
+                                      weight=_p(post_w), eps=float(self.eps))
+            ctx.check(lib.m3_gate_norm_forward(hd, C.byref(gdesc), _p(out)))
+        else:
+            gdesc = _ffi.GateDesc(batch=B, seq=T, channels=di, dtype=code, z_stride=W, y=_p(y), z=_p(proj))
+            ctx.check(lib.m3_gate_forward(hd, C.byref(gdesc), _p(out)))
         return out, MixerCache(new_hist, ssm)
 
     def forward(self, proj: torch.Tensor, path: int = _ffi.PATH_AUTO) -> torch.Tensor:
@@ -310,7 +332,8 @@ class MixerCore(torch.nn.Module):
         if proj.shape[1] == 0:                      # nothing to scan (scan.rs:134-144)
             return proj.new_zeros((proj.shape[0], 0, s.d_inner)) + 0.0 * proj.sum()
         o = {"shape": s, "chunk": self.chunk, "eps": self.eps, "norm": self.use_norm, "disc": int(self.disc),
-             "path": path, "reverse_heads": s.heads // 2 if self.bidirectional else 0}
+             "path": path, "reverse_heads": s.heads // 2 if self.bidirectional else 0,
+             "post_norm": self.post_gate_norm}
         f = lambda t: None if t is None else t.to(torch.float32).contiguous()
         return _MixerCore.apply(o, proj.contiguous(), f(self.conv_w), f(self.conv_b), f(self.dt_bias), f(self.a_log),
-                                f(self.d_skip), f(self.b_bias), f(self.c_bias), f(self.norm_w))
+                                f(self.d_skip), f(self.b_bias), f(self.c_bias), f(self.norm_w), f(self.post_norm_w))

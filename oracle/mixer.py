@@ -58,15 +58,18 @@ class _Narrow(torch.autograd.Function):
 def mixer_core(proj, p: dict, heads: int, head_dim: int, d_state: int, rank: int = 1, groups: Optional[int] = None,
                chunk: int = 64, learned_lambda: bool = True, rotational: bool = True, eps: float = 1e-5,
                conv_history=None, state=None, want_state: bool = False, fixed_lambda: float = 1.0,
-               bidirectional: bool = False, scan_io_dtype=None):
+               bidirectional: bool = False, scan_io_dtype=None, post_gate_norm: bool = False):
     """Everything Mamba3Mixer does between its input and output projections
-    (src/models/mamba3.rs:340-461, :475-484, :540-556, no post_gate_norm, one direction):
+    (src/models/mamba3.rs:340-461, :475-484, :540-556):
     split the projection into z | x B C | dt | lambda | theta, convolve x|B|C and apply SiLU, expand
     B / C groups to heads, add the per-head biases, RMS-normalise, move the rank axis last, softplus /
     sigmoid, scan, gate with SiLU(z).
 
     p: conv_w [K, d_inner + 2 bc], conv_b [same] or None, dt_bias [H], a_log [H], d_skip [H] or None,
-    b_bias / c_bias [H, N] or None, norm_w [N] or None ("norm" False in p disables the norm).
+    b_bias / c_bias [H, N] or None, norm_w [N] or None ("norm" False in p disables the norm);
+    post_gate_norm: the scan's flattened output is RMS-normalised over d_inner, gain post_norm_w [d_inner] or
+    None, before the gate (:478-482; the reference's port in bench/torch_mamba3.py has no such switch, so this
+    branch is pinned only through rms_norm, which the B/C norm of the golden mixer vectors exercises).
     scan_io_dtype (e.g. torch.bfloat16): the scan's per-token inputs and its output pass through that
     type (rounded values, identity gradient, gradients rounded likewise) - the benchmark's "bf16 inputs"
     applied inside the mixer, where the CUDA path hands bf16 tensors from kernel to kernel.
@@ -115,5 +118,7 @@ def mixer_core(proj, p: dict, heads: int, head_dim: int, d_state: int, rank: int
     y = y.reshape(B, T, d_inner)
     if bidirectional:                                               # :548-556: the backward heads' output back
         y = torch.cat([y[..., :d_inner // 2], y[..., d_inner // 2:].flip(1)], dim=-1)
+    if post_gate_norm:
+        y = rms_norm(y, p.get("post_norm_w"), eps)
     gated = y * F.silu(z)                                           # :475-484
     return gated, hist, st

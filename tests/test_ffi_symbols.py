@@ -36,7 +36,8 @@ def test_struct_layouts_match_the_header(tmp_path):
              ("m3_step_desc", _ffi.StepDesc, {"lambda": "lambda_"}), ("m3_step_out", _ffi.StepOut, {}),
              ("m3_host_in", _ffi.HostIn, {"lambda": "lambda_"}), ("m3_host_out", _ffi.HostOut, {}),
              ("m3_conv_desc", _ffi.ConvDesc, {}), ("m3_bc_desc", _ffi.BcDesc, {}),
-             ("m3_act_desc", _ffi.ActDesc, {}), ("m3_gate_desc", _ffi.GateDesc, {})]
+             ("m3_act_desc", _ffi.ActDesc, {}), ("m3_gate_desc", _ffi.GateDesc, {}),
+             ("m3_gate_norm_desc", _ffi.GateNormDesc, {})]
     inv = lambda ren: {v: k for k, v in ren.items()}
     lines = ["#include <stdio.h>", "#include <stddef.h>", f'#include "{ROOT / "include" / "m3scan.h"}"', "int main(void) {"]
     for cname, mirror, ren in pairs:

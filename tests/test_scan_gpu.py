@@ -901,6 +901,97 @@ def test_mixer_core_bidirectional_matches_the_oracle(dtype, rank):
             check("d" + n, a_, e_)
 
 
+@pytest.mark.parametrize("dtype,rank,channels_odd", [(torch.float32, 1, False), (torch.float32, 2, True), (torch.bfloat16, 2, False)])
+def test_mixer_core_post_gate_norm_matches_the_oracle(dtype, rank, channels_odd):
+    """SsmConfig::post_gate_norm (src/ssm/config.rs:113; Mamba3Mixer::finish, src/models/mamba3.rs:475-484): the
+    scan's flattened output is RMS-normalised over d_inner, with a gain, before the gate.  Values, the
+    projection's gradient band by band and every parameter gradient, the gain's included."""
+    from mamba_trainer_b200.nn import MixerCore, MixerShape
+    from mamba_trainer_b200.error import ConfigError
+    from oracle.mixer import mixer_core as oracle_core
+    small = dtype == torch.float32
+    H, P, N = ((3, 5, 6) if channels_odd else (2, 4, 6)) if small else (2, 64, 128)
+    B, T = (2, 21) if small else (4, 300)
+    shape = MixerShape(H, P, N, rank)
+    torch.manual_seed(17 + rank)
+    core = MixerCore(shape, chunk=8 if small else 64, post_gate_norm=True, device="cuda")
+    g = torch.Generator().manual_seed(23)
+    r = lambda *s: torch.randn(*s, generator=g)
+    p = {"conv_w": r(4, shape.conv_channels) * 0.4, "conv_b": r(shape.conv_channels) * 0.2, "dt_bias": r(H) * 0.3 - 2.0,
+         "a_log": torch.rand(H, generator=g), "d_skip": r(H), "b_bias": r(H, N) * 0.3, "c_bias": r(H, N) * 0.3,
+         "norm_w": 1.0 + r(N) * 0.2, "post_norm_w": 1.0 + r(shape.d_inner) * 0.3}
+    _core_params(core, p)
+    proj = r(B, T, shape.in_proj_width).to(dtype)
+    dgated = r(B, T, shape.d_inner).to(dtype)
+    pd = proj.cuda().requires_grad_(True)
+    out = core(pd)
+    names = list(p)
+    grads = torch.autograd.grad(out, [pd] + [getattr(core, n) for n in names], grad_outputs=dgated.cuda())
+    pc = proj.double().requires_grad_(True)
+    pt = {n: v.double().requires_grad_(True) for n, v in p.items()}
+    eo, _, _ = oracle_core(pc, pt, H, P, N, rank, None, 8 if small else 64, True, True, post_gate_norm=True)
+    eg = torch.autograd.grad(eo, [pc] + [pt[n] for n in names], grad_outputs=dgated.double())
+    check = check_f32 if small else check_bf16
+    check("gated", out, eo.detach())
+    di, bc = shape.d_inner, shape.bc_width
+    for name, (lo, hi) in {"z": (0, di), "x": (di, 2 * di), "B": (2 * di, 2 * di + bc), "C": (2 * di + bc, 2 * di + 2 * bc),
+                           "dt": (2 * di + 2 * bc, 2 * di + 2 * bc + H)}.items():
+        check("dproj." + name, grads[0][..., lo:hi], eg[0][..., lo:hi])
+    for n, a_, e_ in zip(names, grads[1:], eg[1:]):
+        if small or n not in ("a_log", "dt_bias"):
+            check("d" + n, a_, e_)
+    # decode == parallel with the norm in place, and the reference's refusal for a bidirectional mixer
+    with torch.no_grad():
+        whole = core(proj.cuda())
+        o1, cache = core.forward_cached(proj[:, :T - 1].cuda())
+        o2, _ = core.forward_cached(proj[:, T - 1:].cuda(), cache)
+    assert ref_metric(torch.cat([o1, o2], 1).float(), whole.float()) <= (2e-3 if small else 3e-2)
+    with pytest.raises(ConfigError):
+        MixerCore(MixerShape(2, 4, 6), bidirectional=True, post_gate_norm=True, device="cuda")
+
+
+def test_gate_norm_c_abi_edges():
+    """m3_gate_norm_*: z as a band of a wider row, a norm without gain, outputs that are not wanted, and
+    the channel limit."""
+    import ctypes as C
+    from mamba_trainer_b200 import _ffi
+    from mamba_trainer_b200.ssm.scan import Context
+    from mamba_trainer_b200.error import UnsupportedError
+    ctx = Context.for_device(torch.device("cuda"))
+    lib, hd = ctx.lib, ctx.handle
+    torch.manual_seed(2)
+    B, T, Cn, W = 3, 37, 1000, 1300
+    y = torch.randn(B, T, Cn, device="cuda")
+    wide = torch.randn(B, T, W, device="cuda")
+    dout = torch.randn(B, T, Cn, device="cuda")
+    ptr = lambda t, off=0: C.c_void_p(t.data_ptr() + off * t.element_size()) if t is not None else None
+    for gain in (None, 1.0 + 0.3 * torch.randn(Cn, device="cuda")):
+        d = _ffi.GateNormDesc(batch=B, seq=T, channels=Cn, dtype=0, z_stride=W, y=ptr(y), z=ptr(wide, 100), weight=ptr(gain), eps=1e-5)
+        out, dy, dwide = torch.empty_like(y), torch.empty_like(y), torch.zeros_like(wide)
+        dw = torch.full((Cn,), 7.0, device="cuda")
+        ctx.check(lib.m3_gate_norm_forward(hd, C.byref(d), ptr(out)))
+        ctx.check(lib.m3_gate_norm_backward(hd, C.byref(d), ptr(dout), ptr(dy), ptr(dwide, 100), ptr(dw)))
+        yd = y.double().requires_grad_(True)
+        zd = wide[..., 100:100 + Cn].double().requires_grad_(True)
+        gd = gain.double().requires_grad_(True) if gain is not None else None
+        n = yd * torch.rsqrt(yd.pow(2).mean(-1, keepdim=True) + 1e-5)
+        e = (n * gd if gd is not None else n) * torch.nn.functional.silu(zd)
+        eg = torch.autograd.grad(e, [yd, zd] + ([gd] if gd is not None else []), grad_outputs=dout.double())
+        check_f32("out", out, e.detach())
+        check_f32("dy", dy, eg[0])
+        check_f32("dz", dwide[..., 100:100 + Cn], eg[1])
+        assert float(dwide[..., :100].abs().max()) == 0.0 and float(dwide[..., 100 + Cn:].abs().max()) == 0.0
+        if gain is not None:
+            check_f32("dweight", dw, eg[2])
+            ctx.check(lib.m3_gate_norm_backward(hd, C.byref(d), ptr(dout), None, None, ptr(dw)))   # d gain alone
+            check_f32("dweight alone", dw, eg[2])
+        else:
+            assert float((dw - 7.0).abs().max()) == 0.0      # no gain, nothing written
+    big = _ffi.GateNormDesc(batch=1, seq=1, channels=8193, dtype=0, z_stride=0, y=ptr(y), z=ptr(y), weight=None, eps=1e-5)
+    with pytest.raises(UnsupportedError):
+        ctx.check(lib.m3_gate_norm_forward(hd, C.byref(big), ptr(y)))
+
+
 def test_mixer_core_degenerate_lengths():
     """A single position and an empty window through the training path."""
     from mamba_trainer_b200.nn import MixerCore, MixerShape
