@@ -10,6 +10,7 @@
 #include <cuda_bf16.h>
 
 #include <initializer_list>
+#include <type_traits>
 
 #include "m3_internal.h"
 
@@ -557,6 +558,168 @@ k_gate_norm_bwd(size_t ntok, int Cn, long long zs, float eps, const T* __restric
   }
 }
 
+// Vector form of the two kernels above (16-byte accesses, rows and strides aligned): a row belongs to a
+// group of GS threads - a warp (eight rows per block, sums by shuffles, no block barrier) while a row has at
+// most 32 * kGnVec vectors, else the whole block - and thread gl of the group owns vectors gl, gl + GS, ...
+// of every row it meets, raw in registers between the two passes over the row.
+constexpr int kGnVec = 8;  // vectors per thread, at most (the kernels are built for 1, 2, 4 and 8)
+
+template <int GS>
+__device__ __forceinline__ float gn_group_sum(float v, float* red) {
+  if (GS == 32) return warp_sum(v);
+  return gn_block_sum(v, red);
+}
+
+template <class T, int GS, int NV>
+__global__ void __launch_bounds__(kGnThreads)
+k_gate_norm_fwd_vec(size_t ntok, int Cn, long long zs, float eps, const T* __restrict__ y, const T* __restrict__ z,
+                    const float* __restrict__ gain, T* __restrict__ out) {
+  constexpr int V = (int)(16 / sizeof(T)), RPB = kGnThreads / GS;
+  __shared__ float red[kGnThreads / 32];
+  const int gl = threadIdx.x % GS, gr = threadIdx.x / GS, nvec = Cn / V;
+  for (size_t bt = (size_t)blockIdx.x * RPB + gr; bt < ntok; bt += (size_t)gridDim.x * RPB) {
+    uint4 qy[NV], qz[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = gl + j * GS;
+      if (v < nvec) {
+        qy[j] = __ldg(reinterpret_cast<const uint4*>(y + bt * Cn + (size_t)v * V));
+        qz[j] = __ldg(reinterpret_cast<const uint4*>(z + bt * zs + (size_t)v * V));
+      }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+      if (gl + j * GS < nvec) {
+        const T* py = reinterpret_cast<const T*>(&qy[j]);
+#pragma unroll
+        for (int k = 0; k < V; ++k) ss += ldf(py, k) * ldf(py, k);
+      }
+    const float r = rsqrtf(gn_group_sum<GS>(ss, red) / (float)Cn + eps);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = gl + j * GS;
+      if (v < nvec) {
+        const T* py = reinterpret_cast<const T*>(&qy[j]);
+        const T* pz = reinterpret_cast<const T*>(&qz[j]);
+        uint4 qo;
+        T* po = reinterpret_cast<T*>(&qo);
+#pragma unroll
+        for (int k = 0; k < V; ++k) stf(po, k, ldf(py, k) * r * (gain ? __ldg(gain + v * V + k) : 1.0f) * silu(ldf(pz, k)));
+        *reinterpret_cast<uint4*>(out + bt * Cn + (size_t)v * V) = qo;
+      }
+    }
+  }
+}
+
+template <class T, int GS, int NV>
+__global__ void __launch_bounds__(kGnThreads)
+k_gate_norm_bwd_vec(size_t ntok, int Cn, long long zs, float eps, const T* __restrict__ y, const T* __restrict__ z,
+                    const float* __restrict__ gain, const T* __restrict__ dout, T* __restrict__ dy, T* __restrict__ dz,
+                    float* __restrict__ part) {
+  constexpr int V = (int)(16 / sizeof(T)), RPB = kGnThreads / GS;
+  __shared__ float red[kGnThreads / 32];
+  extern __shared__ float s_acc[];  // [Cn] when GS == 32 and d gain is wanted: the block's eight rows' sums
+  const int gl = threadIdx.x % GS, gr = threadIdx.x / GS, nvec = Cn / V;
+  float accg[NV * V];
+#pragma unroll
+  for (int i = 0; i < NV * V; ++i) accg[i] = 0.0f;
+  for (size_t bt = (size_t)blockIdx.x * RPB + gr; bt < ntok; bt += (size_t)gridDim.x * RPB) {
+    uint4 qy[NV], qz[NV], qg[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = gl + j * GS;
+      if (v < nvec) {
+        qy[j] = __ldg(reinterpret_cast<const uint4*>(y + bt * Cn + (size_t)v * V));
+        qz[j] = __ldg(reinterpret_cast<const uint4*>(z + bt * zs + (size_t)v * V));
+        qg[j] = __ldg(reinterpret_cast<const uint4*>(dout + bt * Cn + (size_t)v * V));
+      }
+    }
+    float ss = 0.0f, dot = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = gl + j * GS;
+      if (v < nvec) {
+        const T* py = reinterpret_cast<const T*>(&qy[j]);
+        const T* pz = reinterpret_cast<const T*>(&qz[j]);
+        const T* pg = reinterpret_cast<const T*>(&qg[j]);
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          const float yv = ldf(py, k);
+          ss += yv * yv;
+          dot += ldf(pg, k) * silu(ldf(pz, k)) * (gain ? __ldg(gain + v * V + k) : 1.0f) * yv;
+        }
+      }
+    }
+    const float r = rsqrtf(gn_group_sum<GS>(ss, red) / (float)Cn + eps);
+    const float md = gn_group_sum<GS>(dot, red) / (float)Cn;
+    const float r2md = r * r * md;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = gl + j * GS;
+      if (v < nvec) {
+        const T* py = reinterpret_cast<const T*>(&qy[j]);
+        const T* pz = reinterpret_cast<const T*>(&qz[j]);
+        const T* pg = reinterpret_cast<const T*>(&qg[j]);
+        uint4 o1, o2;
+        T* p1 = reinterpret_cast<T*>(&o1);
+        T* p2 = reinterpret_cast<T*>(&o2);
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          const float g = gain ? __ldg(gain + v * V + k) : 1.0f;
+          const float yv = ldf(py, k), zv = ldf(pz, k), gv = ldf(pg, k);
+          const float sg = sigmoid(zv);
+          const float dn = gv * zv * sg;
+          stf(p1, k, r * (dn * g - yv * r2md));
+          stf(p2, k, gv * sg * (1.0f + zv * (1.0f - sg)) * g * yv * r);
+          accg[j * V + k] += dn * yv * r;
+        }
+        if (dy) *reinterpret_cast<uint4*>(dy + bt * Cn + (size_t)v * V) = o1;
+        if (dz) *reinterpret_cast<uint4*>(dz + bt * zs + (size_t)v * V) = o2;
+      }
+    }
+  }
+  if (part) {
+    if (GS == 32) {  // the eight warps' sums, added warp after warp: one order whatever the scheduling
+      for (int w = 0; w < RPB; ++w) {
+        if (gr == w) {
+#pragma unroll
+          for (int j = 0; j < NV; ++j) {
+            const int v = gl + j * GS;
+            if (v < nvec)
+#pragma unroll
+              for (int k = 0; k < V; ++k) s_acc[v * V + k] = (w ? s_acc[v * V + k] : 0.0f) + accg[j * V + k];
+          }
+        }
+        __syncthreads();
+      }
+      for (int c = threadIdx.x; c < Cn; c += kGnThreads) part[(size_t)blockIdx.x * Cn + c] = s_acc[c];
+    } else {
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int v = gl + j * GS;
+        if (v < nvec)
+#pragma unroll
+          for (int k = 0; k < V; ++k) part[(size_t)blockIdx.x * Cn + v * V + k] = accg[j * V + k];
+      }
+    }
+  }
+}
+
+// Calls f(integral_constant<GS>, integral_constant<NV>) with the smallest NV of 1, 2, 4, 8 that covers the row.
+template <class F>
+static void gate_norm_dispatch(int gs, int nvec, F&& f) {
+  const int per = (nvec + gs - 1) / gs;
+  auto with_gs = [&](auto G) {
+    if (per <= 1) f(G, std::integral_constant<int, 1>{});
+    else if (per <= 2) f(G, std::integral_constant<int, 2>{});
+    else if (per <= 4) f(G, std::integral_constant<int, 4>{});
+    else f(G, std::integral_constant<int, 8>{});
+  };
+  if (gs == 32) with_gs(std::integral_constant<int, 32>{});
+  else with_gs(std::integral_constant<int, 256>{});
+}
+
 }  // namespace
 
 extern "C" {
@@ -805,6 +968,17 @@ int m3_gate_backward(m3_ctx* ctx, const m3_gate_desc* s, const void* dout, void*
   return M3_OK;
 }
 
+// Threads per row of the vector kernels (32 or 256), or 0 for the element-wise kernels (rows that are not
+// whole 16-byte vectors, or a pointer off a 16-byte boundary).
+static int gate_norm_group(const m3_gate_norm_desc* s, long long zs, std::initializer_list<const void*> ptrs) {
+  const int V = s->dtype == M3_BF16 ? 8 : 4;
+  if (s->channels % V || zs % V) return 0;
+  for (const void* p : ptrs)
+    if (p && (reinterpret_cast<uintptr_t>(p) % 16)) return 0;
+  const int nvec = s->channels / V;
+  return nvec <= 32 * kGnVec ? 32 : (nvec <= kGnThreads * kGnVec ? 256 : 0);
+}
+
 static int gate_norm_check(m3_ctx* ctx, const m3_gate_norm_desc* s) {
   if (!ctx || !s) return M3_ERR_NULL;
   if (s->batch <= 0 || s->seq < 0 || s->channels <= 0) return m3::fail(ctx, M3_ERR_SHAPE, "gate: extents must be positive");
@@ -825,15 +999,21 @@ int m3_gate_norm_forward(m3_ctx* ctx, const m3_gate_norm_desc* s, void* out) {
   M3_CUDA(ctx, cudaSetDevice(ctx->device));
   const size_t ntok = (size_t)s->batch * s->seq;
   const long long zs = s->z_stride ? s->z_stride : s->channels;
-  const unsigned grid = (unsigned)(ntok < 148u * 8u ? ntok : 148u * 8u);
-  if (s->dtype == M3_BF16) {
-    using T = __nv_bfloat16;
-    k_gate_norm_fwd<T><<<grid, kGnThreads, 0, ctx->stream>>>(ntok, s->channels, zs, s->eps, static_cast<const T*>(s->y),
-                                                              static_cast<const T*>(s->z), s->weight, static_cast<T*>(out));
-  } else {
-    k_gate_norm_fwd<float><<<grid, kGnThreads, 0, ctx->stream>>>(ntok, s->channels, zs, s->eps, static_cast<const float*>(s->y),
-                                                                  static_cast<const float*>(s->z), s->weight, static_cast<float*>(out));
-  }
+  const int gs = gate_norm_group(s, zs, {s->y, s->z, out});
+  const size_t nblk = gs ? (ntok + kGnThreads / gs - 1) / (kGnThreads / gs) : ntok;
+  const unsigned grid = (unsigned)(nblk < 148u * 8u ? nblk : 148u * 8u);
+  auto launch = [&](auto tag) {
+    using T = decltype(tag);
+    const T *y = static_cast<const T*>(s->y), *z = static_cast<const T*>(s->z);
+    T* o = static_cast<T*>(out);
+    if (gs)
+      gate_norm_dispatch(gs, s->channels / (int)(16 / sizeof(T)), [&](auto G, auto N) {
+        k_gate_norm_fwd_vec<T, decltype(G)::value, decltype(N)::value><<<grid, kGnThreads, 0, ctx->stream>>>(
+            ntok, s->channels, zs, s->eps, y, z, s->weight, o);
+      });
+    else k_gate_norm_fwd<T><<<grid, kGnThreads, 0, ctx->stream>>>(ntok, s->channels, zs, s->eps, y, z, s->weight, o);
+  };
+  if (s->dtype == M3_BF16) launch(__nv_bfloat16{}); else launch(float{});
   M3_CUDA(ctx, cudaGetLastError());
   ctx->launches += 1;
   return M3_OK;
@@ -851,20 +1031,24 @@ int m3_gate_norm_backward(m3_ctx* ctx, const m3_gate_norm_desc* s, const void* d
   }
   const size_t ntok = (size_t)s->batch * s->seq;
   const long long zs = s->z_stride ? s->z_stride : s->channels;
-  const unsigned grid = (unsigned)(ntok < 148u * 4u ? ntok : 148u * 4u);
+  const int gs = gate_norm_group(s, zs, {s->y, s->z, dout, dy, dz});
+  const size_t nblk = gs ? (ntok + kGnThreads / gs - 1) / (kGnThreads / gs) : ntok;
+  const unsigned grid = (unsigned)(nblk < 148u * 4u ? nblk : 148u * 4u);
   float* part = nullptr;
   if (want_w) M3_CUDA(ctx, m3::scratch_alloc(ctx, reinterpret_cast<void**>(&part), (size_t)grid * s->channels * sizeof(float), ctx->stream));
-  if (s->dtype == M3_BF16) {
-    using T = __nv_bfloat16;
-    k_gate_norm_bwd<T><<<grid, kGnThreads, 0, ctx->stream>>>(ntok, s->channels, zs, s->eps, static_cast<const T*>(s->y),
-                                                              static_cast<const T*>(s->z), s->weight, static_cast<const T*>(dout),
-                                                              static_cast<T*>(dy), static_cast<T*>(dz), part);
-  } else {
-    k_gate_norm_bwd<float><<<grid, kGnThreads, 0, ctx->stream>>>(ntok, s->channels, zs, s->eps, static_cast<const float*>(s->y),
-                                                                  static_cast<const float*>(s->z), s->weight,
-                                                                  static_cast<const float*>(dout), static_cast<float*>(dy),
-                                                                  static_cast<float*>(dz), part);
-  }
+  auto launch = [&](auto tag) {
+    using T = decltype(tag);
+    const T *y = static_cast<const T*>(s->y), *z = static_cast<const T*>(s->z), *g = static_cast<const T*>(dout);
+    T *py = static_cast<T*>(dy), *pz = static_cast<T*>(dz);
+    const size_t sm = part ? (size_t)s->channels * sizeof(float) : 0;
+    if (gs)
+      gate_norm_dispatch(gs, s->channels / (int)(16 / sizeof(T)), [&](auto G, auto N) {
+        k_gate_norm_bwd_vec<T, decltype(G)::value, decltype(N)::value><<<grid, kGnThreads, gs == 32 ? sm : 0, ctx->stream>>>(
+            ntok, s->channels, zs, s->eps, y, z, s->weight, g, py, pz, part);
+      });
+    else k_gate_norm_bwd<T><<<grid, kGnThreads, 0, ctx->stream>>>(ntok, s->channels, zs, s->eps, y, z, s->weight, g, py, pz, part);
+  };
+  if (s->dtype == M3_BF16) launch(__nv_bfloat16{}); else launch(float{});
   cudaError_t e = cudaGetLastError();
   ctx->launches += 1;
   if (e == cudaSuccess && want_w) {

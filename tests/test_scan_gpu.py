@@ -950,9 +950,11 @@ def test_mixer_core_post_gate_norm_matches_the_oracle(dtype, rank, channels_odd)
         MixerCore(MixerShape(2, 4, 6), bidirectional=True, post_gate_norm=True, device="cuda")
 
 
-def test_gate_norm_c_abi_edges():
+@pytest.mark.parametrize("Cn,W,off", [(1000, 1300, 100), (4096, 4300, 104), (1001, 1300, 99)])
+def test_gate_norm_c_abi_edges(Cn, W, off):
     """m3_gate_norm_*: z as a band of a wider row, a norm without gain, outputs that are not wanted, and
-    the channel limit."""
+    the channel limit; a warp per row, a block per row, and the element-wise kernels for rows that are not
+    whole 16-byte vectors."""
     import ctypes as C
     from mamba_trainer_b200 import _ffi
     from mamba_trainer_b200.ssm.scan import Context
@@ -960,27 +962,27 @@ def test_gate_norm_c_abi_edges():
     ctx = Context.for_device(torch.device("cuda"))
     lib, hd = ctx.lib, ctx.handle
     torch.manual_seed(2)
-    B, T, Cn, W = 3, 37, 1000, 1300
+    B, T = 3, 37
     y = torch.randn(B, T, Cn, device="cuda")
     wide = torch.randn(B, T, W, device="cuda")
     dout = torch.randn(B, T, Cn, device="cuda")
     ptr = lambda t, off=0: C.c_void_p(t.data_ptr() + off * t.element_size()) if t is not None else None
     for gain in (None, 1.0 + 0.3 * torch.randn(Cn, device="cuda")):
-        d = _ffi.GateNormDesc(batch=B, seq=T, channels=Cn, dtype=0, z_stride=W, y=ptr(y), z=ptr(wide, 100), weight=ptr(gain), eps=1e-5)
+        d = _ffi.GateNormDesc(batch=B, seq=T, channels=Cn, dtype=0, z_stride=W, y=ptr(y), z=ptr(wide, off), weight=ptr(gain), eps=1e-5)
         out, dy, dwide = torch.empty_like(y), torch.empty_like(y), torch.zeros_like(wide)
         dw = torch.full((Cn,), 7.0, device="cuda")
         ctx.check(lib.m3_gate_norm_forward(hd, C.byref(d), ptr(out)))
-        ctx.check(lib.m3_gate_norm_backward(hd, C.byref(d), ptr(dout), ptr(dy), ptr(dwide, 100), ptr(dw)))
+        ctx.check(lib.m3_gate_norm_backward(hd, C.byref(d), ptr(dout), ptr(dy), ptr(dwide, off), ptr(dw)))
         yd = y.double().requires_grad_(True)
-        zd = wide[..., 100:100 + Cn].double().requires_grad_(True)
+        zd = wide[..., off:off + Cn].double().requires_grad_(True)
         gd = gain.double().requires_grad_(True) if gain is not None else None
         n = yd * torch.rsqrt(yd.pow(2).mean(-1, keepdim=True) + 1e-5)
         e = (n * gd if gd is not None else n) * torch.nn.functional.silu(zd)
         eg = torch.autograd.grad(e, [yd, zd] + ([gd] if gd is not None else []), grad_outputs=dout.double())
         check_f32("out", out, e.detach())
         check_f32("dy", dy, eg[0])
-        check_f32("dz", dwide[..., 100:100 + Cn], eg[1])
-        assert float(dwide[..., :100].abs().max()) == 0.0 and float(dwide[..., 100 + Cn:].abs().max()) == 0.0
+        check_f32("dz", dwide[..., off:off + Cn], eg[1])
+        assert float(dwide[..., :off].abs().max()) == 0.0 and float(dwide[..., off + Cn:].abs().max()) == 0.0
         if gain is not None:
             check_f32("dweight", dw, eg[2])
             ctx.check(lib.m3_gate_norm_backward(hd, C.byref(d), ptr(dout), None, None, ptr(dw)))   # d gain alone
