@@ -543,6 +543,13 @@ def main():
         per_th = traffic_per_token_head(w, torch.cuda.get_device_properties(dev).multi_processor_count)
         cfg = workload_config(gw, world, args.config)
         cfg["batch_per_gpu"] = w.batch
+        # rank 1 with real dynamics takes the direct form of the stripe kernels, float32 the generic family
+        direct = w.rank == 1 and not w.rotational
+        if w.dtype != torch.bfloat16:
+            fwd_name, bwd_name = "generic family (k_chunk_state ... k_chunk_out)", "generic family (kb_* kernels)"
+        else:
+            fwd_name = "tc_fwd_direct_kernel" if direct else "tc_fwd_kernel"
+            bwd_name = "tc_bwd_direct_kernel" if direct else "tc_bwd_kernel"
         if fallback_note:
             cfg["fallback"] = fallback_note
         line = {
@@ -553,9 +560,9 @@ def main():
             "config": cfg,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": per_th * th if per_th else None, "peak_kind": peak_kind,
-                         "kernel": "tc_bwd_kernel (backward stripe kernel, with its two finalisation launches)",
+                         "kernel": bwd_name + " (backward stripe kernel, with its two finalisation launches)",
                          "ms_per_launch": bwd_ms, "algorithmic_bytes_per_launch": bwd_bytes,
-                         "forward": {"kernel": "tc_fwd_kernel", "ms_per_launch": fwd_ms,
+                         "forward": {"kernel": fwd_name, "ms_per_launch": fwd_ms,
                                      "achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
                                      "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak},
                          "whole_step": {"achieved": whole, "frac": whole / peak, "frac_of_8TBs": whole / 8000.0,
