@@ -302,11 +302,17 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
       if (!dead) commit_px<R>(raw_x, sX, sXw, ts.sw);
       if (!dead && k + 1 < k_hi) issue_px<R>(raw_x, p.x, tok0 + (size_t)LT * Hs, Hs, T, t0 + LT);
       // ---- 2. band, decays ---------------------------------------------------------------------
+      // this row's scalars and the chunks' row factors need no product: they are taken before the wait
+      const int l = row / R;
+      const float acl = s_ac[l];
+      const float eac = s_eac[l];
+      const float ecd = __expf(fmaxf(s_ac[LT - 1], -60.0f));
+      float rfs[4];
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) rfs[cc] = row_factor(acl, s_ac[(64 * ch + 16 * cc) / R + 16 / R - 1]);
       if (!dead) dead = !warp_all(mbar_wait(&bars[0], g & 1, wait_limit));
       if (!dead) {
         tc_fence_after();
-        const int l = row / R;
-        const float acl = s_ac[l];
         const int lmax = (quad * 32 + 31) / R;  // last time step held by this warp
         float g[4][16], yv[2][16], hv[2][16];
 #pragma unroll
@@ -324,8 +330,6 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
         for (int cc = 0; cc < 4; ++cc) tmem_ld_fence(g[cc]);
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) { tmem_ld_fence(yv[cc]); tmem_ld_fence(hv[cc]); }
-        const float eac = s_eac[l];
-        const float ecd = __expf(fmaxf(s_ac[LT - 1], -60.0f));
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
           const int p0 = 32 * ch + 16 * cc;
@@ -350,7 +354,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_fwd_kernel(const __grid_con
             ColScalars<R> cs;
             load_col_scalars<R>(cs, ts, c0);
             const int s0 = c0 / R;
-            const float rf = row_factor(acl, s_ac[s0 + 16 / R - 1]);  // one exponential per chunk
+            const float rf = rfs[cc];  // one exponential per chunk
             if (s0 + 16 / R - 1 < (quad * 32) / R) {
               // strictly below the diagonal for all 32 rows of this warp: the weight needs no selects and,
               // for one rank, is shared by every row up to the row factor
