@@ -344,26 +344,31 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
         epi_signal(BAR_OPS0, kPairCount, dead);
         if (!dead) load_bc_staged<R, ROT>(raw_bc, sB, sC, rev);
         epi_sync();  // every warp holds its share of the rows of B and C (and the angle table is complete)
-        if (!dead) {
-          store_bc<R, ROT>(raw_bc, sB, sC, sTab);
-          if (ROT) {  // this row's (cos, sin) words into TMEM, for the un-rotation after phase B
-#pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-              float v[16];
-#pragma unroll
-              for (int j4 = 0; j4 < 4; ++j4) {
-                const float4 q4 = *reinterpret_cast<const float4*>(&sTab[phi_idx(rl, 16 * c4 + 4 * j4)]);
-                v[4 * j4] = q4.x; v[4 * j4 + 1] = q4.y; v[4 * j4 + 2] = q4.z; v[4 * j4 + 3] = q4.w;
-              }
-              tmem_st16(tmem_addr(tm, quad * 32, TM_TAB + 16 * c4), v);
-            }
-            tmem_wait_st();
-          }
-        }
+        if (!dead) store_bc<R, ROT>(raw_bc, sB, sC, sTab);
       }
       fence_async_smem();
       tc_fence_before();
       epi_signal(BAR_OPS, kPairCount, dead);
+      if (ROT) {
+        // This row's (cos, sin) words go into TMEM, for the un-rotation after phase B, while C^ B^^T runs: the
+        // product does not read them.  The table lies where the first 128 / R rows of M are about to be
+        // written, so the warps that write those rows (the lower quadrants, the ones with time to spare in
+        // epilogue A) wait until every warp has its words; the others only report.
+        if (!dead) {
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            float v[16];
+#pragma unroll
+            for (int j4 = 0; j4 < 4; ++j4) {
+              const float4 q4 = *reinterpret_cast<const float4*>(&sTab[phi_idx(rl, 16 * c4 + 4 * j4)]);
+              v[4 * j4] = q4.x; v[4 * j4 + 1] = q4.y; v[4 * j4 + 2] = q4.z; v[4 * j4 + 3] = q4.w;
+            }
+            tmem_st16(tmem_addr(tm, quad * 32, TM_TAB + 16 * c4), v);
+          }
+          tmem_wait_st();
+        }
+        if (quad * 32 < kRows / R) bar_sync(BAR_TABLE, kEpiThreads); else bar_arrive(BAR_TABLE, kEpiThreads);
+      }
       if (!dead) dead = !warp_all(mbar_wait(&bars[0], it & 1, wait_limit));
       // ---- 3. epilogue A -------------------------------------------------------------------------
       const float acl = ts.ac[rl];

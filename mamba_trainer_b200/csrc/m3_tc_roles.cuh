@@ -38,6 +38,7 @@ enum : int {
                       // scalars have been picked up, and a barrier holds one pending phase only
   BAR_FREE = 5,   // 288: a set of scalars is free again (epilogue warps arrive; look-ahead warp syncs)
   BAR_TAIL = 6,   // 288: a tile's gradients are staged, its operands spent (epilogue warps arrive; copy warp syncs)
+  BAR_TABLE = 8,  // 256: (backward) every epilogue warp has copied its angle-table words out of the buffer M takes over
   BAR_OPS0 = 9,   // 288: the x / dy operands of a tile are staged, ahead of B and C (epilogue warps arrive; issuer syncs)
 };
 
