@@ -516,10 +516,11 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tc_bwd_kernel(const __grid_con
         }
         tmem_wait_st();
       }
-      const float dcd = ecd * inside(cd) * epi_sum(dcd_part, s_red);
       fence_async_smem();
       tc_fence_before();
       epi_signal(BAR_MID, kPairCount, dead);
+      // (the sum behind d cd is wanted by the tile's last step only: it is taken while phase B runs)
+      const float dcd = ecd * inside(cd) * epi_sum(dcd_part, s_red);
       // ---- 4. epilogue B -------------------------------------------------------------------------
       if (!dead) dead = !warp_all(mbar_wait(&bars[1], it & 1, wait_limit));
       const int t = t0 + rl;
