@@ -30,7 +30,11 @@ def test_mixer_core_rejects_inconsistent_configurations():
     with pytest.raises(ConfigError):
         MixerCore(MixerShape(heads=2, head_dim=4, d_state=8, learned_lambda=False),
                   discretization=Discretization.LearnedTrapezoid)
+    with pytest.raises(ConfigError):
+        MixerCore(MixerShape(heads=2, head_dim=4, d_state=8), bidirectional=True, post_gate_norm=True)   # mamba3.rs:175-179
+    assert MixerCore(MixerShape(heads=2, head_dim=4, d_state=8, rank=2), post_gate_norm=True).post_norm_w.shape == (16,)
     core = MixerCore(MixerShape(heads=2, head_dim=4, d_state=8))
+    assert core.post_norm_w is None
     assert core.conv_w.shape == (4, 2 * 4 + 2 * 2 * 8) and core.norm_w.shape == (8,)
     with pytest.raises(ShapeError):
         core(torch.zeros(1, 3, core.shape.in_proj_width + 1))

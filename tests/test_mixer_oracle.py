@@ -68,3 +68,26 @@ def test_mixer_core_matches_reference_port():
         if n == "conv_w":
             want = want[:, 0, :].T
         assert rel_err(g, want) < 1e-11, n
+
+
+def test_post_gate_norm_is_the_norm_of_the_ungated_output_times_the_gate():
+    """SsmConfig::post_gate_norm (src/ssm/config.rs:113; Mamba3Mixer::finish, src/models/mamba3.rs:475-484;
+    RmsNorm::apply, src/nn/norm.rs:95-105): gated' = rms_norm(y) * gain * silu(z) where the port's own path
+    gives gated = y * silu(z).  The port has no such switch, so the branch is pinned through the port's vectors
+    for everything up to y (y = gated / silu(z)) and the norm's definition written out here."""
+    z, p = core_golden()
+    B, T, H, P, N = (int(v) for v in z["dims"])
+    d_inner = H * P
+    proj = T64(z["proj"])
+    pt = {k: T64(v) for k, v in p.items()}
+    g = torch.Generator().manual_seed(4)
+    pt["post_norm_w"] = 1.0 + 0.3 * torch.randn(d_inner, generator=g, dtype=torch.float64)
+    got, _, _ = M.mixer_core(proj, pt, H, P, N, chunk=int(z["chunk"]), eps=float(z["eps"]), post_gate_norm=True)
+    gate = torch.nn.functional.silu(proj[..., :d_inner])
+    y = T64(z["gated"]) / gate                                   # the port's scan output, flattened
+    want = y / torch.sqrt((y * y).mean(-1, keepdim=True) + float(z["eps"])) * pt["post_norm_w"] * gate
+    assert rel_err(got, want) < 1e-9
+    # without a gain the norm still applies
+    del pt["post_norm_w"]
+    got1, _, _ = M.mixer_core(proj, pt, H, P, N, chunk=int(z["chunk"]), eps=float(z["eps"]), post_gate_norm=True)
+    assert rel_err(got1, want / (1.0 + 0.3 * torch.randn(d_inner, generator=torch.Generator().manual_seed(4), dtype=torch.float64))) < 1e-9
